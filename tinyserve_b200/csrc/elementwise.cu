@@ -1,0 +1,144 @@
+// Embedding gather, residual-add + RMSNorm, rotary tables, SiLU-multiply.
+//
+// Rounding points follow the upstream engine's contract (src/tinyserve/layers.py:35-38,
+// src/tinyserve/model.py:178-179): the norm is computed in 32-bit, cast to the model dtype,
+// then multiplied by the weight in the model dtype; silu(gate) is rounded before the product.
+// The residual stream itself is kept in 32-bit, so the residual sum is a 32-bit sum.
+#include "common.cuh"
+
+namespace ts {
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = float(table[tokens[t], :]).  A token id outside [0, vocab) yields a NaN row
+// instead of an out-of-bounds read (the host checks ids too).
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                             float* __restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  const int id = tokens[t];
+  float* o = out + (size_t)t * hidden;
+  if (id < 0 || id >= vocab) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const T* row = table + (size_t)id * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+// ------------------------------------------------------- residual add + RMSNorm
+// x = resid[row] (+ delta[row]);  if rows == nullptr the sum is written back to resid.
+// out[r] = T(x * rsqrt(mean(x^2) + eps)) * weight, the product rounded to T.
+template <typename T>
+__global__ void add_rms_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                    const T* __restrict__ weight, T* __restrict__ out,
+                                    const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* x = resid + (size_t)row * hidden;
+  const T* d = delta ? delta + (size_t)row * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && (d != nullptr);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = x[i];
+    if (d) v += to_float(d[i]);
+    if (write_back) x[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = x[i];
+    if (d && !write_back) v += to_float(d[i]);
+    const float n = round_to<T>(v * rstd);
+    o[i] = from_float<T>(n * to_float(weight[i]));
+  }
+}
+
+// ------------------------------------------------------------ rotary tables
+// angle = position * inv_freq in float64; cos and sin in float64, rounded to float32.
+__global__ void rope_tables_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
+                                   float* __restrict__ cos_out, float* __restrict__ sin_out,
+                                   int num_tokens, int half) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= num_tokens * half) return;
+  const int t = idx / half, i = idx - t * half;
+  const double a = (double)positions[t] * inv_freq[i];
+  double s, c;
+  sincos(a, &s, &c);
+  cos_out[idx] = (float)c;
+  sin_out[idx] = (float)s;
+}
+
+// ------------------------------------------------------------- SiLU-multiply
+// out[t, j] = T(silu(gate_up[t, j])) * gate_up[t, inter + j]
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const size_t t = idx / inter;
+    const int j = (int)(idx - t * inter);
+    const float g = to_float(gate_up[t * 2 * inter + j]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + j]);
+    const float s = round_to<T>(g / (1.f + expf(-g)));
+    out[idx] = from_float<T>(s * u);
+  }
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+extern "C" int ts_embed(const int* tokens, const void* table, float* out, int num_tokens, int hidden,
+                        int vocab, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == TS_DTYPE_F32)
+    embed_kernel<float><<<num_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, hidden, vocab);
+  else if (dtype == TS_DTYPE_BF16)
+    embed_kernel<bf16><<<num_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, out, hidden, vocab);
+  else
+    return TS_ERR_BAD_ARGUMENT;
+  return launch_status();
+}
+
+extern "C" int ts_add_rms_norm(float* resid, const void* delta, const void* weight, void* out,
+                               const int* rows, int num_rows, int hidden, float eps, int dtype,
+                               cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (dtype == TS_DTYPE_F32)
+    add_rms_norm_kernel<float><<<num_rows, threads, 0, stream>>>(resid, (const float*)delta, (const float*)weight,
+                                                                 (float*)out, rows, hidden, eps);
+  else if (dtype == TS_DTYPE_BF16)
+    add_rms_norm_kernel<bf16><<<num_rows, threads, 0, stream>>>(resid, (const bf16*)delta, (const bf16*)weight,
+                                                                (bf16*)out, rows, hidden, eps);
+  else
+    return TS_ERR_BAD_ARGUMENT;
+  return launch_status();
+}
+
+extern "C" int ts_rope_tables(const int* positions, const double* inv_freq, float* cos_out, float* sin_out,
+                              int num_tokens, int half, cudaStream_t stream) {
+  const int total = num_tokens * half;
+  if (total <= 0) return 0;
+  rope_tables_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, cos_out, sin_out, num_tokens, half);
+  return launch_status();
+}
+
+extern "C" int ts_silu_mul(const void* gate_up, void* out, int num_tokens, int inter, int dtype,
+                           cudaStream_t stream) {
+  const size_t total = (size_t)num_tokens * inter;
+  if (total == 0) return 0;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == TS_DTYPE_F32)
+    silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+  else if (dtype == TS_DTYPE_BF16)
+    silu_mul_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+  else
+    return TS_ERR_BAD_ARGUMENT;
+  return launch_status();
+}

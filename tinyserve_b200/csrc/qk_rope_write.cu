@@ -1,0 +1,120 @@
+// Per-head q/k RMSNorm + rotary position encoding + write of k and v into the paged cache,
+// one launch per layer (the upstream engine's fused kernel does the same per (token, head):
+// src/tinyserve/triton_fused.py:43-113; formulas src/tinyserve/layers.py:35-38,84-91).
+//
+// One warp handles one (token, head). q heads: normalise, rotate, write to q_out[t, h, :].
+// k heads: normalise, rotate, write to k_cache at the token's slot. v heads: copy to v_cache.
+// Norm: 32-bit mean of squares over head_dim, value cast to T, times the weight, rounded to T.
+// Rotation in 32-bit on the rounded values, result rounded to T once.
+// Cache layout: [page, kv_head, offset_in_page, head_dim]; slot = page * page_size + offset.
+#include "common.cuh"
+
+namespace ts {
+
+constexpr int QK_WARPS = 4;
+constexpr int QK_MAX_HEAD_DIM = 512;
+
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, const T* __restrict__ q_weight,
+    const T* __restrict__ k_weight, float eps, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, int rotary_dim, int interleaved, const int* __restrict__ slots,
+    T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_tokens, int num_heads,
+    int num_kv_heads, int head_dim, int write_kv) {
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* buf = smem + warp * head_dim;
+  const int heads_per_token = write_kv ? num_heads + 2 * num_kv_heads : num_heads;
+  const long long item = (long long)blockIdx.x * QK_WARPS + warp;
+  if (item >= (long long)num_tokens * heads_per_token) return;
+  const int t = (int)(item / heads_per_token);
+  const int h = (int)(item - (long long)t * heads_per_token);
+  const T* src = qkv + ((size_t)t * heads_per_token + h) * head_dim;
+
+  // where this head goes
+  T* dst;
+  const T* weight = nullptr;
+  bool rotate = rotary_dim > 0;
+  if (h < num_heads) {
+    dst = q_out + ((size_t)t * num_heads + h) * head_dim;
+    weight = q_weight;
+  } else {
+    const int slot = slots[t];
+    const int page = slot / page_size, off = slot - page * page_size;
+    const bool is_k = h < num_heads + num_kv_heads;
+    const int kvh = is_k ? h - num_heads : h - num_heads - num_kv_heads;
+    T* cache = is_k ? k_cache : v_cache;
+    dst = cache + (((size_t)page * num_kv_heads + kvh) * page_size + off) * head_dim;
+    if (is_k) {
+      weight = k_weight;
+    } else {
+      for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+      return;
+    }
+  }
+
+  // norm (optional)
+  if (weight != nullptr) {
+    float ss = 0.f;
+    for (int i = lane; i < head_dim; i += 32) {
+      const float v = to_float(src[i]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)head_dim + eps);
+    for (int i = lane; i < head_dim; i += 32) {
+      const float n = round_to<T>(to_float(src[i]) * rstd);
+      buf[i] = round_to<T>(n * to_float(weight[i]));
+    }
+  } else {
+    for (int i = lane; i < head_dim; i += 32) buf[i] = to_float(src[i]);
+  }
+  __syncwarp();
+
+  if (!rotate) {
+    for (int i = lane; i < head_dim; i += 32) dst[i] = from_float<T>(buf[i]);
+    return;
+  }
+  const int half = rotary_dim >> 1;
+  const float* c = cos_t + (size_t)t * half;
+  const float* s = sin_t + (size_t)t * half;
+  for (int p = lane; p < half; p += 32) {
+    const int ia = interleaved ? 2 * p : p;
+    const int ib = interleaved ? 2 * p + 1 : p + half;
+    const float a = buf[ia], b = buf[ib];
+    dst[ia] = from_float<T>(a * c[p] - b * s[p]);
+    dst[ib] = from_float<T>(b * c[p] + a * s[p]);
+  }
+  for (int i = rotary_dim + lane; i < head_dim; i += 32) dst[i] = from_float<T>(buf[i]);
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+extern "C" int ts_qk_norm_rope_write(const void* qkv, void* q_out, const void* q_weight, const void* k_weight,
+                                     float eps, const float* cos_t, const float* sin_t, int rotary_dim,
+                                     int interleaved, const int* slots, void* k_cache, void* v_cache,
+                                     int page_size, int num_tokens, int num_heads, int num_kv_heads,
+                                     int head_dim, int write_kv, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (head_dim <= 0 || head_dim > QK_MAX_HEAD_DIM || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
+    return TS_ERR_UNSUPPORTED;
+  const int heads_per_token = write_kv ? num_heads + 2 * num_kv_heads : num_heads;
+  const long long items = (long long)num_tokens * heads_per_token;
+  const int blocks = (int)((items + QK_WARPS - 1) / QK_WARPS);
+  const size_t smem = (size_t)QK_WARPS * head_dim * sizeof(float);
+  if (dtype == TS_DTYPE_F32)
+    qk_norm_rope_write_kernel<float><<<blocks, QK_WARPS * 32, smem, stream>>>(
+        (const float*)qkv, (float*)q_out, (const float*)q_weight, (const float*)k_weight, eps, cos_t, sin_t,
+        rotary_dim, interleaved, slots, (float*)k_cache, (float*)v_cache, page_size, num_tokens, num_heads,
+        num_kv_heads, head_dim, write_kv);
+  else if (dtype == TS_DTYPE_BF16)
+    qk_norm_rope_write_kernel<bf16><<<blocks, QK_WARPS * 32, smem, stream>>>(
+        (const bf16*)qkv, (bf16*)q_out, (const bf16*)q_weight, (const bf16*)k_weight, eps, cos_t, sin_t,
+        rotary_dim, interleaved, slots, (bf16*)k_cache, (bf16*)v_cache, page_size, num_tokens, num_heads,
+        num_kv_heads, head_dim, write_kv);
+  else
+    return TS_ERR_BAD_ARGUMENT;
+  return launch_status();
+}

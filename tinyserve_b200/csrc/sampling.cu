@@ -1,0 +1,164 @@
+// Next-token selection on the device: greedy argmax, temperature sampling, nucleus (top-p).
+//
+// Meaning of the options follows upstream src/tinyserve/sampling.py:56-102: temperature 0 is
+// the argmax of the raw 32-bit logits; otherwise the token is drawn from softmax(logits / T)
+// by the exponential race argmax_i p_i / E_i with E_i ~ Exp(1); with top_p < 1 only tokens are
+// eligible whose more likely tokens together hold less than top_p of the mass (the most likely
+// token always is), without renormalising. Differences: the noise comes from a counter-based
+// generator (Philox4x32-10) keyed by the request's seed and indexed by (how many tokens the
+// request has drawn, token id), so a request's tokens do not depend on its batch-mates, on
+// chunking or on recomputation; tokens of exactly equal probability are kept or dropped
+// together by top-p; the race is run on log p_i - log E_i, which orders the same way.
+#include "common.cuh"
+
+namespace ts {
+
+constexpr int SM_THREADS = 1024;
+
+struct Best {
+  float v;
+  int i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  if (b.i < 0) return a;
+  if (a.i < 0) return b;
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+__device__ __forceinline__ Best block_best(Best x, Best* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best y;
+    y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+    x = better(x, y);
+  }
+  __syncthreads();
+  if (lane == 0) scratch[warp] = x;
+  __syncthreads();
+  Best t;
+  t.v = 0.f; t.i = -1;
+  if (lane < nwarps) t = scratch[lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best y;
+    y.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+    t = better(t, y);
+  }
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                                              uint32_t k1, uint32_t out[4]) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+// -log(u) with u uniform in (0, 1) on a 24-bit grid: never 0, never infinite.
+__device__ __forceinline__ float exp1_from_bits(uint32_t x) {
+  const float u = ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  return -logf(u);
+}
+
+__global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restrict__ logits, int vocab,
+                                                            const float* __restrict__ temperature,
+                                                            const float* __restrict__ top_p,
+                                                            const long long* __restrict__ seeds,
+                                                            const long long* __restrict__ draws,
+                                                            int* __restrict__ out) {
+  __shared__ float fscratch[33];
+  __shared__ Best bscratch[32];
+  const int row = blockIdx.x;
+  const float* l = logits + (size_t)row * vocab;
+  const float temp = temperature ? temperature[row] : 0.f;
+  Best best;
+  best.v = 0.f; best.i = -1;
+  if (!(temp > 0.f)) {   // greedy
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      Best c; c.v = l[i]; c.i = i;
+      best = better(best, c);
+    }
+    best = block_best(best, bscratch);
+    if (threadIdx.x == 0) out[row] = best.i < 0 ? 0 : best.i;
+    return;
+  }
+  const float inv_t = 1.f / temp;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, l[i] * inv_t);
+  mx = block_max(mx, fscratch);
+
+  float threshold = 0.f;   // keep tokens with exp(z - mx) >= threshold
+  const float tp = top_p ? top_p[row] : 1.f;
+  if (tp < 1.f) {
+    float z = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) z += expf(l[i] * inv_t - mx);
+    z = block_sum(z, fscratch);
+    const float target = tp * z;
+    // smallest bit pattern b in [0, bits(1.0)] with mass{e > float(b)} < target
+    uint32_t lo = 0u, hi = 0x3f800000u;   // the answer is <= bits(1.0): nothing exceeds 1
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo) >> 1);
+      const float t = __uint_as_float(mid);
+      float mass = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float e = expf(l[i] * inv_t - mx);
+        if (e > t) mass += e;
+      }
+      mass = block_sum(mass, fscratch);
+      if (mass < target) hi = mid; else lo = mid + 1u;
+    }
+    threshold = __uint_as_float(lo);
+  }
+  const uint32_t k0 = (uint32_t)(seeds[row] & 0xffffffffll), k1 = (uint32_t)((unsigned long long)seeds[row] >> 32);
+  const uint32_t d0 = (uint32_t)(draws[row] & 0xffffffffll), d1 = (uint32_t)((unsigned long long)draws[row] >> 32);
+  for (int i4 = threadIdx.x; i4 * 4 < vocab; i4 += blockDim.x) {
+    uint32_t r[4];
+    philox4x32_10((uint32_t)i4, d0, d1, 0u, k0, k1, r);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = i4 * 4 + e;
+      if (i < vocab) {
+        const float zc = l[i] * inv_t - mx;
+        if (expf(zc) >= threshold) {
+          Best c; c.v = zc - logf(exp1_from_bits(r[e])); c.i = i;
+          best = better(best, c);
+        }
+      }
+    }
+  }
+  best = block_best(best, bscratch);
+  if (threadIdx.x == 0) out[row] = best.i < 0 ? 0 : best.i;
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+// temperature/top_p/seeds/draws may all be null for an all-greedy batch.
+extern "C" int ts_sample(const float* logits, int num_rows, int vocab, const float* temperature,
+                         const float* top_p, const long long* seeds, const long long* draws, int* out,
+                         cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (vocab <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (temperature != nullptr && (seeds == nullptr || draws == nullptr)) return TS_ERR_BAD_ARGUMENT;
+  sample_kernel<<<num_rows, SM_THREADS, 0, stream>>>(logits, vocab, temperature, top_p, seeds, draws, out);
+  return launch_status();
+}

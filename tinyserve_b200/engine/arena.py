@@ -1,0 +1,78 @@
+"""Scratch memory of a step: a bump allocator over buffers that are reused every step.
+
+Three regions: ``step`` holds what lives for the whole step (the residual stream, position
+tables, logits); two ``frames`` alternate from layer to layer, so that the output a layer
+leaves pending on the residual stream is still intact while the next layer, working in the
+other frame, reads it. Nothing is allocated from the device allocator in steady state; a
+region grows (once, outside any graph capture) when a step needs more than it has.
+"""
+
+from __future__ import annotations
+
+import torch
+
+_ALIGN = 256
+
+
+class _Region:
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.buf = torch.empty(0, dtype=torch.uint8, device=device)
+        self.used = 0
+        self.high_water = 0
+
+    def reset(self) -> None:
+        self.used = 0
+
+    def take(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        start = (self.used + _ALIGN - 1) // _ALIGN * _ALIGN
+        end = start + nbytes
+        if end > self.buf.numel():
+            # Grow: views handed out earlier keep the old buffer alive until they die.
+            grow = max(end, 2 * self.buf.numel(), 1 << 16)
+            self.buf = torch.empty(grow, dtype=torch.uint8, device=self.device)
+            start, end = 0, nbytes
+        self.used = end
+        self.high_water = max(self.high_water, end)
+        if numel == 0:
+            return torch.empty(shape, dtype=dtype, device=self.device)
+        return self.buf[start:end].view(dtype).view(shape)
+
+
+class Arena:
+    def __init__(self, device: torch.device | str) -> None:
+        self.device = torch.device(device)
+        self._step = _Region(self.device)
+        self._frames = (_Region(self.device), _Region(self.device))
+        self._current = self._step
+        self._frame_index = 0
+
+    def begin_step(self) -> None:
+        self._step.reset()
+        for f in self._frames:
+            f.reset()
+        self._current = self._step
+        self._frame_index = 0
+
+    def next_frame(self) -> None:
+        self._frame_index ^= 1
+        self._current = self._frames[self._frame_index]
+        self._current.reset()
+
+    def step_region(self) -> None:
+        """Later takes live until the end of the step (used after the last layer)."""
+        self._current = self._step
+
+    def take(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        return self._current.take(tuple(shape), dtype)
+
+    def take_step(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        return self._step.take(tuple(shape), dtype)
+
+    @property
+    def reserved_bytes(self) -> int:
+        return self._step.buf.numel() + sum(f.buf.numel() for f in self._frames)

@@ -1,0 +1,177 @@
+"""The step function: run a batch of (request, its next tokens) through the model, from the
+cache that earlier steps left, and return the logits at the wanted places.
+
+A batch is any mix of portions of prompts and single decoded tokens, flattened request
+after request without padding (after upstream src/tinyserve/batch.py:60-115 and
+src/tinyserve/model.py:259-329). The caller has already reserved room for the new tokens
+in each request's cache (``CacheManager.append``); this function only reads the tables. All
+per-step integers (tokens, positions, slots, block tables, lengths, wanted rows) are packed
+on the host into ONE pinned buffer and reach the device in one copy.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, RequestCache
+from ..model import DecoderModel
+from ..parts.base import KVGroupContext, StepContext
+from .arena import Arena
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: the request's cache and its next tokens, which must be
+    the LAST ``len(tokens)`` positions already reserved in that cache."""
+
+    cache: RequestCache
+    tokens: Sequence[int]
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager) -> None:
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.arena = Arena(self.device)
+        self._host: torch.Tensor | None = None     # pinned int32 staging buffer
+        self._host_np: np.ndarray | None = None
+        self._dev: torch.Tensor | None = None
+        self._copied: torch.cuda.Event | None = None   # the staging buffer's last copy
+        self.num_steps = 0
+
+    # ------------------------------------------------------------------ staging
+    def _staging(self, n: int) -> None:
+        if self._copied is not None:
+            # The host buffer is about to be rewritten: its last copy must have left it.
+            self._copied.synchronize()
+        if self._host is None or self._host.numel() < n:
+            cap = max(_round_up(n, 1024), 4096)
+            pin = self.device.type == "cuda"
+            self._host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
+            self._host_np = self._host.numpy()
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+
+    def build_context(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None
+                      ) -> tuple[StepContext, torch.Tensor | None, int]:
+        """Pack the step's integers and make the ``StepContext``. ``want[b]`` lists the
+        places among request b's tokens whose logits are asked for; ``None`` asks for the
+        last token of every request."""
+        if not entries:
+            raise ValueError("a step needs at least one request")
+        groups = self.cache.groups
+        b = len(entries)
+        query_lens = [len(e.tokens) for e in entries]
+        totals = [e.cache.num_tokens for e in entries]
+        for n, total in zip(query_lens, totals):
+            if not 0 < n <= total:
+                raise ValueError(f"{n} new tokens but the request's cache holds {total} positions")
+        t = sum(query_lens)
+        if want is None:
+            want = [[n - 1] for n in query_lens]
+        if len(want) != b:
+            raise ValueError(f"{b} requests but {len(want)} lists of wanted places")
+        rows: list[int] = []
+        start = 0
+        for n, places in zip(query_lens, want):
+            for p in places:
+                if not 0 <= p < n:
+                    raise ValueError(f"wanted place {p} is not among the request's {n} tokens")
+                rows.append(start + p)
+            start += n
+        r = len(rows)
+        widths = [max(len(e.cache.tables[g.index].pages) for e in entries) for g in groups]
+
+        # ---- layout of the packed buffer (every section starts on a 16-byte boundary)
+        off = 0
+
+        def section(n: int) -> slice:
+            nonlocal off
+            s = slice(off, off + n)
+            off = _round_up(off + n, 4)
+            return s
+
+        s_tokens, s_pos = section(t), section(t)
+        s_cu, s_ctx = section(b + 1), section(b)
+        s_dec, s_pre = section(b), section(b)
+        s_rows, s_state = section(r), section(b)
+        s_slots = [section(t) for _ in groups]
+        s_tables = [section(b * w) for w in widths]
+        self._staging(off)
+        buf = self._host_np
+
+        # ---- fill
+        tok = buf[s_tokens]
+        pos = buf[s_pos]
+        cu = buf[s_cu]
+        cu[0] = 0
+        at = 0
+        dec: list[int] = []
+        pre: list[int] = []
+        for i, (e, n, total) in enumerate(zip(entries, query_lens, totals)):
+            tok[at: at + n] = e.tokens
+            pos[at: at + n] = np.arange(total - n, total, dtype=np.int32)
+            at += n
+            cu[i + 1] = at
+            (dec if n == 1 else pre).append(i)
+        buf[s_ctx] = totals
+        buf[s_dec][: len(dec)] = dec
+        buf[s_pre][: len(pre)] = pre
+        buf[s_rows] = rows
+        buf[s_state] = [e.cache.state_slot for e in entries]
+        for g, ss, st, w in zip(groups, s_slots, s_tables, widths):
+            ps = g.page_size
+            slots = buf[ss]
+            table = buf[st].reshape(b, w)
+            table[:] = 0
+            at = 0
+            for i, (e, n, total) in enumerate(zip(entries, query_lens, totals)):
+                pages = e.cache.tables[g.index].pages_array()
+                table[i, : pages.shape[0]] = pages
+                p = pos[at: at + n]
+                slots[at: at + n] = pages[p // ps] * ps + p % ps
+                at += n
+
+        dev = self._dev
+        dev[:off].copy_(self._host[:off], non_blocking=True)
+        if self.device.type == "cuda":
+            if self._copied is None:
+                self._copied = torch.cuda.Event()
+            self._copied.record()
+
+        self.arena.begin_step()
+        kv = {
+            g.index: KVGroupContext(g.page_size, dev[st].view(b, w), dev[ss])
+            for g, ss, st, w in zip(groups, s_slots, s_tables, widths)
+        }
+        ctx = StepContext(
+            num_tokens=t, num_seqs=b, query_lens=query_lens, context_lens=totals,
+            tokens=dev[s_tokens], positions=dev[s_pos], cu_query_lens=dev[s_cu],
+            context_lens_dev=dev[s_ctx], decode_seqs=dev[s_dec], prefill_seqs=dev[s_pre],
+            num_decode=len(dec), num_prefill=len(pre), max_query_len=max(query_lens),
+            max_context_len=max(totals), kv=kv,
+            state_slots=dev[s_state] if self.cache.has_state else None,
+            state_slots_host=[e.cache.state_slot for e in entries],
+            arena=self.arena, dtype=self.model.dtype,
+        )
+        return ctx, (dev[s_rows] if r else None), r
+
+    # --------------------------------------------------------------------- step
+    @torch.inference_mode()
+    def step(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None = None
+             ) -> torch.Tensor | None:
+        """Run one step. Returns float32 logits ``[wanted, vocab]`` in the order of the entries
+        and of their wanted places (a view into step scratch: use it before the next step),
+        or ``None`` when nothing is wanted."""
+        ctx, rows, r = self.build_context(entries, want)
+        logits = self.model.forward(ctx, self.cache.entries, rows, r)
+        self.num_steps += 1
+        return logits

@@ -1,0 +1,272 @@
+"""The operations of the product path, each one a hand-written sm_100a kernel (or, for the
+plain bf16 matrix products, the vendor library, as the upstream engine uses one there).
+
+Every function checks its arguments on the host, then launches on the current CUDA stream.
+There is no CPU implementation and no alternative backend: without a CUDA device or the
+compiled library these functions raise. Tensors are contiguous; ``dt`` below is the model
+dtype (bfloat16 or float32) and selects the kernel instantiation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Any
+
+import torch
+
+from . import build
+
+_F32, _BF16 = 0, 1
+_c = ctypes
+_vp, _i, _f = _c.c_void_p, _c.c_int, _c.c_float
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or the launch failed."""
+
+
+_SIGNATURES: dict[str, list[Any]] = {
+    "ts_embed": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_add_rms_norm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp],
+    "ts_rope_tables": [_vp, _vp, _vp, _vp, _i, _i, _vp],
+    "ts_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
+    "ts_qk_norm_rope_write": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ts_paged_attention_simt": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
+                                _f, _i, _i, _vp, _vp, _i, _vp],
+    "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+}
+_fns: dict[str, Any] = {}
+
+
+def _fn(name: str) -> Any:
+    f = _fns.get(name)
+    if f is None:
+        lib = build.library()
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[name]
+        f.restype = _i
+        _fns[name] = f
+    return f
+
+
+def _check(status: int, name: str) -> None:
+    if status == 0:
+        return
+    if status == -1:
+        raise KernelError(f"{name}: bad argument")
+    if status == -2:
+        raise KernelError(f"{name}: size not supported by this kernel")
+    raise KernelError(f"{name}: CUDA error {status}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"dtype {dtype} is not supported (float32 or bfloat16)")
+
+
+def _dev(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> int:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _opt(t: torch.Tensor | None, name: str, dtype: torch.dtype | None = None) -> int | None:
+    return None if t is None else _dev(t, name, dtype)
+
+
+# ------------------------------------------------------------------ elementwise
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t] = float32(table[tokens[t]])``; tokens int32 ``[T]``, table ``[V, h]`` dt."""
+    t, h = out.shape
+    if tokens.shape != (t,) or table.shape[1] != h:
+        raise KernelError(f"embed: shapes {tuple(tokens.shape)}, {tuple(table.shape)}, {tuple(out.shape)}")
+    _check(_fn("ts_embed")(_dev(tokens, "tokens", torch.int32), _dev(table, "table"),
+                           _dev(out, "out", torch.float32), t, h, table.shape[0], _code(table.dtype),
+                           _stream()), "embed")
+
+
+def add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                 out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """``x = resid (+ delta)``; ``out = dt(x * rsqrt(mean(x^2) + eps)) * weight``.
+
+    Without ``rows`` every row is processed and the sum is written back to ``resid``
+    (float32). With ``rows`` (int32) only those rows are read, ``out`` has one row per entry
+    and ``resid`` is left unchanged."""
+    h = resid.shape[1]
+    n = out.shape[0]
+    dt = out.dtype
+    if weight.shape != (h,) or out.shape[1] != h or (delta is not None and delta.shape != resid.shape):
+        raise KernelError("add_rms_norm: shape mismatch")
+    if rows is None and n != resid.shape[0]:
+        raise KernelError("add_rms_norm: out must have one row per row of resid")
+    if rows is not None and rows.shape != (n,):
+        raise KernelError("add_rms_norm: rows must have one entry per row of out")
+    _check(_fn("ts_add_rms_norm")(_dev(resid, "resid", torch.float32), _opt(delta, "delta", dt),
+                                  _dev(weight, "weight", dt), _dev(out, "out"),
+                                  _opt(rows, "rows", torch.int32), n, h, float(eps), _code(dt), _stream()),
+           "add_rms_norm")
+
+
+def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+    """``cos/sin[t, i] = float32(cos/sin(float64(positions[t]) * inv_freq[i]))``."""
+    t, half = cos.shape
+    if positions.shape != (t,) or inv_freq.shape != (half,) or sin.shape != cos.shape:
+        raise KernelError("rope_tables: shape mismatch")
+    _check(_fn("ts_rope_tables")(_dev(positions, "positions", torch.int32), _dev(inv_freq, "inv_freq", torch.float64),
+                                 _dev(cos, "cos", torch.float32), _dev(sin, "sin", torch.float32), t, half,
+                                 _stream()), "rope_tables")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t, j] = dt(silu(gate_up[t, j])) * gate_up[t, I + j]``."""
+    t, inter = out.shape
+    if gate_up.shape != (t, 2 * inter) or gate_up.dtype != out.dtype:
+        raise KernelError("silu_mul: shape or dtype mismatch")
+    _check(_fn("ts_silu_mul")(_dev(gate_up, "gate_up"), _dev(out, "out"), t, inter, _code(out.dtype), _stream()),
+           "silu_mul")
+
+
+def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: torch.Tensor | None,
+                       k_weight: torch.Tensor | None, eps: float, cos: torch.Tensor | None,
+                       sin: torch.Tensor | None, rotary_dim: int, interleaved: bool, slots: torch.Tensor,
+                       k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int, num_heads: int,
+                       num_kv_heads: int, head_dim: int, write_kv: bool) -> None:
+    """Per (token, head): optional RMSNorm over ``head_dim``, optional rotation of the first
+    ``rotary_dim`` elements; q heads go to ``q_out``, k and v heads to the cache at the token's
+    slot (only when ``write_kv``; then ``qkv`` rows hold q, k and v, else q alone)."""
+    t = q_out.shape[0]
+    dt = q_out.dtype
+    width = (num_heads + 2 * num_kv_heads) * head_dim if write_kv else num_heads * head_dim
+    if qkv.shape != (t, width) or qkv.dtype != dt or tuple(q_out.shape) != (t, num_heads, head_dim):
+        raise KernelError("qk_norm_rope_write: qkv/q_out shape or dtype mismatch")
+    if k_cache.dtype != dt or v_cache.dtype != dt or k_cache.shape != v_cache.shape:
+        raise KernelError("qk_norm_rope_write: cache dtype/shape mismatch")
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, page_size, head_dim):
+        raise KernelError("qk_norm_rope_write: cache layout must be [pages, kv_heads, page_size, head_dim]")
+    if rotary_dim and (cos is None or sin is None or tuple(cos.shape) != (t, rotary_dim // 2)):
+        raise KernelError("qk_norm_rope_write: rotary tables missing or of the wrong shape")
+    if slots.shape != (t,):
+        raise KernelError("qk_norm_rope_write: one slot per token")
+    _check(_fn("ts_qk_norm_rope_write")(
+        _dev(qkv, "qkv"), _dev(q_out, "q_out"), _opt(q_weight, "q_weight", dt), _opt(k_weight, "k_weight", dt),
+        float(eps), _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), int(rotary_dim),
+        int(bool(interleaved)), _dev(slots, "slots", torch.int32), _dev(k_cache, "k_cache"),
+        _dev(v_cache, "v_cache"), page_size, t, num_heads, num_kv_heads, head_dim, int(bool(write_kv)),
+        _code(dt), _stream()), "qk_norm_rope_write")
+
+
+# -------------------------------------------------------------------- attention
+TARGET_DECODE_CTAS = 148 * 4
+MIN_KEYS_PER_SPLIT = 64
+MAX_SPLITS = 32
+
+
+def decode_splits(num_decode: int, num_kv_heads: int, group: int, max_context_len: int) -> int:
+    """How many ranges the keys of each decoding request are cut into. Depends only on the
+    shape of the step (after upstream src/tinyserve/triton_attention.py:499-510)."""
+    passes = (group + 7) // 8 if group > 8 else 1
+    ctas = max(1, num_decode * num_kv_heads * passes)
+    want = -(-TARGET_DECODE_CTAS // ctas)
+    most = max(1, max_context_len // MIN_KEYS_PER_SPLIT)
+    return max(1, min(want, most, MAX_SPLITS))
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
+                    block_tables: torch.Tensor, ctx: Any, scale: float, window: int, out: torch.Tensor) -> None:
+    """Causal attention of this step's queries over each request's cached keys and values.
+
+    ``q`` ``[T, Hq, D]`` dt; caches ``[pages, Hkv, page_size, D]`` dt; ``block_tables``
+    ``[B, W]`` int32; ``ctx`` supplies ``cu_query_lens``, ``context_lens_dev``, the lists of
+    decoding and prefilling requests and the step's maxima. ``window`` 0 means all earlier
+    positions. ``out`` ``[T, Hq * D]`` dt."""
+    t, hq, d = q.shape
+    hkv = k_cache.shape[1]
+    dt = q.dtype
+    if k_cache.dtype != dt or v_cache.dtype != dt or out.dtype != dt:
+        raise KernelError("paged_attention: dtype mismatch")
+    if tuple(k_cache.shape[1:]) != (hkv, page_size, d) or k_cache.shape != v_cache.shape:
+        raise KernelError("paged_attention: cache layout must be [pages, kv_heads, page_size, head_dim]")
+    if out.numel() != t * hq * d or hq % hkv:
+        raise KernelError("paged_attention: out shape or head grouping")
+    if d % 16 or d > 256:
+        raise KernelError(f"paged_attention: head_dim={d} must be a multiple of 16 up to 256")
+    if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
+        raise KernelError("paged_attention: block_tables must be [requests, width]")
+    splits, part_acc, part_ml = 1, None, None
+    if ctx.num_decode:
+        splits = decode_splits(ctx.num_decode, hkv, hq // hkv, ctx.max_context_len)
+        if splits > 1:
+            part_acc = ctx.arena.take((ctx.num_decode, hq, splits, d), torch.float32)
+            part_ml = ctx.arena.take((ctx.num_decode, hq, splits, 2), torch.float32)
+    _check(_fn("ts_paged_attention_simt")(
+        _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+        _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
+        _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+        _dev(ctx.context_lens_dev, "context_lens", torch.int32),
+        _dev(ctx.decode_seqs, "decode_seqs", torch.int32), ctx.num_decode,
+        _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), ctx.num_prefill, ctx.max_query_len,
+        hq, hkv, d, page_size, float(scale), int(window), splits,
+        _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _code(dt), _stream()), "paged_attention")
+
+
+# ------------------------------------------------------------------------- gemm
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[M, N] = x[M, K] @ w[N, K]^T`` with 32-bit accumulation. ``x`` and ``w`` share a
+    dtype; ``out`` has it too, or is float32 (the logits). float32 inputs run on CUDA cores in
+    true 32-bit; bfloat16 inputs use the tensor cores."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n) or x.dtype != w.dtype:
+        raise KernelError(f"gemm: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)}")
+    if out.dtype not in (x.dtype, torch.float32):
+        raise KernelError(f"gemm: out dtype {out.dtype} for inputs {x.dtype}")
+    if m == 0:
+        return
+    if x.dtype == torch.float32:
+        _check(_fn("ts_gemm_simt")(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), m, n, k, _F32, _F32, _stream()),
+               "gemm")
+        return
+    _dev(x, "x"), _dev(w, "w"), _dev(out, "out")
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)                       # vendor library matrix product
+    else:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """The CUDA-core product for any dtype pairing ``gemm`` allows (slow; any size)."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n) or x.dtype != w.dtype:
+        raise KernelError("gemm_simt: shape or dtype mismatch")
+    _check(_fn("ts_gemm_simt")(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), m, n, k, _code(x.dtype),
+                               _code(out.dtype), _stream()), "gemm_simt")
+
+
+# --------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor | None = None,
+           top_p: torch.Tensor | None = None, seeds: torch.Tensor | None = None,
+           draws: torch.Tensor | None = None) -> None:
+    """One token per row of ``logits`` ``[R, V]`` float32 into ``out`` ``[R]`` int32. With no
+    ``temperature`` every row is greedy; else rows with temperature 0 are greedy and the others
+    are drawn (``seeds``/``draws`` int64 ``[R]``: the request's seed and how many tokens it
+    has drawn so far; ``top_p`` float32 ``[R]`` optional)."""
+    r, v = logits.shape
+    if out.shape != (r,):
+        raise KernelError("sample: one output per row")
+    _check(_fn("ts_sample")(_dev(logits, "logits", torch.float32), r, v, _opt(temperature, "temperature", torch.float32),
+                            _opt(top_p, "top_p", torch.float32), _opt(seeds, "seeds", torch.int64),
+                            _opt(draws, "draws", torch.int64), _dev(out, "out", torch.int32), _stream()), "sample")

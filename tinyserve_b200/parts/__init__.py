@@ -1,0 +1,18 @@
+"""The parts layers are assembled from. Importing the package registers the built-in ones."""
+
+from . import attention, block, embedding, mlp, norm, rope  # noqa: F401
+from .base import (
+    BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
+    Block, FeedForward, KVCacheEntry, KVGroupContext, KVNeed, Mixer, Norm, Part,
+    PositionEncoding, ResidualStream, StateCacheEntry, StateNeed, StepContext, TensorSpec,
+    register_block, register_feed_forward, register_mixer, register_norm,
+    register_position_encoding,
+)
+
+__all__ = [
+    "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS",
+    "Block", "FeedForward", "KVCacheEntry", "KVGroupContext", "KVNeed", "Mixer", "Norm", "Part",
+    "PositionEncoding", "ResidualStream", "StateCacheEntry", "StateNeed", "StepContext",
+    "TensorSpec", "register_block", "register_feed_forward", "register_mixer", "register_norm",
+    "register_position_encoding",
+]

@@ -1,0 +1,91 @@
+"""Grouped-query attention over the paged cache, with optional per-head q/k RMSNorm,
+rotary position encoding and an optional sliding window.
+
+Per token (upstream src/tinyserve/model.py:154-173, src/tinyserve/attention.py:89-111):
+``qkv = x Wqkv^T`` (rows q, then k, then v; no bias); q and k are normalised per head over
+``head_dim`` before the rotation; k (rotated) and v go to the cache at the token's slot;
+query head ``h`` reads kv head ``h // (num_heads / num_kv_heads)``; scores are scaled by
+``scale``, masked causally (and to the last ``window`` positions if a window is set),
+soft-maxed in 32-bit and applied to v; the heads are concatenated and projected by ``Wo``.
+The residual add happens in the next norm.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Mapping
+
+import torch
+
+from ..kernels import ops
+from .base import KVCacheEntry, KVNeed, Mixer, StepContext, TensorSpec, register_mixer
+
+
+class GQAAttention(Mixer):
+    def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int,
+                 head_dim: int, scale: float, qk_norm: bool = False, qk_norm_eps: float = 1e-6,
+                 window: int | None = None) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        if window is not None and window <= 0:
+            raise ValueError(f"window must be positive or None, got {window}")
+        self.prefix = prefix
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.head_dim, self.scale = int(head_dim), float(scale)
+        self.qk_norm, self.qk_norm_eps = bool(qk_norm), float(qk_norm_eps)
+        self.window = None if window is None else int(window)
+        self.q_size = self.num_heads * self.head_dim
+        self.kv_size = self.num_kv_heads * self.head_dim
+        self.w_qkv = self.w_q = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    def cache_need(self) -> KVNeed:
+        return KVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        p, h = prefix + self.prefix, self.hidden_size
+        specs = [
+            TensorSpec(p + "qkv_proj.weight", (self.q_size + 2 * self.kv_size, h),
+                       merged_from=(p + "q_proj.weight", p + "k_proj.weight", p + "v_proj.weight"),
+                       merged_rows=(self.q_size, self.kv_size, self.kv_size)),
+            TensorSpec(p + "o_proj.weight", (h, self.q_size)),
+        ]
+        if self.qk_norm:
+            specs += [TensorSpec(p + "q_norm.weight", (self.head_dim,), init="one_plus_normal"),
+                      TensorSpec(p + "k_norm.weight", (self.head_dim,), init="one_plus_normal")]
+        return specs
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        p = prefix + self.prefix
+        self.w_qkv = tensors[p + "qkv_proj.weight"]
+        self.w_q = self.w_qkv[: self.q_size]          # a view: rows of q only
+        self.w_o = tensors[p + "o_proj.weight"]
+        if self.qk_norm:
+            self.q_norm_w = tensors[p + "q_norm.weight"]
+            self.k_norm_w = tensors[p + "k_norm.weight"]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheEntry, writes_cache: bool,
+                position: Any) -> torch.Tensor:
+        t = x.shape[0]
+        arena = ctx.arena
+        group = ctx.kv[cache.group]
+        width = self.q_size + 2 * self.kv_size if writes_cache else self.q_size
+        qkv = arena.take((t, width), ctx.dtype)
+        ops.gemm(x, self.w_qkv if writes_cache else self.w_q, qkv)
+        q = arena.take((t, self.num_heads, self.head_dim), ctx.dtype)
+        ops.qk_norm_rope_write(
+            qkv, q, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+            None if position is None else position.cos,
+            None if position is None else position.sin,
+            0 if position is None else position.rotary_dim,
+            False if position is None else position.interleaved,
+            group.slots, cache.k, cache.v, cache.page_size,
+            self.num_heads, self.num_kv_heads, self.head_dim, writes_cache,
+        )
+        attn = arena.take((t, self.q_size), ctx.dtype)
+        ops.paged_attention(q, cache.k, cache.v, cache.page_size, group.block_tables, ctx,
+                            self.scale, self.window or 0, attn)
+        out = arena.take((t, self.hidden_size), ctx.dtype)
+        ops.gemm(attn, self.w_o, out)
+        return out
+
+
+register_mixer("gqa_attention", GQAAttention)
