@@ -1,0 +1,284 @@
+"""Each CUDA kernel alone against its plain PyTorch reference (``kernel_refs``), in float32
+and bfloat16, at sizes other than the engine's tiny models'. Pages the requests do not own are
+filled with NaN, so a single read too many shows (after upstream
+tests/test_triton_attention.py:13-14)."""
+
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import kernel_refs as ref
+from tinyserve_b200.engine.arena import Arena
+from tinyserve_b200.kernels import ops
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype: torch.dtype) -> dict[str, float]:
+    return {"atol": 1e-5, "rtol": 1e-5} if dtype == torch.float32 else {"atol": 2e-2, "rtol": 2e-2}
+
+
+def rnd(*shape: int, dtype=torch.float32, seed: int = 0, scale: float = 1.0) -> torch.Tensor:
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(72, 301), (1024, 5000)])
+def test_embed(dtype, hidden, vocab) -> None:
+    table = rnd(vocab, hidden, dtype=dtype)
+    tokens = torch.randint(0, vocab, (37,), device="cuda", dtype=torch.int32)
+    out, want = torch.empty(37, hidden, device="cuda"), torch.empty(37, hidden, device="cuda")
+    ops.embed(tokens, table, out)
+    ref.embed(tokens, table, want)
+    assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 80, 1000, 4096])
+@pytest.mark.parametrize("with_delta", [True, False])
+def test_add_rms_norm(dtype, hidden, with_delta) -> None:
+    t = 19
+    resid = rnd(t, hidden, seed=1, scale=3.0)
+    delta = rnd(t, hidden, dtype=dtype, seed=2) if with_delta else None
+    w = (1 + rnd(hidden, seed=3, scale=0.1)).to(dtype)
+    r1, r2 = resid.clone(), resid.clone()
+    out, want = torch.empty(t, hidden, device="cuda", dtype=dtype), torch.empty(t, hidden, device="cuda", dtype=dtype)
+    ops.add_rms_norm(r1, delta, w, 1e-5, out)
+    ref.add_rms_norm(r2, delta, w, 1e-5, want)
+    torch.testing.assert_close(r1, r2, atol=0, rtol=0)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    # selected rows: the stream must stay as it is
+    rows = torch.tensor([3, 0, 18, 3], device="cuda", dtype=torch.int32)
+    r3 = resid.clone()
+    out2, want2 = torch.empty(4, hidden, device="cuda", dtype=dtype), torch.empty(4, hidden, device="cuda", dtype=dtype)
+    ops.add_rms_norm(r3, delta, w, 1e-5, out2, rows=rows)
+    ref.add_rms_norm(resid.clone(), delta, w, 1e-5, want2, rows=rows)
+    assert torch.equal(r3, resid)
+    torch.testing.assert_close(out2.float(), want2.float(), **tol(dtype))
+
+
+def test_rope_tables_far_positions() -> None:
+    pos = torch.tensor([0, 1, 2, 4095, 40959, 1_000_003], device="cuda", dtype=torch.int32)
+    two_i = torch.arange(0, 128, 2, dtype=torch.float64)
+    inv = (1e6 ** (-two_i / 128)).cuda()
+    cos, sin = torch.empty(6, 64, device="cuda"), torch.empty(6, 64, device="cuda")
+    wc, ws = torch.empty_like(cos), torch.empty_like(sin)
+    ops.rope_tables(pos, inv, cos, sin)
+    ref.rope_tables(pos, inv, wc, ws)
+    torch.testing.assert_close(cos, wc, atol=1e-7, rtol=0)
+    torch.testing.assert_close(sin, ws, atol=1e-7, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [100, 176, 3072])
+def test_silu_mul(dtype, inter) -> None:
+    gu = rnd(23, 2 * inter, dtype=dtype, scale=3.0)
+    out, want = torch.empty(23, inter, device="cuda", dtype=dtype), torch.empty(23, inter, device="cuda", dtype=dtype)
+    ops.silu_mul(gu, out)
+    ref.silu_mul(gu, want)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,rot,inter,norm,page", [
+    (4, 2, 16, 16, False, True, 16), (4, 1, 32, 32, False, True, 8), (3, 3, 48, 48, False, True, 32),
+    (16, 8, 128, 128, False, True, 16), (6, 2, 64, 32, True, False, 4), (2, 2, 256, 0, False, True, 16),
+])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_qk_norm_rope_write(dtype, hq, hkv, d, rot, inter, norm, page, write_kv) -> None:
+    t, pages = 29, 11
+    width = (hq + 2 * hkv) * d if write_kv else hq * d
+    qkv = rnd(t, width, dtype=dtype, seed=4, scale=2.0)
+    qw = (1 + rnd(d, seed=5, scale=0.2)).to(dtype) if norm else None
+    kw = (1 + rnd(d, seed=6, scale=0.2)).to(dtype) if norm else None
+    pos = torch.randint(0, 5000, (t,), device="cuda", dtype=torch.int32)
+    cos = sin = None
+    if rot:
+        inv = (1e4 ** (-torch.arange(0, rot, 2, dtype=torch.float64) / rot)).cuda()
+        cos, sin = torch.empty(t, rot // 2, device="cuda"), torch.empty(t, rot // 2, device="cuda")
+        ref.rope_tables(pos, inv, cos, sin)
+    slots = torch.randperm(pages * page, device="cuda")[:t].to(torch.int32)
+    caches = [torch.full((pages, hkv, page, d), float("nan"), device="cuda", dtype=dtype) for _ in range(4)]
+    q1, q2 = (torch.empty(t, hq, d, device="cuda", dtype=dtype) for _ in range(2))
+    args = (qw, kw, 1e-6, cos, sin, rot, inter, slots)
+    ops.qk_norm_rope_write(qkv, q1, *args, caches[0], caches[1], page, hq, hkv, d, write_kv)
+    ref.qk_norm_rope_write(qkv, q2, *args, caches[2], caches[3], page, hq, hkv, d, write_kv)
+    torch.testing.assert_close(q1.float(), q2.float(), **tol(dtype))
+    for a, b in ((caches[0], caches[2]), (caches[1], caches[3])):
+        assert torch.equal(a.isnan(), b.isnan()), "wrote outside the tokens' slots (or missed one)"
+        torch.testing.assert_close(a.float().nan_to_num(0), b.float().nan_to_num(0), **tol(dtype))
+
+
+def _attention_case(dtype, hq, hkv, d, page, lens, window, seed=0, scale=None, spike=None):
+    """lens: list of (context_len, new_tokens). Builds NaN-poisoned caches with the requests'
+    pages scattered, and runs kernel and reference. ``spike`` = (request, key position) makes
+    one far key dominate: q and that k are aligned and scaled up."""
+    b = len(lens)
+    need = [-(-c // page) for c, _ in lens]
+    pages = sum(need) + 5
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max(need) + 2
+    tables = torch.zeros(b, width, dtype=torch.int32)
+    k_cache = torch.full((pages, hkv, page, d), float("nan"), device="cuda", dtype=dtype)
+    v_cache = torch.full((pages, hkv, page, d), float("nan"), device="cuda", dtype=dtype)
+    at = 0
+    for i, (c, _) in enumerate(lens):
+        mine = perm[at: at + need[i]]
+        at += need[i]
+        tables[i, : need[i]] = torch.tensor(mine)
+        k = rnd(c, hkv, d, dtype=dtype, seed=seed * 100 + i)
+        v = rnd(c, hkv, d, dtype=dtype, seed=seed * 100 + 50 + i)
+        if spike is not None and spike[0] == i:
+            k[spike[1]] = k[spike[1]] * 6
+        for p in range(c):
+            k_cache[mine[p // page], :, p % page] = k[p]
+            v_cache[mine[p // page], :, p % page] = v[p]
+    qlens = [n for _, n in lens]
+    t = sum(qlens)
+    q = rnd(t, hq, d, dtype=dtype, seed=seed + 7)
+    cu = [0]
+    for n in qlens:
+        cu.append(cu[-1] + n)
+    if spike is not None:
+        i, pos = spike
+        c = lens[i][0]
+        page_id = int(tables[i, pos // page])
+        kk = k_cache[page_id, :, pos % page].float()          # [hkv, d]
+        q[cu[i + 1] - 1] = (kk.repeat_interleave(hq // hkv, dim=0) * 0.5).to(dtype)
+    dec = [i for i, n in enumerate(qlens) if n == 1]
+    pre = [i for i, n in enumerate(qlens) if n > 1]
+    pad = lambda xs: torch.tensor(xs + [0] * (b - len(xs)), dtype=torch.int32, device="cuda")
+    ctx = SimpleNamespace(
+        num_seqs=b, cu_query_lens=torch.tensor(cu, dtype=torch.int32, device="cuda"),
+        context_lens_dev=torch.tensor([c for c, _ in lens], dtype=torch.int32, device="cuda"),
+        decode_seqs=pad(dec), prefill_seqs=pad(pre), num_decode=len(dec), num_prefill=len(pre),
+        max_query_len=max(qlens), max_context_len=max(c for c, _ in lens), arena=Arena("cuda"))
+    sc = scale if scale is not None else d ** -0.5
+    out = torch.full((t, hq * d), float("nan"), device="cuda", dtype=dtype)
+    want = torch.empty(t, hq * d, device="cuda", dtype=dtype)
+    tables = tables.cuda()
+    ops.paged_attention(q, k_cache, v_cache, page, tables, ctx, sc, window, out)
+    ref.paged_attention(q, k_cache, v_cache, page, tables, ctx, sc, window, want)
+    return out, want
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [
+    (4, 2, 16, 16), (4, 1, 32, 8), (3, 3, 48, 32), (16, 8, 128, 16), (8, 1, 64, 16), (12, 2, 80, 4),
+    (2, 1, 256, 16), (5, 5, 128, 64),
+])
+def test_attention_mixed_batch(dtype, hq, hkv, d, page) -> None:
+    lens = [(1, 1), (16, 1), (17, 1), (33, 33), (64, 2), (300, 1), (129, 40), (96, 96), (500, 3), (1025, 1)]
+    out, want = _attention_case(dtype, hq, hkv, d, page, lens, 0)
+    assert not out.isnan().any()
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 16, 100])
+def test_attention_window(dtype, window) -> None:
+    lens = [(1, 1), (16, 1), (40, 40), (300, 1), (129, 40), (257, 3)]
+    out, want = _attention_case(dtype, 4, 2, 32, 8, lens, window)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_decode_only_many_splits(dtype) -> None:
+    lens = [(2048, 1), (1, 1), (777, 1)]
+    out, want = _attention_case(dtype, 16, 8, 128, 16, lens, 0)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("new", [1, 5])
+@pytest.mark.parametrize("pos", [0, 15, 16, 511, 700])
+def test_attention_far_key_dominates(dtype, new, pos) -> None:
+    """One key among a thousand carries almost all the weight: dropping it (a split that ends
+    early, a page missed) changes the result completely."""
+    lens = [(1000, new), (64, 1)]
+    out, want = _attention_case(dtype, 4, 2, 64, 16, lens, 0, spike=(0, pos), scale=1.0)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                                (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("m,n,k", [(1, 301, 72), (7, 80, 176), (64, 64, 16), (65, 130, 33), (200, 1000, 1024)])
+def test_gemm_simt(in_dtype, out_dtype, m, n, k) -> None:
+    x, w = rnd(m, k, dtype=in_dtype, seed=1), rnd(n, k, dtype=in_dtype, seed=2)
+    out, want = (torch.empty(m, n, device="cuda", dtype=out_dtype) for _ in range(2))
+    ops.gemm_simt(x, w, out)
+    ref.gemm(x, w, want)
+    t = {"atol": 1e-4, "rtol": 1e-5} if out_dtype == torch.float32 else {"atol": 2e-1, "rtol": 2e-2}
+    torch.testing.assert_close(out.float(), want.float(), **t)
+
+
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                             (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("m,n,k", [(1, 301, 72), (8, 4096, 1024), (300, 1024, 3072), (5, 151936, 1024)])
+def test_gemm(dtype, out_dtype, m, n, k) -> None:
+    x, w = rnd(m, k, dtype=dtype, seed=1), rnd(n, k, dtype=dtype, seed=2, scale=0.05)
+    out, want = (torch.empty(m, n, device="cuda", dtype=out_dtype) for _ in range(2))
+    ops.gemm(x, w, out)
+    ref.gemm(x, w, want)
+    t = {"atol": 1e-4, "rtol": 1e-4} if dtype == torch.float32 else {"atol": 5e-2, "rtol": 2e-2}
+    torch.testing.assert_close(out.float(), want.float(), **t)
+
+
+def test_gemm_fp32_row_does_not_depend_on_batch() -> None:
+    x, w = rnd(70, 200, seed=1), rnd(333, 200, seed=2)
+    full = torch.empty(70, 333, device="cuda")
+    one = torch.empty(1, 333, device="cuda")
+    ops.gemm(x, w, full)
+    ops.gemm(x[41:42].contiguous(), w, one)
+    assert torch.equal(full[41:42], one)
+
+
+@pytest.mark.parametrize("vocab", [301, 4096, 151936])
+def test_sample_greedy(vocab) -> None:
+    logits = rnd(9, vocab, seed=3)
+    logits[2, 17] = logits[2, 200] = 50.0      # a tie: the first index wins
+    out = torch.empty(9, device="cuda", dtype=torch.int32)
+    ops.sample(logits, out)
+    assert out.tolist() == logits.argmax(-1).tolist()
+    assert out[2].item() == 17
+
+
+@pytest.mark.parametrize("vocab", [301, 5000])
+def test_sample_temperature_and_top_p_match_reference(vocab) -> None:
+    r = 12
+    logits = rnd(r, vocab, seed=4, scale=2.0)
+    temps = torch.tensor([0.0, 0.8, 1.0, 1.5] * 3, device="cuda")
+    top_p = torch.tensor([1.0] * 4 + [0.9] * 4 + [0.3] * 4, device="cuda")
+    seeds = torch.arange(r, device="cuda", dtype=torch.int64) * 7919 + (1 << 40)
+    for draw in (0, 1, 5):
+        draws = torch.full((r,), draw, device="cuda", dtype=torch.int64)
+        out, want = (torch.empty(r, device="cuda", dtype=torch.int32) for _ in range(2))
+        ops.sample(logits, out, temps, top_p, seeds, draws)
+        ref.sample(logits, want, temps, top_p, seeds, draws)
+        assert out.tolist() == want.tolist()
+
+
+def test_sample_frequencies_follow_softmax() -> None:
+    vocab, n = 8, 20000
+    row = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5, -3.0, 1.5, 0.2], device="cuda")
+    logits = row.repeat(n, 1).contiguous()
+    temps = torch.full((n,), 0.7, device="cuda")
+    seeds = torch.arange(n, device="cuda", dtype=torch.int64)
+    draws = torch.zeros(n, device="cuda", dtype=torch.int64)
+    out = torch.empty(n, device="cuda", dtype=torch.int32)
+    ops.sample(logits, out, temps, None, seeds, draws)
+    freq = torch.bincount(out.long(), minlength=vocab).float() / n
+    torch.testing.assert_close(freq, torch.softmax(row / 0.7, -1), atol=0.012, rtol=0)
+    # nucleus: only the tokens whose more likely tokens hold < 0.6 may appear
+    top_p = torch.full((n,), 0.6, device="cuda")
+    ops.sample(logits, out, temps, top_p, seeds, draws)
+    p = torch.softmax(row / 0.7, -1)
+    order = p.argsort(descending=True)
+    above = p[order].cumsum(0) - p[order]
+    allowed = set(order[above < 0.6].tolist())
+    assert set(out.unique().tolist()) == allowed
