@@ -1,0 +1,276 @@
+"""Headline benchmark: decode tokens/s at batch 8 (and 1, 64) and prefill tokens/s at 2,048
+tokens for the Qwen3-0.6B layer sizes with random weights in bfloat16, on ONE B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line. ``value`` is decoded tokens per second timed on the device with CUDA
+events around K decode steps (step function + sampling kernel, no host read-back between
+steps); ``e2e`` is the same through the Python entry point (``Engine.step``): host token lists
+in, pinned-memory copy of each step's inputs, sampled tokens read back to the host every step.
+``prefill`` times one 2,048-token prompt; ``roofline`` relates the decode step to the bytes it
+must read (every weight once + the cache of the live requests) and the measured HBM bandwidth.
+This engine serves one GPU: for ``--gpus`` above 1 it says so and exits with 2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# BASELINE configs[2]: the Qwen3-0.6B layer sizes.
+QWEN3_0_6B = {
+    "architectures": ["Qwen3ForCausalLM"], "vocab_size": 151936, "hidden_size": 1024,
+    "intermediate_size": 3072, "num_hidden_layers": 28, "num_attention_heads": 16,
+    "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+    "max_position_embeddings": 4096, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            d = json.loads(path.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"])}, "measured"
+        except (ValueError, KeyError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.rows: list[list[str]] = []
+        self._proc: subprocess.Popen | None = None
+        self._thread: threading.Thread | None = None
+
+    def start(self) -> None:
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                           "--format=csv,noheader,nounits", "-lms", "100"],
+                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread.start()
+
+    def _read(self) -> None:
+        assert self._proc is not None and self._proc.stdout is not None
+        for line in self._proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+        rows = [r for r in self.rows if len(r) == 6 and r[0].isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower() == "active" for r in rows)]
+        return {"sm_mhz": int(statistics.median(int(r[0]) for r in rows)), "sm_max_mhz": int(rows[0][1]),
+                "reasons": reasons, "samples": len(rows)}
+
+
+def reference_arm() -> int:
+    """The upstream engine cannot be installed offline here: its build backend (hatchling) is
+    neither in the image nor in the offline wheelhouse."""
+    ref = ROOT / "baseline" / "_ref" / "tinyserve"
+    why = ("the reference's build backend hatchling is not installed and not in the offline wheelhouse, "
+           "so pip cannot build it (baseline/_ref is empty)")
+    if ref.is_dir():
+        why = "baseline/_ref holds the reference, but no reference arm was wired for it in this build"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU only; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return reference_arm()
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    from tinyserve_b200 import LLM
+    from tinyserve_b200.cache import CacheManager
+    from tinyserve_b200.config import config_from_dict
+    from tinyserve_b200.engine import Engine
+    from tinyserve_b200.engine.step import StepEntry
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.model import DecoderModel
+
+    cfg_dict = dict(QWEN3_0_6B)
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(cfg_dict)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    model = DecoderModel.from_config(cfg, seed=0, dtype=torch.bfloat16, device=dev)
+    pk, pk_src = peaks()
+    page = 16
+    vocab = cfg.vocab_size
+    g = torch.Generator().manual_seed(0)
+
+    def prompts(n: int, length: int) -> list[list[int]]:
+        return torch.randint(0, min(vocab, 150_000), (n, length), generator=g).tolist()
+
+    def new_engine(batch: int, tokens_per_seq: int) -> Engine:
+        pages = batch * (-(-tokens_per_seq // page) + 1)
+        cache = CacheManager(model.cache_needs(), page_size=page, num_pages=pages, max_requests=batch,
+                             dtype=torch.bfloat16, device=dev)
+        return Engine(model, cache, max_num_seqs=batch, max_batch_tokens=max(2048, batch), chunked_prefill=True)
+
+    def decode_bytes(batch: int, ctx: float) -> float:
+        kv = CacheManager.bytes_per_token(model.cache_needs(), 2)
+        return model.weight_bytes() + batch * ctx * kv
+
+    def prefilled(batch: int, steps: int) -> Engine:
+        # While later prompts are still being prefilled, earlier requests already decode.
+        margin = -(-batch * args.prompt_len // 2048) + 8
+        e = new_engine(batch, args.prompt_len + steps + margin)
+        for p in prompts(batch, args.prompt_len):
+            e.add_request(p, max_new_tokens=steps + margin)
+        while any(r.num_pending() > 1 or r.cache is None for r in e.requests.values()):
+            e.step()
+        return e
+
+    def device_decode(batch: int, warmup: int, steps: int) -> tuple[float, float, int]:
+        """K decode steps timed on the device: step function + sampling kernel, tokens stay on
+        the device. Returns (ms per step, mean context length, kernels launched)."""
+        e = prefilled(batch, warmup + steps)
+        reqs = list(e.requests.values())
+        out = torch.empty(batch, dtype=torch.int32, device=dev)
+        ctx_sum = 0
+
+        def one() -> None:
+            nonlocal ctx_sum
+            entries = []
+            for r in reqs:
+                e.cache.append(r.cache, 1)
+                entries.append(StepEntry(r.cache, [r.output[-1]]))
+                ctx_sum += r.cache.num_tokens
+            ops.sample(e.runner.step(entries), out)
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        ctx_sum = 0
+        before = ops.launch_count
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / steps, ctx_sum / (steps * batch), ops.launch_count - before
+
+    def e2e_decode(batch: int, warmup: int, steps: int) -> tuple[float, int, int]:
+        e = prefilled(batch, warmup + steps)
+        for _ in range(warmup):
+            e.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            e.step()
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3 / steps
+        # per step: the packed int32 inputs (token, position, slot, lengths, block table) and the tokens back
+        width = -(-(args.prompt_len + warmup + steps) // page)
+        h2d = 4 * (batch * (8 + width) + 16)
+        return ms, h2d, 4 * batch
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms, ctx, launches = device_decode(args.batch, args.warmup, args.steps)
+    clocks = sampler.stop()
+    value = args.batch * 1e3 / ms
+    e2e_ms, h2d, d2h = e2e_decode(args.batch, args.warmup, args.steps)
+    achieved = decode_bytes(args.batch, ctx) / (ms * 1e-3) / 1e9
+
+    result = {
+        "metric": "decode tok/s at batch 8 (Qwen3-0.6B sizes, bf16, 1,024-token prompts)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids, random-init weights", "impl": "ours",
+        "config": {
+            "model": "Qwen3-0.6B sizes", "layers": cfg.num_layers, "layers_of_configuration": full_layers,
+            "hidden": cfg.hidden_size, "q_heads": cfg.num_heads, "kv_heads": cfg.num_kv_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+            "tied_embeddings": cfg.tie_word_embeddings, "global_batch": args.batch, "seq_len": args.prompt_len,
+            "context_limit": cfg.max_position_embeddings, "mean_context": round(ctx, 1), "page_size": page,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 1.19 GB read every step)",
+            "peaks": pk_src,
+        },
+        "e2e": {"value": round(args.batch * 1e3 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk_src},
+    }
+    if not args.skip_points:
+        points = {}
+        for b in (1, 64):
+            pms, _, _ = device_decode(b, 3, max(16, args.steps // 4))
+            points[f"decode_b{b}"] = round(b * 1e3 / pms, 1)
+        result["points"] = points
+        # prefill: one 2,048-token prompt in one step
+        t_pre = 2048
+        e = new_engine(1, t_pre + 8)
+        toks = prompts(1, t_pre)[0]
+        times = []
+        for it in range(3 + 5):
+            req = e.cache.new_request()
+            e.cache.append(req, t_pre)
+            torch.cuda.synchronize()
+            s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_.record()
+            e.runner.step([StepEntry(req, toks)])
+            e_.record()
+            torch.cuda.synchronize()
+            e.cache.free(req)
+            if it >= 3:
+                times.append(s_.elapsed_time(e_))
+        pre_ms = statistics.median(times)
+        matmul_params = (model.weight_bytes() // 2) - cfg.vocab_size * cfg.hidden_size   # all but the table
+        flops = 2.0 * t_pre * matmul_params + 2.0 * cfg.vocab_size * cfg.hidden_size     # head on one row
+        flops += cfg.num_layers * 4.0 * cfg.num_heads * cfg.head_dim * (t_pre * (t_pre + 1) / 2)
+        result["prefill"] = {"value": round(t_pre * 1e3 / pre_ms, 1), "tokens": t_pre, "ms": round(pre_ms, 3),
+                             "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk_src}
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

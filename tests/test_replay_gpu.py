@@ -23,10 +23,24 @@ ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"A": [5, 17, 33, 70, 130], "B": [1, 9, 24, 40, 63, 97], "C": [3, 50, 31, 64]}
 
 
-def tolerance(dtype: torch.dtype) -> dict[str, float]:
-    # float32: sums in another order than the CPU's. bfloat16: logits of magnitude ~5 built
-    # from bf16 activations; the bound is a few bf16 steps at that magnitude.
-    return {"atol": 3e-5, "rtol": 3e-5} if dtype == torch.float32 else {"atol": 0.12, "rtol": 0.05}
+FP32_TOL = {"atol": 3e-5, "rtol": 3e-5}    # sums in another order than the CPU's
+
+
+def close_enough(rows: torch.Tensor, want32: torch.Tensor, want16: torch.Tensor | None, dtype: torch.dtype) -> None:
+    """float32: equal to the plain implementation up to summation order. bfloat16: the error
+    against the 32-bit oracle is measured against the error that the plain implementation
+    itself makes when it runs in bfloat16 with upstream's rounding points; the engine may not
+    be worse than that by more than a quarter in the root mean square, nor by more than twice
+    at the worst logit."""
+    if dtype == torch.float32:
+        torch.testing.assert_close(rows, want32, **FP32_TOL)
+        return
+    err = (rows - want32).abs()
+    ref = (want16 - want32).abs()
+    rms, ref_rms = float(err.pow(2).mean().sqrt()), float(ref.pow(2).mean().sqrt())
+    assert rms <= 1.25 * ref_rms + 1e-3, f"rms error {rms:.4f} against {ref_rms:.4f} of plain bfloat16"
+    assert float(err.max()) <= 2.0 * float(ref.max()) + 1e-2, \
+        f"worst error {float(err.max()):.4f} against {float(ref.max()):.4f} of plain bfloat16"
 
 
 def run_steps(model, page: int, steps, max_tokens: int):
@@ -53,11 +67,12 @@ def run_steps(model, page: int, steps, max_tokens: int):
 
 
 def check(got, want, reqs, dtype) -> None:
+    want32, want16 = want
     for rid, toks in reqs.items():
         assert sorted(got[rid]) == list(range(len(toks)))
         rows = torch.stack([got[rid][p] for p in range(len(toks))])
         assert not rows.isnan().any(), f"{rid}: NaN in the logits (a read outside the request's pages?)"
-        torch.testing.assert_close(rows, want[rid], **tolerance(dtype))
+        close_enough(rows, want32[rid], want16[rid], dtype)
 
 
 @pytest.fixture(scope="module")
@@ -69,7 +84,9 @@ def tiny(tmp_path_factory):
         pcfg = plain.read_config(folder)
         # The oracle is the plain implementation in 32-bit on the same (bf16-representable) weights.
         pw = plain.read_weights(folder, torch.float32)
-        want = {rid: plain.forward(pcfg, pw, toks) for rid, toks in reqs.items()}
+        pw16 = plain.read_weights(folder, torch.bfloat16)
+        want = ({rid: plain.forward(pcfg, pw, toks) for rid, toks in reqs.items()},
+                {rid: plain.forward(pcfg, pw16, toks) for rid, toks in reqs.items()})
         out[name] = (folder, page, seed, reqs, want)
     return out
 
@@ -126,7 +143,8 @@ def test_long_decoding_and_first_tokens(tiny, models, dtype) -> None:
     folder, page, seed, _, _ = tiny[name]
     toks = random_prompt(300, TINIES[name][0]["vocab_size"], 77)
     pcfg, pw = plain.read_config(folder), plain.read_weights(folder, torch.float32)
-    want = {"d": plain.forward(pcfg, pw, toks)}
+    want = ({"d": plain.forward(pcfg, pw, toks)},
+            {"d": plain.forward(pcfg, plain.read_weights(folder, torch.bfloat16), toks)})
     steps = [([("d", [t], [0])], []) for t in toks]
     steps[-1] = (steps[-1][0], ["d"])
     check(run_steps(models[name, dtype], page, steps, cases.max_live_tokens(steps)), want, {"d": toks}, dtype)

@@ -1,0 +1,73 @@
+"""One request's state as the scheduler moves it between its queues (after upstream
+src/tinyserve/sequence.py:23-74).
+
+A request's tokens are its prompt followed by what it has generated. The cache holds the
+first ``num_cached`` of them; the rest are pending and go into coming steps: the whole prompt
+for a fresh request, one token while decoding, prompt plus output after a preemption (its
+cache was given back, so everything is recomputed).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from enum import Enum
+
+from ..cache.manager import RequestCache
+from ..sampling.params import SamplingParams
+
+
+class Status(Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
+
+
+@dataclass
+class Request:
+    request_id: int
+    prompt: list[int]
+    max_new_tokens: int
+    eos_ids: frozenset[int] = frozenset()
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    output: list[int] = field(default_factory=list)
+    status: Status = Status.WAITING
+    cache: RequestCache | None = None
+    num_scheduled: int = 0        # tokens given to the last scheduled step
+    num_preemptions: int = 0
+
+    def __post_init__(self) -> None:
+        if not self.prompt:
+            raise ValueError("prompt must not be empty")
+        if self.max_new_tokens <= 0:
+            raise ValueError(f"max_new_tokens must be positive, got {self.max_new_tokens}")
+
+    @property
+    def tokens(self) -> list[int]:
+        return self.prompt + self.output
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
+    def num_cached(self) -> int:
+        return 0 if self.cache is None else self.cache.num_tokens
+
+    @property
+    def max_cached_tokens(self) -> int:
+        """The most tokens it can ever hold in the cache: the last generated token is never
+        fed back."""
+        return len(self.prompt) + self.max_new_tokens - 1
+
+    def num_pending(self) -> int:
+        return self.num_tokens - self.num_cached
+
+    def in_prefill(self) -> bool:
+        """After scheduling: tokens are still left for later steps, so this step's logits
+        predict nothing and the request samples nothing."""
+        return self.num_pending() > 0
+
+    def is_done(self) -> bool:
+        if len(self.output) >= self.max_new_tokens:
+            return True
+        return bool(self.output) and self.output[-1] in self.eos_ids

@@ -39,6 +39,9 @@ _SIGNATURES: dict[str, list[Any]] = {
 }
 _fns: dict[str, Any] = {}
 
+# Kernels of this library launched so far (library matrix products are not counted).
+launch_count = 0
+
 
 def _fn(name: str) -> Any:
     f = _fns.get(name)
@@ -51,8 +54,10 @@ def _fn(name: str) -> Any:
     return f
 
 
-def _check(status: int, name: str) -> None:
+def _check(status: int, name: str, kernels: int = 1) -> None:
+    global launch_count
     if status == 0:
+        launch_count += kernels
         return
     if status == -1:
         raise KernelError(f"{name}: bad argument")
@@ -219,7 +224,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _dev(ctx.decode_seqs, "decode_seqs", torch.int32), ctx.num_decode,
         _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), ctx.num_prefill, ctx.max_query_len,
         hq, hkv, d, page_size, float(scale), int(window), splits,
-        _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _code(dt), _stream()), "paged_attention")
+        _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _code(dt), _stream()), "paged_attention",
+        kernels=(1 if ctx.num_prefill else 0) + (1 if ctx.num_decode else 0) + (1 if splits > 1 else 0))
 
 
 # ------------------------------------------------------------------------- gemm

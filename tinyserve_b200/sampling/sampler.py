@@ -1,0 +1,87 @@
+"""Batched next-token selection for one step: one kernel launch for the whole batch, one
+device-to-host copy of the chosen tokens (the step's only synchronisation).
+
+Every request draws from its own noise stream: a Philox key made of its seed (its own, or one
+derived from the engine's seed and the request's id) and a counter made of how many tokens it
+has drawn so far. So what a request generates does not depend on its batch-mates, on how its
+prompt was cut into portions, or on being recomputed after a preemption (upstream keeps a
+``torch.Generator`` per seeded request for the same end, src/tinyserve/engine.py:126-147).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Sequence
+
+import torch
+
+from ..kernels import ops
+from .params import SamplingParams
+
+_MASK = (1 << 64) - 1
+
+
+def derive_seed(engine_seed: int, request_id: int) -> int:
+    """A well-mixed 63-bit seed for a request that brought none (splitmix64 finaliser)."""
+    z = (engine_seed * 0x9E3779B97F4A7C15 + (request_id + 1) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return (z ^ (z >> 31)) & 0x7FFF_FFFF_FFFF_FFFF
+
+
+@dataclass(frozen=True)
+class TokenLogprobs:
+    logprob: float
+    top: list[tuple[int, float]]
+
+
+class Sampler:
+    def __init__(self, device: torch.device | str, max_rows: int = 1024) -> None:
+        self.device = torch.device(device)
+        pin = self.device.type == "cuda"
+        self._cap = max_rows
+        self._f_host = torch.empty(2 * max_rows, dtype=torch.float32, pin_memory=pin)
+        self._i_host = torch.empty(2 * max_rows, dtype=torch.int64, pin_memory=pin)
+        self._f_dev = torch.empty(2 * max_rows, dtype=torch.float32, device=self.device)
+        self._i_dev = torch.empty(2 * max_rows, dtype=torch.int64, device=self.device)
+        self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
+        self._out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=pin)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               draws: Sequence[int]) -> list[int]:
+        """``logits`` ``[R, V]`` float32 on the device; row r belongs to a request with
+        ``params[r]``, noise seed ``seeds[r]`` that has drawn ``draws[r]`` tokens so far."""
+        r = logits.shape[0]
+        if not (len(params) == len(seeds) == len(draws) == r):
+            raise ValueError(f"{r} rows, {len(params)} params, {len(seeds)} seeds, {len(draws)} draws")
+        if r > self._cap:
+            raise ValueError(f"{r} rows exceed the sampler's capacity {self._cap}")
+        out = self._out[:r]
+        if all(p.greedy for p in params):
+            ops.sample(logits, out)
+        else:
+            f, i = self._f_host, self._i_host
+            f[:r] = torch.tensor([p.temperature for p in params], dtype=torch.float32)
+            f[r: 2 * r] = torch.tensor([p.top_p for p in params], dtype=torch.float32)
+            i[:r] = torch.tensor(list(seeds), dtype=torch.int64)
+            i[r: 2 * r] = torch.tensor(list(draws), dtype=torch.int64)
+            self._f_dev[: 2 * r].copy_(f[: 2 * r], non_blocking=True)
+            self._i_dev[: 2 * r].copy_(i[: 2 * r], non_blocking=True)
+            top_p = self._f_dev[r: 2 * r] if any(p.top_p < 1 for p in params) else None
+            ops.sample(logits, out, self._f_dev[:r], top_p, self._i_dev[:r], self._i_dev[r: 2 * r])
+        host = self._out_host[:r]
+        host.copy_(out, non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        return host.tolist()
+
+
+def token_logprobs(logits: torch.Tensor, tokens: Sequence[int], ks: Sequence[int]) -> list[TokenLogprobs]:
+    """log_softmax of the raw logits at each drawn token, and the ``ks[r]`` most likely tokens
+    (upstream src/tinyserve/sampling.py:113-128). A reporting aid, off the hot path."""
+    lp = torch.log_softmax(logits.float(), dim=-1)
+    idx = torch.tensor(list(tokens), device=logits.device, dtype=torch.long)
+    chosen = lp.gather(-1, idx[:, None])[:, 0].tolist()
+    top_v, top_i = lp.topk(max(ks, default=0), dim=-1)
+    vals, ids = top_v.tolist(), top_i.tolist()
+    return [TokenLogprobs(chosen[b], list(zip(ids[b][:k], vals[b][:k]))) for b, k in enumerate(ks)]
