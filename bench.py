@@ -110,6 +110,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -146,10 +147,11 @@ def main() -> int:
         return torch.randint(0, min(vocab, 150_000), (n, length), generator=g).tolist()
 
     def new_engine(batch: int, tokens_per_seq: int) -> Engine:
-        pages = batch * (-(-tokens_per_seq // page) + 1)
+        pages = max(batch * (-(-tokens_per_seq // page) + 1), cfg.max_position_embeddings // page)
         cache = CacheManager(model.cache_needs(), page_size=page, num_pages=pages, max_requests=batch,
                              dtype=torch.bfloat16, device=dev)
-        return Engine(model, cache, max_num_seqs=batch, max_batch_tokens=max(2048, batch), chunked_prefill=True)
+        return Engine(model, cache, max_num_seqs=batch, max_batch_tokens=max(2048, batch), chunked_prefill=True,
+                      decode_graphs=not args.no_graphs, graph_max_context=cfg.max_position_embeddings)
 
     def decode_bytes(batch: int, ctx: float) -> float:
         kv = CacheManager.bytes_per_token(model.cache_needs(), 2)

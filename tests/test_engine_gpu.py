@@ -1,0 +1,117 @@
+"""Generation through the Python entry point on the GPU: greedy tokens equal the plain
+implementation's; decode graphs change nothing but the launch path; sampling is reproducible."""
+
+from __future__ import annotations
+
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from tiny_configs import TINIES, random_prompt, write_tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    out = {}
+    for name, lens in (("A", [5, 17, 33]), ("B", [1, 9, 24, 40, 63])):
+        cfg, page, seed = TINIES[name]
+        folder = write_tiny(tmp_path_factory.mktemp(name), name, torch.bfloat16)
+        prompts = [random_prompt(n, cfg["vocab_size"], 50 + i) for i, n in enumerate(lens)]
+        pc, pw = plain.read_config(folder), plain.read_weights(folder, torch.float32)
+        out[name] = (folder, page, prompts, [plain.greedy(pc, pw, p, 8) for p in prompts])
+    return out
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("chunked", [False, True])
+def test_greedy_float32_equals_plain(tiny, name, graphs, chunked) -> None:
+    from tinyserve_b200 import LLM
+
+    folder, page, prompts, want = tiny[name]
+    llm = LLM.from_folder(folder, dtype="float32", page_size=page, num_pages=64, max_num_seqs=4,
+                          max_batch_tokens=16 if chunked else 128, chunked_prefill=chunked, decode_graphs=graphs)
+    assert llm.generate(prompts, 8) == want
+    assert (llm.engine.runner.num_graph_steps > 0) == graphs
+    assert all(g.allocator.num_used == 0 for g in llm.cache.groups)
+
+
+def test_greedy_bfloat16_close_to_plain_and_tight_cache(tiny) -> None:
+    from tinyserve_b200 import LLM
+
+    folder, page, prompts, want = tiny["B"]
+    llm = LLM.from_folder(folder, dtype="bfloat16", page_size=page, num_pages=10, max_num_seqs=4,
+                          max_batch_tokens=128, decode_graphs=True)
+    got = llm.generate(prompts, 8)
+    same = sum(a == b for g, w in zip(got, want) for a, b in zip(g, w))
+    assert same >= 0.8 * 8 * len(prompts), (got, want)     # bf16 may flip a near-tie; most tokens agree
+
+
+def test_graph_logits_equal_eager_logits(tiny) -> None:
+    """The recorded decode step and the kernel-by-kernel one give the same logits up to the
+    order of the split-K sums."""
+    from tinyserve_b200.cache import CacheManager
+    from tinyserve_b200.engine.step import ModelRunner, StepEntry
+    from tinyserve_b200.model import DecoderModel
+
+    folder, page, prompts, _ = tiny["A"]
+    model = DecoderModel.from_folder(folder, torch.float32, "cuda")
+    outs = []
+    for graphs in (False, True):
+        cache = CacheManager(model.cache_needs(), page_size=page, num_pages=32, max_requests=4,
+                             dtype=torch.float32, device="cuda")
+        runner = ModelRunner(model, cache)
+        if graphs:
+            runner.record_decode_graphs(4, 256)
+        reqs = [cache.new_request() for _ in prompts]
+        for r, p in zip(reqs, prompts):
+            cache.append(r, len(p))
+        runner.step([StepEntry(r, p) for r, p in zip(reqs, prompts)])
+        rows = []
+        for t in range(5):
+            for r in reqs:
+                cache.append(r, 1)
+            rows.append(runner.step([StepEntry(r, [7 + t]) for r in reqs]).clone())
+        assert (runner.num_graph_steps == 5) == graphs
+        outs.append(torch.stack(rows))
+    torch.testing.assert_close(outs[0], outs[1], atol=2e-5, rtol=2e-5)
+
+
+def test_seeded_sampling_is_reproducible_and_batch_independent(tiny) -> None:
+    from tinyserve_b200 import LLM, SamplingParams
+
+    folder, page, prompts, _ = tiny["B"]
+    p = SamplingParams(temperature=0.8, top_p=0.9, seed=7)
+    alone = LLM.from_folder(folder, dtype="float32", page_size=page, num_pages=64, max_num_seqs=4).generate(
+        [prompts[2]], 6, sampling=p)[0]
+    llm = LLM.from_folder(folder, dtype="float32", page_size=page, num_pages=64, max_num_seqs=4,
+                          max_batch_tokens=16, chunked_prefill=True)
+    e = llm.engine
+    others = [e.add_request(q, 6, sampling=SamplingParams(temperature=1.0, seed=i)) for i, q in enumerate(prompts[:2])]
+    mine = e.add_request(prompts[2], 6, sampling=p)
+    while e.has_work():
+        e.step()
+    assert e.requests[mine].output == alone and len(set(alone)) > 1
+    assert all(len(e.requests[i].output) == 6 for i in others)
+
+
+def test_command_line(tiny) -> None:
+    folder, page, prompts, want = tiny["A"]
+    ids = ",".join(str(t) for t in prompts[1])
+    cmd = [sys.executable, str(ROOT / "bin" / "generate"), "--model-dir", str(folder), "--prompt-ids", ids,
+           "--max-new-tokens", "8", "--dtype", "float32", "--block-size", str(page)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert f"new ids:    {want[1]}" in out.stdout
+    out = subprocess.run(cmd + ["--no-cache", "--max-new-tokens", "3"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and f"new ids:    {want[1][:3]}" in out.stdout
+    out = subprocess.run(cmd + ["--temperature", "0.8", "--top-p", "0.9", "--seed", "3", "--num-samples", "2"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "2 samples, 16 tokens" in out.stdout, out.stdout + out.stderr[-1000:]

@@ -66,10 +66,17 @@ class Engine:
     def __init__(self, model: DecoderModel, cache: CacheManager, max_num_seqs: int = 64,
                  max_batch_tokens: int = 2048, clock: Callable[[], float] = time.perf_counter,
                  seed: int = 0, trace_steps: bool = False, chunked_prefill: bool = False,
-                 runner: ModelRunner | None = None) -> None:
+                 runner: ModelRunner | None = None, decode_graphs: bool = False,
+                 graph_max_context: int | None = None) -> None:
+        """``decode_graphs``: record the decode step once per batch-size bucket (CUDA graphs)
+        and replay it whenever every scheduled request brings one token (upstream passes a
+        ``DecodeGraphs`` object for this, src/tinyserve/engine.py:96,188-196)."""
         self.model = model
         self.cache = cache
         self.runner = runner if runner is not None else ModelRunner(model, cache)
+        if decode_graphs and not self.runner.graphs:
+            limit = min(model.spec.max_position_embeddings, cache.num_pages * cache.page_size)
+            self.runner.record_decode_graphs(max_num_seqs, graph_max_context or limit)
         self.scheduler = Scheduler(cache, max_num_seqs, max_batch_tokens, chunked_prefill=chunked_prefill)
         self.sampler = Sampler(model.device, max_rows=max(max_num_seqs, 1))
         self.clock = clock

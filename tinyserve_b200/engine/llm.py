@@ -33,7 +33,8 @@ def _dtype(dtype: str | torch.dtype) -> torch.dtype:
 class LLM:
     def __init__(self, model: DecoderModel, *, page_size: int = 16, num_pages: int | None = None,
                  kv_fraction: float = 0.85, max_num_seqs: int = 64, max_batch_tokens: int = 2048,
-                 chunked_prefill: bool = False, seed: int = 0, trace_steps: bool = False) -> None:
+                 chunked_prefill: bool = False, seed: int = 0, trace_steps: bool = False,
+                 decode_graphs: bool = True, graph_max_context: int | None = None) -> None:
         """``num_pages``: size of every page pool; by default the pools together take
         ``kv_fraction`` of the device memory that is free once the weights are loaded."""
         self.model = model
@@ -52,7 +53,9 @@ class LLM:
         self.cache = CacheManager(needs, page_size=page_size, num_pages=num_pages, max_requests=max_num_seqs,
                                   dtype=model.dtype, device=model.device)
         self.engine = Engine(model, self.cache, max_num_seqs=max_num_seqs, max_batch_tokens=max_batch_tokens,
-                             chunked_prefill=chunked_prefill, seed=seed, trace_steps=trace_steps)
+                             chunked_prefill=chunked_prefill, seed=seed, trace_steps=trace_steps,
+                             decode_graphs=decode_graphs and model.device.type == "cuda",
+                             graph_max_context=graph_max_context)
 
     @classmethod
     def from_folder(cls, model_dir: str | Path, dtype: str | torch.dtype = "bfloat16", device: str = "cuda",

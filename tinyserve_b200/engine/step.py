@@ -19,6 +19,7 @@ import torch
 
 from ..cache.manager import CacheManager, RequestCache
 from ..model import DecoderModel
+from ..kernels import ops
 from ..parts.base import KVGroupContext, StepContext
 from .arena import Arena
 
@@ -36,12 +37,137 @@ class StepEntry:
     tokens: Sequence[int]
 
 
+def default_buckets(max_batch: int) -> list[int]:
+    """Batch sizes a decode graph is recorded for: 1, 2, 4, ... and ``max_batch`` itself
+    (after upstream src/tinyserve/cuda_graphs.py:40-49)."""
+    out, b = [], 1
+    while b < max_batch:
+        out.append(b)
+        b *= 2
+    out.append(max_batch)
+    return out
+
+
+class DecodeGraph:
+    """One recorded decode step for a fixed number of rows.
+
+    Every per-step integer lives at a fixed place of one device buffer that the recorded
+    kernels read; a step copies this step's values there and replays. Rows beyond the live
+    requests are one-token requests on the pad page, whose results nobody reads (after
+    upstream src/tinyserve/batch.py:118-206). The graph has scratch memory of its own, which
+    never moves once recorded."""
+
+    def __init__(self, runner: "ModelRunner", rows: int, max_context: int) -> None:
+        self.rows = rows
+        cache, dev = runner.cache, runner.device
+        groups = cache.groups
+        self.width = -(-max_context // cache.page_size)
+        off = 0
+
+        def section(n: int) -> slice:
+            nonlocal off
+            s = slice(off, off + n)
+            off = _round_up(off + n, 4)
+            return s
+
+        n = rows
+        self.s_tokens, self.s_pos, self.s_cu, self.s_ctx = section(n), section(n), section(n + 1), section(n)
+        self.s_dec, self.s_pre, self.s_rows, self.s_state = section(n), section(n), section(n), section(n)
+        self.s_slots = [section(n) for _ in groups]
+        self.s_tables = [section(n * self.width) for _ in groups]
+        self.size = off
+        self.host = torch.empty(off, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.empty(off, dtype=torch.int32, device=dev)
+        self.copied = torch.cuda.Event()
+        self.arena = Arena(dev)
+        buf = self.host_np
+        buf[:] = 0
+        buf[self.s_cu] = np.arange(n + 1)
+        buf[self.s_dec] = np.arange(n)
+        buf[self.s_rows] = np.arange(n)
+        self._fill_padding(runner, 0)
+        self.dev.copy_(self.host)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+
+    def _fill_padding(self, runner: "ModelRunner", live: int) -> None:
+        buf, n = self.host_np, self.rows
+        buf[self.s_tokens][live:] = 0
+        buf[self.s_pos][live:] = 0
+        buf[self.s_ctx][live:] = 1
+        buf[self.s_state][live:] = 0
+        for g, ss, st in zip(runner.cache.groups, self.s_slots, self.s_tables):
+            buf[ss][live:] = g.pad_page * g.page_size
+            buf[st].reshape(n, self.width)[live:, 0] = g.pad_page
+
+    def context(self, runner: "ModelRunner") -> StepContext:
+        n, dev, w = self.rows, self.dev, self.width
+        cache = runner.cache
+        kv = {g.index: KVGroupContext(g.page_size, dev[st].view(n, w), dev[ss])
+              for g, ss, st in zip(cache.groups, self.s_slots, self.s_tables)}
+        cap = w * cache.page_size
+        return StepContext(
+            num_tokens=n, num_seqs=n, query_lens=[1] * n, context_lens=[cap] * n,
+            tokens=dev[self.s_tokens], positions=dev[self.s_pos], cu_query_lens=dev[self.s_cu],
+            context_lens_dev=dev[self.s_ctx], decode_seqs=dev[self.s_dec], prefill_seqs=dev[self.s_pre],
+            num_decode=n, num_prefill=0, max_query_len=1, max_context_len=cap, kv=kv,
+            state_slots=dev[self.s_state] if cache.has_state else None, state_slots_host=[0] * n,
+            arena=self.arena, dtype=runner.model.dtype)
+
+    def record(self, runner: "ModelRunner") -> None:
+        model, caches = runner.model, runner.cache.entries
+
+        def run() -> torch.Tensor:
+            self.arena.begin_step()
+            return model.forward(self.context(runner), caches, self.dev[self.s_rows], self.rows)
+
+        # Twice without recording: the first sizes the scratch memory, the second shows that
+        # it no longer moves; then the same launches are recorded.
+        run()
+        reserved = self.arena.reserved_bytes
+        run()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        with torch.cuda.graph(graph):
+            logits = run()
+        self.num_kernels = ops.launch_count - before
+        ops.launch_count = before          # recorded, not run
+        if self.arena.reserved_bytes != reserved:
+            raise RuntimeError("scratch memory moved while a decode graph was being recorded")
+        self.graph, self.logits = graph, logits
+
+    def fill(self, runner: "ModelRunner", entries: Sequence[StepEntry]) -> None:
+        self.copied.synchronize()          # the last copy must have left the host buffer
+        buf, n, b = self.host_np, self.rows, len(entries)
+        buf[self.s_tokens][:b] = [e.tokens[0] for e in entries]
+        totals = [e.cache.num_tokens for e in entries]
+        buf[self.s_ctx][:b] = totals
+        buf[self.s_pos][:b] = np.asarray(totals, dtype=np.int32) - 1
+        buf[self.s_state][:b] = [e.cache.state_slot for e in entries]
+        for g, ss, st in zip(runner.cache.groups, self.s_slots, self.s_tables):
+            ps = g.page_size
+            slots, table = buf[ss], buf[st].reshape(n, self.width)
+            for i, e in enumerate(entries):
+                pages = e.cache.tables[g.index].pages_array()
+                table[i, : pages.shape[0]] = pages
+                p = totals[i] - 1
+                slots[i] = pages[p // ps] * ps + p % ps
+        self._fill_padding(runner, b)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager) -> None:
         self.model = model
         self.cache = cache
         self.device = model.device
         self.arena = Arena(self.device)
+        self.graphs: dict[int, DecodeGraph] = {}
+        self.graph_max_context = 0
+        self.num_graph_steps = 0
         self._host: torch.Tensor | None = None     # pinned int32 staging buffer
         self._host_np: np.ndarray | None = None
         self._dev: torch.Tensor | None = None
@@ -164,6 +290,33 @@ class ModelRunner:
         )
         return ctx, (dev[s_rows] if r else None), r
 
+    # ------------------------------------------------------------------- graphs
+    @torch.inference_mode()
+    def record_decode_graphs(self, max_batch: int, max_context: int, buckets: Sequence[int] | None = None) -> None:
+        """Record one decode step per batch-size bucket. Afterwards a step in which every
+        request brings exactly one token, asks for that token's logits, and fits the largest
+        bucket and ``max_context`` is replayed from the recording instead of being launched
+        kernel by kernel."""
+        if self.device.type != "cuda":
+            raise RuntimeError("decode graphs need a CUDA device")
+        if not all(layer.block.mixer.graph_safe for layer in self.model.parts.layers):
+            raise RuntimeError("a mixer of this model reads the step on the host; its decode step cannot be recorded")
+        self.graph_max_context = max_context
+        for rows in sorted(set(buckets or default_buckets(max_batch))):
+            g = DecodeGraph(self, rows, max_context)
+            g.record(self)
+            self.graphs[rows] = g
+
+    def _graph_for(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None) -> DecodeGraph | None:
+        if not self.graphs or len(entries) > max(self.graphs):
+            return None
+        for e in entries:
+            if len(e.tokens) != 1 or e.cache.num_tokens > self.graph_max_context:
+                return None
+        if want is not None and any(list(w) != [0] for w in want):
+            return None
+        return self.graphs[min(r for r in self.graphs if r >= len(entries))]
+
     # --------------------------------------------------------------------- step
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None = None
@@ -171,6 +324,14 @@ class ModelRunner:
         """Run one step. Returns float32 logits ``[wanted, vocab]`` in the order of the entries
         and of their wanted places (a view into step scratch: use it before the next step),
         or ``None`` when nothing is wanted."""
+        graph = self._graph_for(entries, want)
+        if graph is not None:
+            graph.fill(self, entries)
+            graph.graph.replay()
+            ops.launch_count += graph.num_kernels
+            self.num_steps += 1
+            self.num_graph_steps += 1
+            return graph.logits[: len(entries)]
         ctx, rows, r = self.build_context(entries, want)
         logits = self.model.forward(ctx, self.cache.entries, rows, r)
         self.num_steps += 1

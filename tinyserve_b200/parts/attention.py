@@ -21,6 +21,8 @@ from .base import KVCacheEntry, KVNeed, Mixer, StepContext, TensorSpec, register
 
 
 class GQAAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, scale: float, qk_norm: bool = False, qk_norm_eps: float = 1e-6,
                  window: int | None = None) -> None:

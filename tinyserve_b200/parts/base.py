@@ -171,6 +171,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if ``forward`` reads nothing of the step on the host (no lengths, no slot lists):
+    # only then can a decode step with this mixer be recorded once and replayed as a graph.
+    graph_safe: bool = False
+
     def cache_need(self) -> KVNeed | StateNeed | None:
         return None
 
