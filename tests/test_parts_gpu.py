@@ -22,8 +22,13 @@ pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
 
 
-def tol(dtype):
-    return {"atol": 2e-5, "rtol": 2e-5} if dtype == torch.float32 else {"atol": 3e-2, "rtol": 3e-2}
+def tol(dtype, want=None):
+    """float32: summation order only. bfloat16: a few steps of the 8-bit mantissa at the scale
+    of the largest value (inputs, intermediate activations and the output are each rounded)."""
+    if dtype == torch.float32:
+        return {"atol": 2e-5, "rtol": 2e-5}
+    scale = 1.0 if want is None else max(1.0, float(want.abs().max()))
+    return {"atol": 2e-2 * scale, "rtol": 3e-2}
 
 
 def rnd(*shape, seed=0, scale=1.0):
@@ -102,7 +107,7 @@ def test_attention_part_whole_then_token_by_token(dtype, hq, hkv, d, hidden) -> 
     # whole
     ctx, cache = context(dtype, [part.cache_need()], [(t, t)])
     got = part.forward(x.cuda(), ctx, cache.entries[0], True, rope.prepare(ctx))
-    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype, want))
     # token by token into one cache
     cache = CacheManager([part.cache_need()], page_size=4, num_pages=32, max_requests=2, dtype=dtype, device="cuda")
     runner = ModelRunner(SimpleNamespace(dtype=dtype, device=torch.device("cuda")), cache)
@@ -112,7 +117,7 @@ def test_attention_part_whole_then_token_by_token(dtype, hq, hkv, d, hidden) -> 
         cache.append(r, 1)
         ctx, _, _ = runner.build_context([StepEntry(r, [1])], None)
         rows.append(part.forward(x[i: i + 1].cuda(), ctx, cache.entries[0], True, rope.prepare(ctx)).float().cpu())
-    torch.testing.assert_close(torch.cat(rows), want, **tol(dtype))
+    torch.testing.assert_close(torch.cat(rows), want, **tol(dtype, want))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -125,7 +130,7 @@ def test_swiglu_part(dtype) -> None:
     ctx, _ = context(dtype, [], [(t, t)])
     got = part.forward(x.cuda(), ctx)
     want = plain.swiglu(x.float(), g.float(), u.float(), dn.float())
-    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype, want))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -142,5 +147,6 @@ def test_embedding_and_head(dtype) -> None:
     x = rnd(4, hidden, seed=2).to(dtype)
     out = torch.empty(4, vocab, device="cuda")
     head.forward(x.cuda(), out)
-    torch.testing.assert_close(out.cpu(), plain.linear(x.float(), table.float()), **tol(dtype))
+    want = plain.linear(x.float(), table.float())
+    torch.testing.assert_close(out.cpu(), want, **tol(dtype, want))
     assert head.ignorable_tensors("") == {"lm_head.weight"}

@@ -18,26 +18,33 @@ class _Region:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self.buf = torch.empty(0, dtype=torch.uint8, device=device)
-        self.used = 0
-        self.high_water = 0
+        self.used = 0          # offset in ``buf`` of the next take
+        self.demand = 0        # bytes taken since the last reset, wherever they came from
+        self.high_water = 0    # the largest demand of any step so far
 
     def reset(self) -> None:
+        if self.high_water > self.buf.numel():
+            # The last step outgrew the buffer and was served piecemeal; make one buffer that
+            # holds a whole step, so that from now on nothing moves.
+            self.buf = torch.empty(self.high_water, dtype=torch.uint8, device=self.device)
         self.used = 0
+        self.demand = 0
 
     def take(self, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         numel = 1
         for s in shape:
             numel *= int(s)
         nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        self.demand = (self.demand + _ALIGN - 1) // _ALIGN * _ALIGN + nbytes
+        self.high_water = max(self.high_water, self.demand)
         start = (self.used + _ALIGN - 1) // _ALIGN * _ALIGN
         end = start + nbytes
         if end > self.buf.numel():
             # Grow: views handed out earlier keep the old buffer alive until they die.
-            grow = max(end, 2 * self.buf.numel(), 1 << 16)
+            grow = max(nbytes, 2 * self.buf.numel(), 1 << 16)
             self.buf = torch.empty(grow, dtype=torch.uint8, device=self.device)
             start, end = 0, nbytes
         self.used = end
-        self.high_water = max(self.high_water, end)
         if numel == 0:
             return torch.empty(shape, dtype=dtype, device=self.device)
         return self.buf[start:end].view(dtype).view(shape)

@@ -125,8 +125,8 @@ class DecodeGraph:
         # Twice without recording: the first sizes the scratch memory, the second shows that
         # it no longer moves; then the same launches are recorded.
         run()
-        reserved = self.arena.reserved_bytes
         run()
+        reserved = self.arena.reserved_bytes
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
