@@ -229,6 +229,45 @@ def test_gemm(dtype, out_dtype, m, n, k) -> None:
     torch.testing.assert_close(out.float(), want.float(), **t)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("n,k", [(16, 32), (48, 96), (1024, 2048), (4096, 1024), (151936, 1024), (1040, 3072)])
+def test_gemm_skinny(out_dtype, m, n, k) -> None:
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=1), rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=out_dtype)
+    want = torch.empty(m, n, device="cuda", dtype=out_dtype)
+    ops.gemm_skinny(x, w, out)
+    ref.gemm(x, w, want)
+    t = {"atol": 2e-4, "rtol": 1e-4} if out_dtype == torch.float32 else {"atol": 2e-2, "rtol": 1e-2}
+    torch.testing.assert_close(out.float(), want.float(), **t)
+
+
+def test_gemm_skinny_refuses_what_it_cannot_take() -> None:
+    x, w = rnd(4, 80, dtype=torch.bfloat16), rnd(32, 80, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.gemm_skinny(x, w, torch.empty(4, 32, device="cuda", dtype=torch.bfloat16))
+    out = torch.empty(4, 32, device="cuda", dtype=torch.bfloat16)
+    ops.gemm(x, w, out)                                   # the general entry takes another kernel
+    want = torch.empty_like(out)
+    ref.gemm(x, w, want)
+    torch.testing.assert_close(out.float(), want.float(), atol=5e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 256), (1, 72, 80), (200, 1000, 1024), (2048, 4096, 1024),
+                                   (300, 1024, 3072), (77, 151936, 1024), (129, 130, 136)])
+def test_gemm_tcgen05(out_dtype, tile_n, m, n, k) -> None:
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=1), rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=out_dtype)
+    want = torch.empty(m, n, device="cuda", dtype=out_dtype)
+    ops.gemm_tcgen05(x, w, out, tile_n)
+    ops.check_device_errors()
+    ref.gemm(x, w, want)
+    t = {"atol": 2e-4, "rtol": 1e-4} if out_dtype == torch.float32 else {"atol": 2e-2, "rtol": 1e-2}
+    torch.testing.assert_close(out.float(), want.float(), **t)
+
+
 def test_gemm_fp32_row_does_not_depend_on_batch() -> None:
     x, w = rnd(70, 200, seed=1), rnd(333, 200, seed=2)
     full = torch.empty(70, 333, device="cuda")

@@ -1,0 +1,273 @@
+// out[M, N] = x[M, K] * w[N, K]^T in bf16 on the 5th-generation tensor cores: TMA loads into
+// 128-byte-swizzled shared memory, tcgen05.mma issued by one thread with the accumulator in
+// tensor memory (TMEM), tcgen05.ld for the epilogue. bf16 or float output from the 32-bit
+// accumulator. The library product that this replaces is upstream's F.linear
+// (src/tinyserve/model.py:156,173,178-179,208).
+//
+// One CTA computes a 128 x BN tile. Both operands are K-major in memory ([rows, K] row-major),
+// which is the layout the instruction wants, so a stage is two TMA boxes: 128 rows x 64 k of x
+// and BN rows x 64 k of w. Out-of-range rows and the K tail read as zeros (TMA fill), so any
+// M, N and any K that is a multiple of 8 (16-byte row pitch) are taken.
+//   warp 0, one lane : TMA producer        (waits "empty", arms "full" with the byte count)
+//   warp 1, one lane : MMA issuer          (waits "full", 4 x tcgen05.mma of K = 16 per stage,
+//                                           tcgen05.commit frees the stage; last commit -> "done")
+//   warps 0-3        : epilogue            (tcgen05.ld of the warp's 32 TMEM lanes, cast, store)
+// Every wait on an mbarrier is bounded: when the bound is hit the kernel records it in
+// *error_flag, stops waiting and still frees its tensor memory, so a fault in the pipeline
+// shows as an error code on the host and never as a hang.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace ts {
+
+constexpr int TG_BM = 128;
+constexpr int TG_BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
+constexpr int TG_THREADS = 128;
+constexpr long long TG_WAIT_CYCLES = 2000000000ll;   // about a second: far beyond any real wait
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity. Returns false if the bound was hit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  const long long start = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if ((i & 1023u) == 1023u && clock64() - start > TG_WAIT_CYCLES) break;
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* result_in_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(result_in_smem)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
+// 8-row groups 1024 bytes apart (stride byte offset), leading byte offset unused (1), version 1.
+__device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+template <int BN, int STAGES, typename TOut>
+__global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                  const __grid_constant__ CUtensorMap map_w,
+                                                                  TOut* __restrict__ out, int M, int N, int K,
+                                                                  int* __restrict__ error_flag) {
+  constexpr uint32_t A_BYTES = TG_BM * TG_BK * 2, B_BYTES = BN * TG_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  // instruction descriptor: D = f32, A = B = bf16, both K-major, N = BN, M = 128
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t done_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * BN;
+  const int num_kb = (K + TG_BK - 1) / TG_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&done_bar, 1);
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_base_slot, BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t phase = (kb / STAGES) & 1;
+      if (!mbar_wait(&empty_bar[s], phase ^ 1)) { failed = 1; break; }
+      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
+      tma_load_2d(a, &map_x, &full_bar[s], kb * TG_BK, m0);
+      tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t phase = (kb / STAGES) & 1;
+      if (!mbar_wait(&full_bar[s], phase)) { failed = 1; break; }
+      tc_fence_after();
+      const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+      const uint64_t adesc = sw128_desc(a_addr), bdesc = sw128_desc(a_addr + A_BYTES);
+#pragma unroll
+      for (int k = 0; k < TG_BK / 16; ++k) {
+        // 16 k = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
+        umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
+      }
+      umma_commit(&empty_bar[s]);     // the stage is free once these MMAs have read it
+    }
+    umma_commit(&done_bar);           // the accumulator is complete once every MMA has finished
+  }
+  __syncwarp();
+
+  // ---------------- epilogue: warp w owns TMEM lanes 32 w .. 32 w + 31 = rows m0 + 32 w + lane
+  bool ok = mbar_wait(&done_bar, 0);
+  tc_fence_after();
+  if (!ok || failed) {
+    if (lane == 0) atomicExch(error_flag, 1);
+  } else {
+    const int row = m0 + warp * 32 + lane;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
+      if (row < M) {
+        TOut* dst = out + (size_t)row * N + n0 + c * 32;
+        if (n0 + c * 32 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+          if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]);
+              Vec<bf16> v;
+              v.pack(f);
+              v.store((bf16*)dst + j);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>((float*)dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                      __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          }
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (n0 + c * 32 + j < N) dst[j] = from_float<TOut>(__uint_as_float(r[j]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, BN);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// rows x K bf16 row-major; box = box_rows x 64, 128-byte swizzle, zero fill outside.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TG_BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, typename TOut>
+static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, int M, int N, int K, int* error_flag,
+                     cudaStream_t stream) {
+  const size_t smem = (size_t)STAGES * (TG_BM + BN) * TG_BK * 2 + 1024;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, TOut>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid((N + BN - 1) / BN, (M + TG_BM - 1) / TG_BM);
+  kern<<<grid, TG_THREADS, smem, stream>>>(mx, mw, out, M, N, K, error_flag);
+  return launch_status();
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+// error_flag: device int that the kernel sets to 1 if a bounded wait ran out.
+extern "C" int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int out_dtype,
+                               int tile_n, int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
+  if (tile_n != 64 && tile_n != 128 && tile_n != 256) return TS_ERR_BAD_ARGUMENT;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, TG_BM) || !make_map(&mw, w, N, K, tile_n)) return TS_ERR_UNSUPPORTED;
+  const bool f32 = out_dtype == TS_DTYPE_F32;
+  if (!f32 && out_dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
+#define TS_TC(BN_, ST_)                                                                               \
+  return f32 ? launch_tc<BN_, ST_, float>(mx, mw, (float*)out, M, N, K, error_flag, stream)           \
+             : launch_tc<BN_, ST_, bf16>(mx, mw, (bf16*)out, M, N, K, error_flag, stream)
+  if (tile_n == 64) { TS_TC(64, 4); }
+  if (tile_n == 128) { TS_TC(128, 3); }
+  TS_TC(256, 4);
+#undef TS_TC
+}

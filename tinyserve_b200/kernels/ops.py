@@ -34,7 +34,10 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_qk_norm_rope_write": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ts_paged_attention_simt": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
                                 _f, _i, _i, _vp, _vp, _i, _vp],
+    "ts_prefill_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _fns: dict[str, Any] = {}
@@ -210,6 +213,19 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         raise KernelError(f"paged_attention: head_dim={d} must be a multiple of 16 up to 256")
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
         raise KernelError("paged_attention: block_tables must be [requests, width]")
+    num_prefill = ctx.num_prefill
+    if num_prefill and dt == torch.bfloat16 and d <= 128:
+        # prefill rows on the tensor cores; the decode rows follow below
+        _check(_fn("ts_prefill_attention_mma")(
+            _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+            _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
+            _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+            _dev(ctx.context_lens_dev, "context_lens", torch.int32),
+            _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
+            hq, hkv, d, page_size, float(scale), int(window), _stream()), "prefill_attention_mma")
+        num_prefill = 0
+        if not ctx.num_decode:
+            return
     splits, part_acc, part_ml = 1, None, None
     if ctx.num_decode:
         splits = decode_splits(ctx.num_decode, hkv, hq // hkv, ctx.max_context_len)
@@ -222,10 +238,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
         _dev(ctx.context_lens_dev, "context_lens", torch.int32),
         _dev(ctx.decode_seqs, "decode_seqs", torch.int32), ctx.num_decode,
-        _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), ctx.num_prefill, ctx.max_query_len,
+        _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
         hq, hkv, d, page_size, float(scale), int(window), splits,
         _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _code(dt), _stream()), "paged_attention",
-        kernels=(1 if ctx.num_prefill else 0) + (1 if ctx.num_decode else 0) + (1 if splits > 1 else 0))
+        kernels=(1 if num_prefill else 0) + (1 if ctx.num_decode else 0) + (1 if splits > 1 else 0))
 
 
 # ------------------------------------------------------------------------- gemm
@@ -245,11 +261,64 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _check(_fn("ts_gemm_simt")(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), m, n, k, _F32, _F32, _stream()),
                "gemm")
         return
+    if m <= SKINNY_MAX_ROWS and k % 32 == 0 and n % 16 == 0:
+        gemm_skinny(x, w, out)
+        return
     _dev(x, "x"), _dev(w, "w"), _dev(out, "out")
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)                       # vendor library matrix product
     else:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+
+
+# Up to this many rows a bf16 product streams the weights through the skinny kernel.
+SKINNY_MAX_ROWS = 16
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """bf16 ``out[M, N] = x[M, K] @ w[N, K]^T`` for M <= 64, K % 32 == 0, N % 16 == 0: weights
+    streamed once from HBM into tensor-core fragments (``csrc/gemm_skinny.cu``)."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny: shape or dtype mismatch")
+    _check(_fn("ts_gemm_skinny")(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), m, n, k, _code(out.dtype), _stream()),
+           "gemm_skinny")
+
+
+_error_words: dict[torch.device, torch.Tensor] = {}
+
+
+def _error_word(device: torch.device) -> torch.Tensor:
+    """A device int32 that kernels with bounded waits set when a wait ran out."""
+    w = _error_words.get(device)
+    if w is None:
+        w = _error_words[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return w
+
+
+def check_device_errors() -> None:
+    """Raise if a kernel gave up on a bounded wait since the last check (synchronises)."""
+    for dev, w in _error_words.items():
+        if int(w.item()) != 0:
+            w.zero_()
+            raise KernelError(f"a kernel on {dev} gave up waiting on its pipeline (bounded wait ran out)")
+
+
+# Output-tile width of the tcgen05 product; 128 keeps two CTAs on an SM.
+TCGEN05_TILE_N = 128
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_n: int | None = None) -> None:
+    """bf16 ``out[M, N] = x[M, K] @ w[N, K]^T`` with tcgen05.mma, TMA and TMEM
+    (``csrc/gemm_tcgen05.cu``); K % 8 == 0, any M and N; out bf16 or float32."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n) or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tcgen05: shape or dtype mismatch")
+    _check(_fn("ts_gemm_tcgen05")(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), m, n, k, _code(out.dtype),
+                                  tile_n or TCGEN05_TILE_N, _error_word(x.device).data_ptr(), _stream()),
+           "gemm_tcgen05")
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
