@@ -110,6 +110,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between kernels")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     args = ap.parse_args()
@@ -130,6 +131,7 @@ def main() -> int:
     from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
+    ops.set_programmatic_launch(not args.no_pdl)
     cfg_dict = dict(QWEN3_0_6B)
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:

@@ -125,6 +125,13 @@ def gemm(x, w, out) -> None:
 gemm_simt = gemm
 
 
+def gemm_swiglu(x, w_gate_up, out, arena=None) -> None:
+    inter = out.shape[1]
+    gu = torch.empty(x.shape[0], 2 * inter, dtype=x.dtype, device=x.device)
+    gemm(x, w_gate_up, gu)
+    silu_mul(gu, out)
+
+
 # ---------------------------------------------------------------------- sampling
 def _philox4x32_10(c: np.ndarray, k0: int, k1: int) -> np.ndarray:
     """c: [N, 4] uint32 counters -> [N, 4] uint32 (Philox4x32 with 10 rounds)."""
@@ -167,9 +174,8 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None) ->
         if not temp > 0:
             res.append(int(row.argmax()))
             continue
-        z = row * np.float32(1.0 / temp)
-        z = z - z.max()
-        e = torch.exp(z)
+        z = row * (np.float32(1.0) / np.float32(temp))
+        e = torch.exp(z - z.max())
         keep = torch.ones(v, dtype=torch.bool)
         tp = 1.0 if top_p is None else float(top_p[b])
         if tp < 1:
@@ -190,7 +196,7 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None) ->
 
 
 _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
-          "gemm", "gemm_simt", "sample"]
+          "gemm", "gemm_simt", "gemm_swiglu", "sample"]
 
 
 @contextmanager

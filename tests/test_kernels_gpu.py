@@ -242,6 +242,20 @@ def test_gemm_skinny(out_dtype, m, n, k) -> None:
     torch.testing.assert_close(out.float(), want.float(), **t)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", [1, 8, 13, 16, 40])
+@pytest.mark.parametrize("inter,k", [(3072, 1024), (176, 80), (48, 64), (112, 96)])
+def test_gemm_swiglu(dtype, m, inter, k) -> None:
+    x = rnd(m, k, dtype=dtype, seed=1)
+    w = rnd(2 * inter, k, dtype=dtype, seed=2, scale=0.1)
+    out = torch.full((m, inter), float("nan"), device="cuda", dtype=dtype)
+    want = torch.empty(m, inter, device="cuda", dtype=dtype)
+    ops.gemm_swiglu(x, w, out, Arena("cuda"))
+    ref.gemm_swiglu(x, w, want)
+    t = {"atol": 1e-4, "rtol": 1e-4} if dtype == torch.float32 else {"atol": 3e-2, "rtol": 3e-2}
+    torch.testing.assert_close(out.float(), want.float(), **t)
+
+
 def test_gemm_skinny_refuses_what_it_cannot_take() -> None:
     x, w = rnd(4, 80, dtype=torch.bfloat16), rnd(32, 80, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="not supported"):
@@ -303,16 +317,20 @@ def test_sample_temperature_and_top_p_match_reference(vocab) -> None:
 
 
 def test_sample_frequencies_follow_softmax() -> None:
-    vocab, n = 8, 20000
+    vocab, n = 8, 4096
     row = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5, -3.0, 1.5, 0.2], device="cuda")
     logits = row.repeat(n, 1).contiguous()
     temps = torch.full((n,), 0.7, device="cuda")
     seeds = torch.arange(n, device="cuda", dtype=torch.int64)
-    draws = torch.zeros(n, device="cuda", dtype=torch.int64)
     out = torch.empty(n, device="cuda", dtype=torch.int32)
-    ops.sample(logits, out, temps, None, seeds, draws)
-    freq = torch.bincount(out.long(), minlength=vocab).float() / n
-    torch.testing.assert_close(freq, torch.softmax(row / 0.7, -1), atol=0.012, rtol=0)
+    counts = torch.zeros(vocab, device="cuda")
+    for draw in range(4):                                  # 16,384 independent draws
+        draws = torch.full((n,), draw, device="cuda", dtype=torch.int64)
+        ops.sample(logits, out, temps, None, seeds, draws)
+        counts += torch.bincount(out.long(), minlength=vocab).float()
+    freq = counts / (4 * n)
+    torch.testing.assert_close(freq, torch.softmax(row / 0.7, -1), atol=0.015, rtol=0)
+    draws = torch.zeros(n, device="cuda", dtype=torch.int64)
     # nucleus: only the tokens whose more likely tokens hold < 0.6 may appear
     top_p = torch.full((n,), 0.6, device="cuda")
     ops.sample(logits, out, temps, top_p, seeds, draws)

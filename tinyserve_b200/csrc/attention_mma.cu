@@ -49,6 +49,8 @@ __global__ void __launch_bounds__(MA_THREADS) prefill_attn_mma_kernel(AttnArgs a
   bf16* Ks = Qs + MA_BM * DS;                            // [2][64][DS]
   bf16* Vs = Ks + 2 * MA_BN * DS;                        // [2][64][DS]
 
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int group = a.num_heads / a.num_kv_heads;
@@ -259,8 +261,7 @@ static int launch_mma(const AttnArgs& a, int max_query_len, cudaStream_t stream)
   const int ge = (group <= MA_BM && MA_BM % group == 0) ? group : 1;
   const int tpt = MA_BM / ge;
   dim3 grid((max_query_len + tpt - 1) / tpt, a.num_seqs, ge == group ? a.num_kv_heads : a.num_heads);
-  kern<<<grid, MA_THREADS, smem, stream>>>(a, ge);
-  return launch_status();
+  return launch(kern, grid, MA_THREADS, smem, stream, a, ge);
 }
 
 }  // namespace ts

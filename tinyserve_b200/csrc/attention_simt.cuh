@@ -11,7 +11,8 @@
 //    src/tinyserve/triton_prefill.py:50-125, which tiles the same way over the paged cache).
 //  * decode kernel: one CTA per (request, kv head, split of the keys); a group of lanes reads
 //    one key with 16-byte loads, all query heads of the group share each key and value; the
-//    splits are merged by a second kernel (after src/tinyserve/triton_attention.py:243-327).
+//    CTA that finishes last merges the splits (the split-K scheme is upstream's,
+//    src/tinyserve/triton_attention.py:243-327, which merges in a second kernel).
 // Keys outside a request's own range are never loaded: their scores are -inf and their values
 // zero, so whatever lies in pages of other requests cannot reach the result.
 #pragma once
@@ -39,6 +40,8 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
   float* row_l = row_m + PF_TQ;                 // [TQ]
   float* row_c = row_l + PF_TQ;                 // [TQ] correction factor of this tile
 
+  pdl_trigger();
+  pdl_wait();
   const int seq = a.seq_ids[blockIdx.y];
   const int head = blockIdx.z;
   const int kvh = head / (a.num_heads / a.num_kv_heads);
@@ -201,19 +204,25 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
 // ================================================================ decode (split-K)
 constexpr int DC_WARPS = 4;
 constexpr int DC_THREADS = DC_WARPS * 32;
-constexpr int DC_UNROLL = 2;     // keys per lane group in flight
+constexpr int DC_MAX_COUNTERS = 1 << 16;
+
+// One arrival counter per (request, CTA row of the grid): the CTA that arrives last merges the
+// key ranges. Counters are zero when the library is loaded and every merge puts its counter
+// back to zero, so no launch ever has to clear them.
+static __device__ unsigned int g_decode_counters[DC_MAX_COUNTERS];
 
 // GT = query heads handled per CTA (a kv group is covered by ceil(G / GT) CTAs);
-// CPL = 16-byte chunks of a key per lane.
-template <typename T, int GT, int CPL>
+// CPL = 16-byte chunks of a key per lane; U = keys per lane group whose loads are in flight.
+template <typename T, int GT, int CPL, int U>
 __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int lanes_per_key, int passes) {
   constexpr int VEC = Vec<T>::N;
   constexpr int EPL = VEC * CPL;                 // elements of a key per lane
   extern __shared__ float smem[];                // [DC_WARPS][GT][D + 2]
+  __shared__ int is_last;
+  pdl_trigger();
   const int D = a.head_dim;
   const int G = a.num_heads / a.num_kv_heads;
   const int si = blockIdx.x;
-  const int seq = a.seq_ids[si];
   const int kvh = blockIdx.y / passes;
   const int g0 = (blockIdx.y - kvh * passes) * GT;   // first head of the group this CTA handles
   const int ng = min(GT, G - g0);
@@ -223,7 +232,9 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
   const int sub = lane / LPK, lk = lane - sub * LPK;  // which key of the warp's batch, which lane of it
   const int KPW = 32 / LPK;                           // keys per warp per batch
   const int chunks = D / VEC;
+  pdl_wait();
 
+  const int seq = a.seq_ids[si];
   const int ctx = a.ctx_lens[seq];
   const int qrow = a.cu_q[seq];
   const int lo = (a.window > 0) ? max(0, ctx - a.window) : 0;
@@ -264,12 +275,13 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
     for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
   }
 
-  const int stride = DC_WARPS * KPW * DC_UNROLL;
-  for (int base = k_begin + (warp * DC_UNROLL) * KPW; base < k_end; base += stride) {
-    float kf[DC_UNROLL][EPL], vf[DC_UNROLL][EPL];
-    bool valid[DC_UNROLL];
+  const int stride = DC_WARPS * KPW * U;
+  for (int base = k_begin + (warp * U) * KPW; base < k_end; base += stride) {
+    // ---- all loads of this batch first: U keys and U values per lane group, kept packed
+    Vec<T> kraw[U][CPL], vraw[U][CPL];
+    bool valid[U];
 #pragma unroll
-    for (int u = 0; u < DC_UNROLL; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int kpos = base + u * KPW + sub;
       valid[u] = kpos < k_end;
       size_t off = 0;
@@ -281,49 +293,66 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
       for (int c = 0; c < CPL; ++c) {
         const int chunk = lk + c * LPK;
         if (valid[u] && chunk < chunks) {
-          Vec<T> kv, vv;
-          kv.load(kc + off + (size_t)chunk * VEC);
-          vv.load(vc + off + (size_t)chunk * VEC);
-          kv.unpack(&kf[u][c * VEC]);
-          vv.unpack(&vf[u][c * VEC]);
+          kraw[u][c].load(kc + off + (size_t)chunk * VEC);
+          vraw[u][c].load(vc + off + (size_t)chunk * VEC);
         } else {
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) { kf[u][c * VEC + e] = 0.f; vf[u][c * VEC + e] = 0.f; }
+          kraw[u][c].zero();
+          vraw[u][c].zero();
         }
       }
     }
+    // ---- scores
+    float s[GT][U];
 #pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      float s[DC_UNROLL];
+    for (int u = 0; u < U; ++u) {
+      float kf[EPL];
 #pragma unroll
-      for (int u = 0; u < DC_UNROLL; ++u) {
+      for (int c = 0; c < CPL; ++c) kraw[u][c].unpack(&kf[c * VEC]);
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
         float d = 0.f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) d = fmaf(qreg[g][e], kf[u][e], d);
-        for (int o = LPK >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-        s[u] = valid[u] ? d : NEG_INF;
+        for (int e = 0; e < EPL; ++e) d = fmaf(qreg[g][e], kf[e], d);
+        s[g][u] = d;
       }
+    }
+#pragma unroll
+    for (int g = 0; g < GT; ++g)
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float d = s[g][u];
+        for (int o = LPK >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        s[g][u] = valid[u] ? d : NEG_INF;
+      }
+    // ---- online softmax, one rescale per batch
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
       float m_new = m[g];
 #pragma unroll
-      for (int u = 0; u < DC_UNROLL; ++u) m_new = fmaxf(m_new, s[u]);
-      if (m_new != NEG_INF) {
-        const float corr = exp2f(m[g] - m_new);     // m = -inf gives 0
-        float p[DC_UNROLL], psum = 0.f;
+      for (int u = 0; u < U; ++u) m_new = fmaxf(m_new, s[g][u]);
+      const float corr = (m_new == NEG_INF) ? 1.f : exp2f(m[g] - m_new);   // m = -inf gives 0
+      float psum = 0.f;
 #pragma unroll
-        for (int u = 0; u < DC_UNROLL; ++u) {
-          p[u] = valid[u] ? exp2f(s[u] - m_new) : 0.f;
-          psum += p[u];
-        }
-        l[g] = l[g] * corr + psum;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          float v = acc[g][e] * corr;
-#pragma unroll
-          for (int u = 0; u < DC_UNROLL; ++u) v = fmaf(p[u], vf[u][e], v);
-          acc[g][e] = v;
-        }
-        m[g] = m_new;
+      for (int u = 0; u < U; ++u) {
+        const float p = (s[g][u] == NEG_INF) ? 0.f : exp2f(s[g][u] - m_new);
+        s[g][u] = p;
+        psum += p;
       }
+      l[g] = l[g] * corr + psum;
+      m[g] = m_new;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) acc[g][e] *= corr;
+    }
+    // ---- values
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float vf[EPL];
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) vraw[u][c].unpack(&vf[c * VEC]);
+#pragma unroll
+      for (int g = 0; g < GT; ++g)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = fmaf(s[g][u], vf[e], acc[g][e]);
     }
   }
 
@@ -384,28 +413,37 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
       if (d == 0) { a.part_ml[pidx * 2] = mm; a.part_ml[pidx * 2 + 1] = den; }
     }
   }
-}
+  if (a.num_splits == 1) return;
 
-// out = sum_s w_s acc_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
-template <typename T>
-__global__ void decode_merge_kernel(AttnArgs a) {
-  const int si = blockIdx.x, head = blockIdx.y;
-  const int seq = a.seq_ids[si];
-  const int qrow = a.cu_q[seq];
-  const int D = a.head_dim, S = a.num_splits;
-  const size_t base = ((size_t)si * a.num_heads + head) * S;
-  float mm = NEG_INF;
-  for (int s = 0; s < S; ++s) mm = fmaxf(mm, a.part_ml[(base + s) * 2]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  // ---- the CTA that arrives last for this (request, heads) merges the ranges:
+  //      out = sum_s w_s acc_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
+  __threadfence();
+  __syncthreads();
+  unsigned int* counter = &g_decode_counters[((size_t)si * gridDim.y + blockIdx.y) % DC_MAX_COUNTERS];
+  if (threadIdx.x == 0) {
+    const unsigned int old = atomicAdd(counter, 1u);
+    is_last = (old == (unsigned int)a.num_splits - 1u);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int S = a.num_splits;
+  for (int idx = threadIdx.x; idx < ng * D; idx += DC_THREADS) {
+    const int g = idx / D, d = idx - g * D;
+    const int head = kvh * G + g0 + g;
+    const size_t pbase = ((size_t)si * a.num_heads + head) * S;
+    float mm = NEG_INF;
+    for (int sp = 0; sp < S; ++sp) mm = fmaxf(mm, __ldcg(&a.part_ml[(pbase + sp) * 2]));
     float num = 0.f, den = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const float ms = a.part_ml[(base + s) * 2];
+    for (int sp = 0; sp < S; ++sp) {
+      const float ms = __ldcg(&a.part_ml[(pbase + sp) * 2]);
       const float c = (ms == NEG_INF) ? 0.f : exp2f(ms - mm);
-      num += a.part_acc[(base + s) * D + d] * c;
-      den += a.part_ml[(base + s) * 2 + 1] * c;
+      num += __ldcg(&a.part_acc[(pbase + sp) * D + d]) * c;
+      den += __ldcg(&a.part_ml[(pbase + sp) * 2 + 1]) * c;
     }
     ((T*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = from_float<T>(num / den);
   }
+  if (threadIdx.x == 0) *counter = 0u;
 }
 
 template <typename T, int DJMAX>
@@ -419,8 +457,7 @@ static int launch_prefill_dj(const AttnArgs& a, int max_query_len, cudaStream_t 
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((max_query_len + PF_TQ - 1) / PF_TQ, a.num_seqs, a.num_heads);
-  kern<<<grid, PF_THREADS, smem, stream>>>(a);
-  return launch_status();
+  return launch(kern, grid, PF_THREADS, smem, stream, a);
 }
 
 template <typename T>
@@ -434,22 +471,18 @@ static int launch_prefill(const AttnArgs& a, int max_query_len, cudaStream_t str
 
 template <typename T, int GT, int CPL>
 static int launch_decode_gc(const AttnArgs& a, int lpk, cudaStream_t stream) {
+  constexpr int U = (CPL == 1 && GT <= 4) ? 8 : 4;
   const int G = a.num_heads / a.num_kv_heads;
   const int passes = (G + GT - 1) / GT;
+  if ((long long)a.num_seqs * a.num_kv_heads * passes > DC_MAX_COUNTERS && a.num_splits > 1) return TS_ERR_UNSUPPORTED;
   const size_t smem = sizeof(float) * (size_t)DC_WARPS * GT * (a.head_dim + 2);
-  auto kern = decode_attn_kernel<T, GT, CPL>;
+  auto kern = decode_attn_kernel<T, GT, CPL, U>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(a.num_seqs, a.num_kv_heads * passes, a.num_splits);
-  kern<<<grid, DC_THREADS, smem, stream>>>(a, lpk, passes);
-  int st = launch_status();
-  if (st != 0 || a.num_splits == 1) return st;
-  int threads = ((a.head_dim + 31) / 32) * 32;
-  if (threads > 256) threads = 256;
-  decode_merge_kernel<T><<<dim3(a.num_seqs, a.num_heads), threads, 0, stream>>>(a);
-  return launch_status();
+  return launch(kern, grid, DC_THREADS, smem, stream, a, lpk, passes);
 }
 
 template <typename T>

@@ -91,4 +91,33 @@ static inline int launch_status() {
   return (int)e;
 }
 
+// ---- programmatic dependent launch
+// Kernels of one step form a chain on one stream. When this switch is on they are launched so
+// that the next kernel's CTAs may be scheduled while the previous kernel is still draining:
+// every kernel calls pdl_trigger() at its start and pdl_wait() before it reads anything an
+// earlier kernel wrote or writes anything at all. pdl_wait() returns once every earlier kernel
+// of the chain has finished and its writes are visible, so ordering is what it was; only the
+// launch latency and the part of a kernel that needs no input (index arithmetic, prefetch of
+// weights) overlap the predecessor. Off, the two calls do nothing.
+extern int g_programmatic_launch;   // defined in elementwise.cu, set by ts_set_programmatic_launch
+
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                         Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_programmatic_launch ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace ts

@@ -8,12 +8,16 @@
 
 namespace ts {
 
+int g_programmatic_launch = 0;
+
 // ---------------------------------------------------------------- embedding
 // out[t, :] = float(table[tokens[t], :]).  A token id outside [0, vocab) yields a NaN row
 // instead of an out-of-bounds read (the host checks ids too).
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = tokens[t];
   float* o = out + (size_t)t * hidden;
@@ -28,11 +32,15 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
 // ------------------------------------------------------- residual add + RMSNorm
 // x = resid[row] (+ delta[row]);  if rows == nullptr the sum is written back to resid.
 // out[r] = T(x * rsqrt(mean(x^2) + eps)) * weight, the product rounded to T.
+// The row is kept in shared memory between the two passes when it fits (cache_row).
 template <typename T>
 __global__ void add_rms_norm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                     const T* __restrict__ weight, T* __restrict__ out,
-                                    const int* __restrict__ rows, int hidden, float eps) {
+                                    const int* __restrict__ rows, int hidden, float eps, int cache_row) {
+  extern __shared__ float xs[];
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
   float* x = resid + (size_t)row * hidden;
@@ -43,14 +51,20 @@ __global__ void add_rms_norm_kernel(float* __restrict__ resid, const T* __restri
     float v = x[i];
     if (d) v += to_float(d[i]);
     if (write_back) x[i] = v;
+    if (cache_row) xs[i] = v;
     ss += v * v;
   }
   ss = block_sum(ss, scratch);
   const float rstd = rsqrtf(ss / (float)hidden + eps);
   T* o = out + (size_t)r * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = x[i];
-    if (d && !write_back) v += to_float(d[i]);
+    float v;
+    if (cache_row) {
+      v = xs[i];
+    } else {
+      v = x[i];
+      if (d && !write_back) v += to_float(d[i]);
+    }
     const float n = round_to<T>(v * rstd);
     o[i] = from_float<T>(n * to_float(weight[i]));
   }
@@ -61,6 +75,8 @@ __global__ void add_rms_norm_kernel(float* __restrict__ resid, const T* __restri
 __global__ void rope_tables_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
                                    float* __restrict__ cos_out, float* __restrict__ sin_out,
                                    int num_tokens, int half) {
+  pdl_trigger();
+  pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= num_tokens * half) return;
   const int t = idx / half, i = idx - t * half;
@@ -75,6 +91,8 @@ __global__ void rope_tables_kernel(const int* __restrict__ positions, const doub
 // out[t, j] = T(silu(gate_up[t, j])) * gate_up[t, inter + j]
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) {
@@ -91,17 +109,19 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 
 using namespace ts;
 
+// Turn programmatic dependent launch of this library's kernels on (1) or off (0).
+extern "C" void ts_set_programmatic_launch(int on) { g_programmatic_launch = on ? 1 : 0; }
+extern "C" int ts_get_programmatic_launch() { return g_programmatic_launch; }
+
 extern "C" int ts_embed(const int* tokens, const void* table, float* out, int num_tokens, int hidden,
                         int vocab, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == TS_DTYPE_F32)
-    embed_kernel<float><<<num_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, hidden, vocab);
-  else if (dtype == TS_DTYPE_BF16)
-    embed_kernel<bf16><<<num_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, out, hidden, vocab);
-  else
-    return TS_ERR_BAD_ARGUMENT;
-  return launch_status();
+    return launch(embed_kernel<float>, num_tokens, threads, 0, stream, tokens, (const float*)table, out, hidden, vocab);
+  if (dtype == TS_DTYPE_BF16)
+    return launch(embed_kernel<bf16>, num_tokens, threads, 0, stream, tokens, (const bf16*)table, out, hidden, vocab);
+  return TS_ERR_BAD_ARGUMENT;
 }
 
 extern "C" int ts_add_rms_norm(float* resid, const void* delta, const void* weight, void* out,
@@ -109,23 +129,23 @@ extern "C" int ts_add_rms_norm(float* resid, const void* delta, const void* weig
                                cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  const int cache_row = hidden <= 8192 ? 1 : 0;
+  const size_t smem = cache_row ? sizeof(float) * hidden : 0;
   if (dtype == TS_DTYPE_F32)
-    add_rms_norm_kernel<float><<<num_rows, threads, 0, stream>>>(resid, (const float*)delta, (const float*)weight,
-                                                                 (float*)out, rows, hidden, eps);
-  else if (dtype == TS_DTYPE_BF16)
-    add_rms_norm_kernel<bf16><<<num_rows, threads, 0, stream>>>(resid, (const bf16*)delta, (const bf16*)weight,
-                                                                (bf16*)out, rows, hidden, eps);
-  else
-    return TS_ERR_BAD_ARGUMENT;
-  return launch_status();
+    return launch(add_rms_norm_kernel<float>, num_rows, threads, smem, stream, resid, (const float*)delta,
+                  (const float*)weight, (float*)out, rows, hidden, eps, cache_row);
+  if (dtype == TS_DTYPE_BF16)
+    return launch(add_rms_norm_kernel<bf16>, num_rows, threads, smem, stream, resid, (const bf16*)delta,
+                  (const bf16*)weight, (bf16*)out, rows, hidden, eps, cache_row);
+  return TS_ERR_BAD_ARGUMENT;
 }
 
 extern "C" int ts_rope_tables(const int* positions, const double* inv_freq, float* cos_out, float* sin_out,
                               int num_tokens, int half, cudaStream_t stream) {
   const int total = num_tokens * half;
   if (total <= 0) return 0;
-  rope_tables_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, cos_out, sin_out, num_tokens, half);
-  return launch_status();
+  return launch(rope_tables_kernel, (total + 255) / 256, 256, 0, stream, positions, inv_freq, cos_out, sin_out,
+                num_tokens, half);
 }
 
 extern "C" int ts_silu_mul(const void* gate_up, void* out, int num_tokens, int inter, int dtype,
@@ -135,10 +155,8 @@ extern "C" int ts_silu_mul(const void* gate_up, void* out, int num_tokens, int i
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (dtype == TS_DTYPE_F32)
-    silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
-  else if (dtype == TS_DTYPE_BF16)
-    silu_mul_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, inter, total);
-  else
-    return TS_ERR_BAD_ARGUMENT;
-  return launch_status();
+    return launch(silu_mul_kernel<float>, (int)blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total);
+  if (dtype == TS_DTYPE_BF16)
+    return launch(silu_mul_kernel<bf16>, (int)blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total);
+  return TS_ERR_BAD_ARGUMENT;
 }

@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(GTHREADS) gemm_simt_kernel(const TIn* __restri
                                                              TOut* __restrict__ out, int M, int N, int K) {
   __shared__ float As[GK][GM + 4];
   __shared__ float Bs[GK][GN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
   const int ty = tid >> 4, tx = tid & 15;
@@ -79,12 +81,10 @@ extern "C" int ts_gemm_simt(const void* x, const void* w, void* out, int M, int 
   if (K <= 0) return TS_ERR_BAD_ARGUMENT;
   dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM);
   if (in_dtype == TS_DTYPE_F32 && out_dtype == TS_DTYPE_F32)
-    gemm_simt_kernel<float, float><<<grid, GTHREADS, 0, stream>>>((const float*)x, (const float*)w, (float*)out, M, N, K);
-  else if (in_dtype == TS_DTYPE_BF16 && out_dtype == TS_DTYPE_BF16)
-    gemm_simt_kernel<bf16, bf16><<<grid, GTHREADS, 0, stream>>>((const bf16*)x, (const bf16*)w, (bf16*)out, M, N, K);
-  else if (in_dtype == TS_DTYPE_BF16 && out_dtype == TS_DTYPE_F32)
-    gemm_simt_kernel<bf16, float><<<grid, GTHREADS, 0, stream>>>((const bf16*)x, (const bf16*)w, (float*)out, M, N, K);
-  else
-    return TS_ERR_BAD_ARGUMENT;
-  return launch_status();
+    return launch(gemm_simt_kernel<float, float>, grid, GTHREADS, 0, stream, (const float*)x, (const float*)w, (float*)out, M, N, K);
+  if (in_dtype == TS_DTYPE_BF16 && out_dtype == TS_DTYPE_BF16)
+    return launch(gemm_simt_kernel<bf16, bf16>, grid, GTHREADS, 0, stream, (const bf16*)x, (const bf16*)w, (bf16*)out, M, N, K);
+  if (in_dtype == TS_DTYPE_BF16 && out_dtype == TS_DTYPE_F32)
+    return launch(gemm_simt_kernel<bf16, float>, grid, GTHREADS, 0, stream, (const bf16*)x, (const bf16*)w, (float*)out, M, N, K);
+  return TS_ERR_BAD_ARGUMENT;
 }

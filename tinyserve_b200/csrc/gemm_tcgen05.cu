@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
 
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * BN;
   const int num_kb = (K + TG_BK - 1) / TG_BK;
@@ -132,6 +133,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  pdl_wait();      // barriers and tensor memory are set up; x may now be read, out written
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer
@@ -244,8 +246,7 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, in
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   dim3 grid((N + BN - 1) / BN, (M + TG_BM - 1) / TG_BM);
-  kern<<<grid, TG_THREADS, smem, stream>>>(mx, mw, out, M, N, K, error_flag);
-  return launch_status();
+  return launch(kern, grid, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag);
 }
 
 }  // namespace ts

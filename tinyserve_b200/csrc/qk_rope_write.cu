@@ -22,6 +22,8 @@ __global__ void qk_norm_rope_write_kernel(
     T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_tokens, int num_heads,
     int num_kv_heads, int head_dim, int write_kv) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* buf = smem + warp * head_dim;
   const int heads_per_token = write_kv ? num_heads + 2 * num_kv_heads : num_heads;
@@ -105,16 +107,14 @@ extern "C" int ts_qk_norm_rope_write(const void* qkv, void* q_out, const void* q
   const int blocks = (int)((items + QK_WARPS - 1) / QK_WARPS);
   const size_t smem = (size_t)QK_WARPS * head_dim * sizeof(float);
   if (dtype == TS_DTYPE_F32)
-    qk_norm_rope_write_kernel<float><<<blocks, QK_WARPS * 32, smem, stream>>>(
+    return launch(qk_norm_rope_write_kernel<float>, blocks, QK_WARPS * 32, smem, stream,
         (const float*)qkv, (float*)q_out, (const float*)q_weight, (const float*)k_weight, eps, cos_t, sin_t,
         rotary_dim, interleaved, slots, (float*)k_cache, (float*)v_cache, page_size, num_tokens, num_heads,
         num_kv_heads, head_dim, write_kv);
-  else if (dtype == TS_DTYPE_BF16)
-    qk_norm_rope_write_kernel<bf16><<<blocks, QK_WARPS * 32, smem, stream>>>(
+  if (dtype == TS_DTYPE_BF16)
+    return launch(qk_norm_rope_write_kernel<bf16>, blocks, QK_WARPS * 32, smem, stream,
         (const bf16*)qkv, (bf16*)q_out, (const bf16*)q_weight, (const bf16*)k_weight, eps, cos_t, sin_t,
         rotary_dim, interleaved, slots, (bf16*)k_cache, (bf16*)v_cache, page_size, num_tokens, num_heads,
         num_kv_heads, head_dim, write_kv);
-  else
-    return TS_ERR_BAD_ARGUMENT;
-  return launch_status();
+  return TS_ERR_BAD_ARGUMENT;
 }

@@ -8,17 +8,27 @@
 // generator (Philox4x32-10) keyed by the request's seed and indexed by (how many tokens the
 // request has drawn, token id), so a request's tokens do not depend on its batch-mates, on
 // chunking or on recomputation; tokens of exactly equal probability are kept or dropped
-// together by top-p; the race is run on log p_i - log E_i, which orders the same way.
+// together by top-p; the race is run on logit / T - log E_i, which orders the same way.
+//
+// A row without top-p is cut into chunks, one CTA each; the CTA that arrives last picks the
+// winner among the chunks' winners. A row with top-p needs sums over the whole row and is done
+// by one CTA.
 #include "common.cuh"
 
 namespace ts {
 
 constexpr int SM_THREADS = 1024;
+constexpr int SM_MAX_ROWS = 4096;
+constexpr int SM_MAX_CHUNKS = 32;
 
 struct Best {
   float v;
   int i;
 };
+// Winners of the chunks, and an arrival counter per row that the last CTA puts back to zero.
+static __device__ Best g_chunk_best[SM_MAX_ROWS * SM_MAX_CHUNKS];
+static __device__ unsigned int g_row_arrivals[SM_MAX_ROWS];
+
 __device__ __forceinline__ Best better(Best a, Best b) {
   if (b.i < 0) return a;
   if (a.i < 0) return b;
@@ -72,10 +82,50 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t
   out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
 
+// exp(logit / T - max) with each step rounded on its own, so that the nucleus threshold found by
+// the search and the later eligibility test see bit-identical values (no fused multiply-add).
+__device__ __forceinline__ float scaled(float logit, float inv_t) { return __fmul_rn(logit, inv_t); }
+__device__ __forceinline__ float weight_of(float logit, float inv_t, float mx) {
+  return expf(__fsub_rn(scaled(logit, inv_t), mx));
+}
+
 // -log(u) with u uniform in (0, 1) on a 24-bit grid: never 0, never infinite.
 __device__ __forceinline__ float exp1_from_bits(uint32_t x) {
   const float u = ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);
   return -logf(u);
+}
+
+// Best candidate of tokens [begin, end) (begin a multiple of 4) for one row.
+// threshold: tokens with exp(z - mx) below it are not eligible (0 = all are).
+__device__ __forceinline__ Best scan_range(const float* __restrict__ l, int begin, int end, float temp,
+                                           float mx, float threshold, uint32_t k0, uint32_t k1, uint32_t d0,
+                                           uint32_t d1) {
+  Best best;
+  best.v = 0.f; best.i = -1;
+  if (!(temp > 0.f)) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      Best c; c.v = l[i]; c.i = i;
+      best = better(best, c);
+    }
+    return best;
+  }
+  const float inv_t = 1.f / temp;
+  for (int i4 = begin / 4 + threadIdx.x; i4 * 4 < end; i4 += blockDim.x) {
+    uint32_t r[4];
+    philox4x32_10((uint32_t)i4, d0, d1, 0u, k0, k1, r);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = i4 * 4 + e;
+      if (i < end) {
+        const float z = scaled(l[i], inv_t);
+        if (threshold <= 0.f || weight_of(l[i], inv_t, mx) >= threshold) {
+          Best c; c.v = z - logf(exp1_from_bits(r[e])); c.i = i;
+          best = better(best, c);
+        }
+      }
+    }
+  }
+  return best;
 }
 
 __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restrict__ logits, int vocab,
@@ -83,69 +133,83 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
                                                             const float* __restrict__ top_p,
                                                             const long long* __restrict__ seeds,
                                                             const long long* __restrict__ draws,
-                                                            int* __restrict__ out) {
+                                                            int* __restrict__ out, int chunks) {
   __shared__ float fscratch[33];
   __shared__ Best bscratch[32];
-  const int row = blockIdx.x;
+  __shared__ int is_last;
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x, chunk = blockIdx.y;
   const float* l = logits + (size_t)row * vocab;
   const float temp = temperature ? temperature[row] : 0.f;
-  Best best;
-  best.v = 0.f; best.i = -1;
-  if (!(temp > 0.f)) {   // greedy
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      Best c; c.v = l[i]; c.i = i;
-      best = better(best, c);
-    }
-    best = block_best(best, bscratch);
-    if (threadIdx.x == 0) out[row] = best.i < 0 ? 0 : best.i;
-    return;
+  const float tp = (top_p && temp > 0.f) ? top_p[row] : 1.f;
+  uint32_t k0 = 0, k1 = 0, d0 = 0, d1 = 0;
+  if (temp > 0.f) {
+    k0 = (uint32_t)(seeds[row] & 0xffffffffll); k1 = (uint32_t)((unsigned long long)seeds[row] >> 32);
+    d0 = (uint32_t)(draws[row] & 0xffffffffll); d1 = (uint32_t)((unsigned long long)draws[row] >> 32);
   }
-  const float inv_t = 1.f / temp;
-  float mx = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, l[i] * inv_t);
-  mx = block_max(mx, fscratch);
 
-  float threshold = 0.f;   // keep tokens with exp(z - mx) >= threshold
-  const float tp = top_p ? top_p[row] : 1.f;
   if (tp < 1.f) {
+    // ---- nucleus: the whole row in the CTA of chunk 0
+    if (chunk != 0) return;
+    const float inv_t = 1.f / temp;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, scaled(l[i], inv_t));
+    mx = block_max(mx, fscratch);
     float z = 0.f;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) z += expf(l[i] * inv_t - mx);
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) z += weight_of(l[i], inv_t, mx);
     z = block_sum(z, fscratch);
     const float target = tp * z;
     // smallest bit pattern b in [0, bits(1.0)] with mass{e > float(b)} < target
-    uint32_t lo = 0u, hi = 0x3f800000u;   // the answer is <= bits(1.0): nothing exceeds 1
+    uint32_t lo = 0u, hi = 0x3f800000u;
     while (lo < hi) {
       const uint32_t mid = lo + ((hi - lo) >> 1);
       const float t = __uint_as_float(mid);
       float mass = 0.f;
       for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float e = expf(l[i] * inv_t - mx);
+        const float e = weight_of(l[i], inv_t, mx);
         if (e > t) mass += e;
       }
       mass = block_sum(mass, fscratch);
       if (mass < target) hi = mid; else lo = mid + 1u;
     }
-    threshold = __uint_as_float(lo);
+    Best best = scan_range(l, 0, vocab, temp, mx, __uint_as_float(lo), k0, k1, d0, d1);
+    best = block_best(best, bscratch);
+    if (threadIdx.x == 0) out[row] = best.i < 0 ? 0 : best.i;
+    return;
   }
-  const uint32_t k0 = (uint32_t)(seeds[row] & 0xffffffffll), k1 = (uint32_t)((unsigned long long)seeds[row] >> 32);
-  const uint32_t d0 = (uint32_t)(draws[row] & 0xffffffffll), d1 = (uint32_t)((unsigned long long)draws[row] >> 32);
-  for (int i4 = threadIdx.x; i4 * 4 < vocab; i4 += blockDim.x) {
-    uint32_t r[4];
-    philox4x32_10((uint32_t)i4, d0, d1, 0u, k0, k1, r);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = i4 * 4 + e;
-      if (i < vocab) {
-        const float zc = l[i] * inv_t - mx;
-        if (expf(zc) >= threshold) {
-          Best c; c.v = zc - logf(exp1_from_bits(r[e])); c.i = i;
-          best = better(best, c);
-        }
-      }
-    }
-  }
+
+  // ---- greedy or temperature only: this CTA's chunk, then the last CTA picks among chunks
+  int per = (vocab + chunks - 1) / chunks;
+  per = (per + 3) & ~3;
+  const int begin = chunk * per, end = min(vocab, begin + per);
+  Best best = scan_range(l, begin, end, temp, 0.f, 0.f, k0, k1, d0, d1);
   best = block_best(best, bscratch);
-  if (threadIdx.x == 0) out[row] = best.i < 0 ? 0 : best.i;
+  if (chunks == 1) {
+    if (threadIdx.x == 0) out[row] = best.i < 0 ? 0 : best.i;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    g_chunk_best[row * SM_MAX_CHUNKS + chunk] = best;
+    __threadfence();
+    const unsigned int old = atomicAdd(&g_row_arrivals[row], 1u);
+    is_last = (old == (unsigned int)chunks - 1u);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    Best b;
+    b.v = 0.f; b.i = -1;
+    for (int c = 0; c < chunks; ++c) {
+      Best o;
+      o.v = __ldcg(&g_chunk_best[row * SM_MAX_CHUNKS + c].v);
+      o.i = __ldcg(&g_chunk_best[row * SM_MAX_CHUNKS + c].i);
+      b = better(b, o);
+    }
+    out[row] = b.i < 0 ? 0 : b.i;
+    g_row_arrivals[row] = 0u;
+  }
 }
 
 }  // namespace ts
@@ -157,8 +221,14 @@ extern "C" int ts_sample(const float* logits, int num_rows, int vocab, const flo
                          const float* top_p, const long long* seeds, const long long* draws, int* out,
                          cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  if (vocab <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (vocab <= 0 || num_rows > SM_MAX_ROWS) return TS_ERR_BAD_ARGUMENT;
   if (temperature != nullptr && (seeds == nullptr || draws == nullptr)) return TS_ERR_BAD_ARGUMENT;
-  sample_kernel<<<num_rows, SM_THREADS, 0, stream>>>(logits, vocab, temperature, top_p, seeds, draws, out);
-  return launch_status();
+  // enough CTAs to fill the machine, each with at least a few thousand tokens
+  int chunks = (148 * 2 + num_rows - 1) / num_rows;
+  const int most = (vocab + 4095) / 4096;
+  if (chunks > most) chunks = most;
+  if (chunks > SM_MAX_CHUNKS) chunks = SM_MAX_CHUNKS;
+  if (chunks < 1) chunks = 1;
+  return launch(sample_kernel, dim3(num_rows, chunks), SM_THREADS, 0, stream, logits, vocab, temperature, top_p,
+                seeds, draws, out, chunks);
 }

@@ -35,8 +35,12 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_paged_attention_simt": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
                                 _f, _i, _i, _vp, _vp, _i, _vp],
     "ts_prefill_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "ts_decode_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
+                                _vp, _vp],
+    "ts_decode_attention_mma_slots": [_i],
     "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -226,6 +230,24 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         num_prefill = 0
         if not ctx.num_decode:
             return
+    if dt == torch.bfloat16 and d <= 128:
+        # decode rows on the tensor cores too: one CTA per (request, kv group, key range)
+        ctas = ctx.num_decode * hkv * (-(-(hq // hkv) // 16))
+        splits = max(1, min(_mma_decode_slots(d) // ctas, ctx.max_context_len // 64, MAX_SPLITS))
+        part_acc = part_ml = None
+        if splits > 1:
+            part_acc = ctx.arena.take((ctx.num_decode, hq, splits, d), torch.float32)
+            part_ml = ctx.arena.take((ctx.num_decode, hq, splits, 2), torch.float32)
+        _check(_fn("ts_decode_attention_mma")(
+            _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+            _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
+            _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+            _dev(ctx.context_lens_dev, "context_lens", torch.int32),
+            _dev(ctx.decode_seqs, "decode_seqs", torch.int32), ctx.num_decode,
+            hq, hkv, d, page_size, float(scale), int(window), splits,
+            _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _error_word(q.device).data_ptr(), _stream()),
+            "decode_attention_mma")
+        return
     splits, part_acc, part_ml = 1, None, None
     if ctx.num_decode:
         splits = decode_splits(ctx.num_decode, hkv, hq // hkv, ctx.max_context_len)
@@ -241,7 +263,17 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
         hq, hkv, d, page_size, float(scale), int(window), splits,
         _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _code(dt), _stream()), "paged_attention",
-        kernels=(1 if num_prefill else 0) + (1 if ctx.num_decode else 0) + (1 if splits > 1 else 0))
+        kernels=(1 if num_prefill else 0) + (1 if ctx.num_decode else 0))
+
+
+_slots_cache: dict[int, int] = {}
+
+
+def _mma_decode_slots(head_dim: int) -> int:
+    n = _slots_cache.get(head_dim)
+    if n is None:
+        n = _slots_cache[head_dim] = int(_fn("ts_decode_attention_mma_slots")(head_dim))
+    return n
 
 
 # ------------------------------------------------------------------------- gemm
@@ -319,6 +351,34 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_n: in
     _check(_fn("ts_gemm_tcgen05")(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), m, n, k, _code(out.dtype),
                                   tile_n or TCGEN05_TILE_N, _error_word(x.device).data_ptr(), _stream()),
            "gemm_tcgen05")
+
+
+def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, arena: Any) -> None:
+    """``out[M, I] = silu(x Wgate^T) * (x Wup^T)`` with ``w_gate_up`` = gate rows then up rows,
+    ``[2 I, K]``. For a few bf16 rows the product and the activation are one kernel (the gate
+    and up rows of an output column are computed by the same CTA); otherwise a product into
+    scratch from ``arena`` followed by the SiLU-multiply kernel."""
+    m, k = x.shape
+    inter = out.shape[1]
+    if tuple(w_gate_up.shape) != (2 * inter, k) or out.shape[0] != m or out.dtype != x.dtype:
+        raise KernelError("gemm_swiglu: shape or dtype mismatch")
+    if x.dtype == torch.bfloat16 and m <= SKINNY_MAX_ROWS and k % 32 == 0 and inter % 16 == 0:
+        _check(_fn("ts_gemm_skinny_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
+                                            _stream()), "gemm_swiglu")
+        return
+    gate_up = arena.take((m, 2 * inter), x.dtype)
+    gemm(x, w_gate_up, gate_up)
+    silu_mul(gate_up, out)
+
+
+def set_programmatic_launch(on: bool) -> None:
+    """Launch this library's kernels so that each may start while its predecessor on the stream
+    is draining (programmatic dependent launch); every kernel waits for its predecessor before
+    it touches data. Off by default."""
+    lib = build.library()
+    lib.ts_set_programmatic_launch.argtypes = [_i]
+    lib.ts_set_programmatic_launch.restype = None
+    lib.ts_set_programmatic_launch(1 if on else 0)
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

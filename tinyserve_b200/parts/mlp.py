@@ -38,10 +38,8 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         t = x.shape[0]
-        gate_up = ctx.arena.take((t, 2 * self.intermediate_size), ctx.dtype)
-        ops.gemm(x, self.w_gate_up, gate_up)
         act = ctx.arena.take((t, self.intermediate_size), ctx.dtype)
-        ops.silu_mul(gate_up, act)
+        ops.gemm_swiglu(x, self.w_gate_up, act, ctx.arena)
         out = ctx.arena.take((t, self.hidden_size), ctx.dtype)
         ops.gemm(act, self.w_down, out)
         return out
