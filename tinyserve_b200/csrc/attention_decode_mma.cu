@@ -135,8 +135,7 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_mma_kernel(AttnArgs a,
     const int kpos = lo_al + tile * DM_TK + row;
     bf16* dst = my_k + (size_t)stage * 2 * TILE_ELEMS + (lane >> 4) * TILE_ELEMS + row * DS;
     if (kpos >= lo && kpos < ctx) {
-      const int page = table[kpos / a.page_size];
-      const size_t off = kv_offset(page, kvh, kpos % a.page_size, a);
+      const size_t off = kv_offset_of(table, kpos, kvh, a);
       dm_bar_arrive_tx(&bars[warp][stage], D * 2u);
       dm_bulk_copy(dst, ((lane >> 4) ? vc : kc) + off, D * 2u, &bars[warp][stage]);
     } else {
@@ -290,33 +289,9 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_mma_kernel(AttnArgs a,
   }
   if (a.num_splits == 1) return;
   // ---- the CTA that arrives last for this (request, heads) merges the ranges
-  __threadfence();
-  __syncthreads();
   unsigned int* counter = &g_dm_arrivals[((size_t)si * gridDim.y + blockIdx.y) % DM_MAX_COUNTERS];
-  if (threadIdx.x == 0) {
-    const unsigned int old = atomicAdd(counter, 1u);
-    is_last = (old == (unsigned int)a.num_splits - 1u);
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  const int S = a.num_splits;
-  for (int idx = threadIdx.x; idx < ng * D; idx += DM_THREADS) {
-    const int r = idx / D, d = idx - r * D;
-    const int head = kvh * G + g0 + r;
-    const size_t pbase = ((size_t)si * a.num_heads + head) * S;
-    float mm = -INFINITY;
-    for (int sp = 0; sp < S; ++sp) mm = fmaxf(mm, __ldcg(&a.part_ml[(pbase + sp) * 2]));
-    float num = 0.f, den = 0.f;
-    for (int sp = 0; sp < S; ++sp) {
-      const float ms = __ldcg(&a.part_ml[(pbase + sp) * 2]);
-      const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-      num += __ldcg(&a.part_acc[(pbase + sp) * D + d]) * c;
-      den += __ldcg(&a.part_ml[(pbase + sp) * 2 + 1]) * c;
-    }
-    ((bf16*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = __float2bfloat16_rn(num / den);
-  }
-  if (threadIdx.x == 0) *counter = 0u;
+  if (!cta_arrives_last(counter, (unsigned int)a.num_splits, &is_last)) return;
+  merge_splits<bf16>(a, si, qrow, kvh * G + g0, ng, red);
 }
 
 template <int D16>
@@ -359,6 +334,7 @@ extern "C" int ts_decode_attention_mma(
   a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
   a.seq_ids = decode_seqs; a.num_seqs = num_decode;
   a.num_heads = num_heads; a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.page_size = page_size;
+  a.page_shift = page_shift_of(page_size);
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.num_splits = num_splits; a.part_acc = part_acc; a.part_ml = part_ml;

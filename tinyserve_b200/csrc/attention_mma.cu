@@ -60,7 +60,9 @@ __global__ void __launch_bounds__(MA_THREADS) prefill_attn_mma_kernel(AttnArgs a
   const int row0 = a.cu_q[seq];
   const int n = a.cu_q[seq + 1] - row0;
   const int tpt = MA_BM / ge;                            // tokens per tile
-  const int q0 = blockIdx.x * tpt;
+  // the tiles with the most keys (the last queries) are launched first, so the partly filled
+  // last round of CTAs is made of the cheapest ones
+  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tpt;
   if (q0 >= n) return;
   const int ctx = a.ctx_lens[seq];
   const int first_pos = ctx - n;
@@ -96,8 +98,7 @@ __global__ void __launch_bounds__(MA_THREADS) prefill_attn_mma_kernel(AttnArgs a
       const int kk = idx / CH, c = idx - kk * CH;
       const int kpos = k0 + kk;
       if (kpos >= k_lo && kpos <= qpos_last) {
-        const int page = table[kpos / a.page_size];
-        const size_t off = kv_offset(page, kvh, kpos % a.page_size, a) + (size_t)c * 8;
+        const size_t off = kv_offset_of(table, kpos, kvh, a) + (size_t)c * 8;
         __pipeline_memcpy_async(kd + kk * DS + c * 8, kc + off, 16);
         __pipeline_memcpy_async(vd + kk * DS + c * 8, vc + off, 16);
       } else {
@@ -132,6 +133,7 @@ __global__ void __launch_bounds__(MA_THREADS) prefill_attn_mma_kernel(AttnArgs a
   const int warp_last_row = min(warp * 16 + 15, nrows - 1);
   const int warp_qpos_max = first_pos + q0 + max(warp_last_row, 0) / ge;
   const bool warp_active = warp * 16 < nrows;
+  const int warp_qpos_min = first_pos + q0 + (warp * 16) / ge;
 
   float o[2 * D16][4];
 #pragma unroll
@@ -167,20 +169,33 @@ __global__ void __launch_bounds__(MA_THREADS) prefill_attn_mma_kernel(AttnArgs a
           mma_16816(s[2 * np + 1], qf[kk], bfr[2], bfr[3]);
         }
       }
-      // ---- scale, mask, online softmax
+      // ---- scale, mask, online softmax. A tile that every row of the warp sees whole needs no
+      //      mask (rows beyond the tile's last have zero queries and finite scores).
       float mx[2] = {-INFINITY, -INFINITY};
+      const bool whole = (k0 + MA_BN - 1 <= warp_qpos_min) && (a.window == 0 || k0 > warp_qpos_max - a.window);
+      if (whole) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int h = e >> 1;
-          const int kpos = k0 + i * 8 + 2 * t + (e & 1);
-          bool ok = rvalid[h] && kpos <= qpos[h];
-          if (a.window > 0) ok = ok && (kpos > qpos[h] - a.window);
-          const float v = ok ? s[i][e] * a.scale_log2 : -INFINITY;
-          s[i][e] = v;
-          mx[h] = fmaxf(mx[h], v);
-        }
+          for (int e = 0; e < 4; ++e) {
+            const float v = s[i][e] * a.scale_log2;
+            s[i][e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+          }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            const int kpos = k0 + i * 8 + 2 * t + (e & 1);
+            bool ok = rvalid[h] && kpos <= qpos[h];
+            if (a.window > 0) ok = ok && (kpos > qpos[h] - a.window);
+            const float v = ok ? s[i][e] * a.scale_log2 : -INFINITY;
+            s[i][e] = v;
+            mx[h] = fmaxf(mx[h], v);
+          }
+      }
       float corr[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -282,6 +297,7 @@ extern "C" int ts_prefill_attention_mma(
   a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
   a.seq_ids = prefill_seqs; a.num_seqs = num_prefill;
   a.num_heads = num_heads; a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.page_size = page_size;
+  a.page_shift = page_shift_of(page_size);
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.num_splits = 1; a.part_acc = nullptr; a.part_ml = nullptr;

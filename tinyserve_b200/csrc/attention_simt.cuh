@@ -90,8 +90,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
       const int kpos = k0 + kk;
       float kf[VEC], vf[VEC];
       if (kpos >= k_lo && kpos <= qpos_last) {
-        const int page = table[kpos / a.page_size];
-        const size_t off = kv_offset(page, kvh, kpos % a.page_size, a) + (size_t)c * VEC;
+        const size_t off = kv_offset_of(table, kpos, kvh, a) + (size_t)c * VEC;
         Vec<T> kv, vv;
         kv.load(kc + off);
         vv.load(vc + off);
@@ -285,10 +284,7 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
       const int kpos = base + u * KPW + sub;
       valid[u] = kpos < k_end;
       size_t off = 0;
-      if (valid[u]) {
-        const int page = table[kpos / a.page_size];
-        off = kv_offset(page, kvh, kpos % a.page_size, a);
-      }
+      if (valid[u]) off = kv_offset_of(table, kpos, kvh, a);
 #pragma unroll
       for (int c = 0; c < CPL; ++c) {
         const int chunk = lk + c * LPK;
@@ -415,35 +411,10 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
   }
   if (a.num_splits == 1) return;
 
-  // ---- the CTA that arrives last for this (request, heads) merges the ranges:
-  //      out = sum_s w_s acc_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
-  __threadfence();
-  __syncthreads();
+  // ---- the CTA that arrives last for this (request, heads) merges the ranges
   unsigned int* counter = &g_decode_counters[((size_t)si * gridDim.y + blockIdx.y) % DC_MAX_COUNTERS];
-  if (threadIdx.x == 0) {
-    const unsigned int old = atomicAdd(counter, 1u);
-    is_last = (old == (unsigned int)a.num_splits - 1u);
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  const int S = a.num_splits;
-  for (int idx = threadIdx.x; idx < ng * D; idx += DC_THREADS) {
-    const int g = idx / D, d = idx - g * D;
-    const int head = kvh * G + g0 + g;
-    const size_t pbase = ((size_t)si * a.num_heads + head) * S;
-    float mm = NEG_INF;
-    for (int sp = 0; sp < S; ++sp) mm = fmaxf(mm, __ldcg(&a.part_ml[(pbase + sp) * 2]));
-    float num = 0.f, den = 0.f;
-    for (int sp = 0; sp < S; ++sp) {
-      const float ms = __ldcg(&a.part_ml[(pbase + sp) * 2]);
-      const float c = (ms == NEG_INF) ? 0.f : exp2f(ms - mm);
-      num += __ldcg(&a.part_acc[(pbase + sp) * D + d]) * c;
-      den += __ldcg(&a.part_ml[(pbase + sp) * 2 + 1]) * c;
-    }
-    ((T*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = from_float<T>(num / den);
-  }
-  if (threadIdx.x == 0) *counter = 0u;
+  if (!cta_arrives_last(counter, (unsigned int)a.num_splits, &is_last)) return;
+  merge_splits<T>(a, si, qrow, kvh * G + g0, ng, smem);
 }
 
 template <typename T, int DJMAX>

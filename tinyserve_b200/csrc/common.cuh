@@ -86,6 +86,24 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return t;
 }
 
+// "The CTA that arrives last does the merge": every CTA of a group calls this after writing its
+// partial results; it returns true in exactly one of them, the last to arrive, after which that
+// CTA may read all partial results (with __ldcg). The barrier orders the CTA's writes before
+// thread 0's release, and thread 0's acquire before the CTA's later reads. The counter is put
+// back to zero by the last arriver, so it never needs clearing between launches.
+__device__ __forceinline__ bool cta_arrives_last(unsigned int* counter, unsigned int group_size, int* flag_in_smem) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int old;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+    const int last = (old == group_size - 1u);
+    if (last) *counter = 0u;
+    *flag_in_smem = last;
+  }
+  __syncthreads();
+  return *flag_in_smem != 0;
+}
+
 static inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return (int)e;

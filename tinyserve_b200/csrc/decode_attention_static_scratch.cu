@@ -60,6 +60,7 @@ extern "C" int ts_decode_attention_static_scratch(const void* q, void* out, cons
   a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
   a.seq_ids = decode_seqs; a.num_seqs = num_decode;
   a.num_heads = num_heads; a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.page_size = page_size;
+  a.page_shift = page_shift_of(page_size);
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.num_splits = num_splits; a.part_acc = nullptr; a.part_ml = nullptr;

@@ -70,6 +70,67 @@ __global__ void add_rms_norm_kernel(float* __restrict__ resid, const T* __restri
   }
 }
 
+// The same with 16-byte accesses on the 32-bit stream and 8-byte (bf16) or 16-byte (float)
+// accesses on the rest: 4 elements per thread and step. Needs hidden % 4 == 0 and the row cache.
+template <typename T>
+__global__ void add_rms_norm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                        const T* __restrict__ weight, T* __restrict__ out,
+                                        const int* __restrict__ rows, int hidden, float eps) {
+  extern __shared__ float xs[];
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* x = resid + (size_t)row * hidden;
+  const T* d = delta ? delta + (size_t)row * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && (d != nullptr);
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(x + i);
+    if (d) {
+      if constexpr (sizeof(T) == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(d + i);
+        v.x += __uint_as_float(raw.x << 16); v.y += __uint_as_float(raw.x & 0xffff0000u);
+        v.z += __uint_as_float(raw.y << 16); v.w += __uint_as_float(raw.y & 0xffff0000u);
+      } else {
+        const float4 dv = *reinterpret_cast<const float4*>(d + i);
+        v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+      }
+    }
+    if (write_back) *reinterpret_cast<float4*>(x + i) = v;
+    *reinterpret_cast<float4*>(xs + i) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(xs + i);
+    const float f[4] = {v.x, v.y, v.z, v.w};
+    float w[4], res[4];
+    if constexpr (sizeof(T) == 2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(weight + i);
+      w[0] = __uint_as_float(raw.x << 16); w[1] = __uint_as_float(raw.x & 0xffff0000u);
+      w[2] = __uint_as_float(raw.y << 16); w[3] = __uint_as_float(raw.y & 0xffff0000u);
+    } else {
+      const float4 wv = *reinterpret_cast<const float4*>(weight + i);
+      w[0] = wv.x; w[1] = wv.y; w[2] = wv.z; w[3] = wv.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) res[e] = round_to<T>(f[e] * rstd) * w[e];
+    if constexpr (sizeof(T) == 2) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(res[0], res[1]), b = __floats2bfloat162_rn(res[2], res[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&a);
+      pk.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(o + i) = pk;
+    } else {
+      *reinterpret_cast<float4*>(o + i) = make_float4(res[0], res[1], res[2], res[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------ rotary tables
 // angle = position * inv_freq in float64; cos and sin in float64, rounded to float32.
 __global__ void rope_tables_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
@@ -105,6 +166,31 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   }
 }
 
+// The same with 16-byte accesses; needs inter to be a multiple of the vector length.
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total_vecs) {
+  constexpr int VEC = Vec<T>::N;
+  pdl_trigger();
+  pdl_wait();
+  const int vecs_per_row = inter / VEC;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total_vecs; idx += stride) {
+    const size_t t = idx / vecs_per_row;
+    const int j = (int)(idx - t * vecs_per_row) * VEC;
+    Vec<T> gv, uv, ov;
+    gv.load(gate_up + t * 2 * inter + j);
+    uv.load(gate_up + t * 2 * inter + inter + j);
+    float g[VEC], u[VEC], o[VEC];
+    gv.unpack(g);
+    uv.unpack(u);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) o[e] = round_to<T>(g[e] / (1.f + expf(-g[e]))) * u[e];
+    ov.pack(o);
+    ov.store(out + t * inter + j);
+  }
+}
+
 }  // namespace ts
 
 using namespace ts;
@@ -131,6 +217,17 @@ extern "C" int ts_add_rms_norm(float* resid, const void* delta, const void* weig
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const int cache_row = hidden <= 8192 ? 1 : 0;
   const size_t smem = cache_row ? sizeof(float) * hidden : 0;
+  const bool aligned = (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+  if (cache_row && hidden % 4 == 0 && aligned) {
+    const int vthreads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+    if (dtype == TS_DTYPE_F32)
+      return launch(add_rms_norm_vec_kernel<float>, num_rows, vthreads, smem, stream, resid, (const float*)delta,
+                    (const float*)weight, (float*)out, rows, hidden, eps);
+    if (dtype == TS_DTYPE_BF16)
+      return launch(add_rms_norm_vec_kernel<bf16>, num_rows, vthreads, smem, stream, resid, (const bf16*)delta,
+                    (const bf16*)weight, (bf16*)out, rows, hidden, eps);
+    return TS_ERR_BAD_ARGUMENT;
+  }
   if (dtype == TS_DTYPE_F32)
     return launch(add_rms_norm_kernel<float>, num_rows, threads, smem, stream, resid, (const float*)delta,
                   (const float*)weight, (float*)out, rows, hidden, eps, cache_row);
@@ -152,6 +249,17 @@ extern "C" int ts_silu_mul(const void* gate_up, void* out, int num_tokens, int i
                            cudaStream_t stream) {
   const size_t total = (size_t)num_tokens * inter;
   if (total == 0) return 0;
+  const int vec = dtype == TS_DTYPE_F32 ? 4 : 8;
+  if (inter % vec == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+    const size_t total_vecs = total / vec;
+    size_t vblocks = (total_vecs + 255) / 256;
+    if (vblocks > 148 * 16) vblocks = 148 * 16;
+    if (dtype == TS_DTYPE_F32)
+      return launch(silu_mul_vec_kernel<float>, (int)vblocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total_vecs);
+    if (dtype == TS_DTYPE_BF16)
+      return launch(silu_mul_vec_kernel<bf16>, (int)vblocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, inter, total_vecs);
+    return TS_ERR_BAD_ARGUMENT;
+  }
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (dtype == TS_DTYPE_F32)

@@ -188,34 +188,32 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
   }
   if (ksplit == 1) return;
   // ---- the CTA of this row tile that arrives last adds the slices in order
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int old = atomicAdd(&g_skinny_arrivals[blockIdx.x], 1u);
-    is_last = (old == (unsigned int)ksplit - 1u);
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
+  if (!cta_arrives_last(&g_skinny_arrivals[blockIdx.x], (unsigned int)ksplit, &is_last)) return;
   for (int idx = threadIdx.x; idx < RT * 16 * COLS; idx += SK_THREADS) {
     const int m = idx / (RT * 16), row = idx - m * (RT * 16);
     if (m < M) {
-      float s = 0.f, u = 0.f;
-      for (int ks = 0; ks < ksplit; ++ks) {
+      float sv[SK_MAX_SPLIT], uv[SK_MAX_SPLIT];
+#pragma unroll
+      for (int ks = 0; ks < SK_MAX_SPLIT; ++ks) {      // independent loads, summed in slice order
         const float* pp = g_skinny_partial + (size_t)ks * SK_SPLIT_MAX_ROWS * width + (size_t)m * width;
-        s += __ldcg(pp + n0 + row);
-        if constexpr (FUSE) u += __ldcg(pp + N + n0 + row);
+        sv[ks] = ks < ksplit ? __ldcg(pp + n0 + row) : 0.f;
+        if constexpr (FUSE) uv[ks] = ks < ksplit ? __ldcg(pp + N + n0 + row) : 0.f;
+      }
+      float s = 0.f, u = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < SK_MAX_SPLIT; ++ks) {
+        s += sv[ks];
+        if constexpr (FUSE) u += uv[ks];
       }
       if constexpr (FUSE) {
-        const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
-        const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
-        out[(size_t)m * N + n0 + row] = from_float<TOut>(sv * uv);
+        const float gv = round_to<bf16>(s), uvv = round_to<bf16>(u);
+        const float act = round_to<bf16>(gv / (1.f + expf(-gv)));
+        out[(size_t)m * N + n0 + row] = from_float<TOut>(act * uvv);
       } else {
         out[(size_t)m * N + n0 + row] = from_float<TOut>(s);
       }
     }
   }
-  if (threadIdx.x == 0) g_skinny_arrivals[blockIdx.x] = 0u;
 }
 
 template <typename TOut, int NT, int RT, bool FUSE>
@@ -231,7 +229,7 @@ static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, 
   const int tiles = N / (16 * RT);
   int ksplit = 1;
   if (M <= SK_SPLIT_MAX_ROWS && (FUSE ? 2 * N : N) <= SK_SPLIT_MAX_COLS && tiles <= SK_MAX_TILES) {
-    while (ksplit < SK_MAX_SPLIT && tiles * ksplit < 148 * 2 && K % (64 * ksplit) == 0 && K / (2 * ksplit) >= SK_KSTEP)
+    while (ksplit < SK_MAX_SPLIT && tiles * ksplit < 148 && K % (64 * ksplit) == 0 && K / (2 * ksplit) >= SK_KSTEP)
       ksplit *= 2;
   }
   return launch(kern, dim3(tiles, ksplit), SK_THREADS, smem, stream, x, w, out, M, N, K);

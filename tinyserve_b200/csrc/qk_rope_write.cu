@@ -90,6 +90,92 @@ __global__ void qk_norm_rope_write_kernel(
   for (int i = rotary_dim + lane; i < head_dim; i += 32) dst[i] = from_float<T>(buf[i]);
 }
 
+
+// Register-only variant for the common case: the whole head is rotated with the "half" pairing
+// (rotary_dim == head_dim, head_dim % 4 == 0). A lane owns pairs p = 2 lane, 2 lane + 1 (+ 64 j):
+// elements p, p + 1 and their partners p + D/2, p + 1 + D/2, each fetched with one access.
+template <typename T, int MAXJ>
+__global__ void qk_norm_rope_write_fast_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, const T* __restrict__ q_weight,
+    const T* __restrict__ k_weight, float eps, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, const int* __restrict__ slots, T* __restrict__ k_cache,
+    T* __restrict__ v_cache, int page_size, int num_tokens, int num_heads, int num_kv_heads, int head_dim,
+    int write_kv) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_per_token = write_kv ? num_heads + 2 * num_kv_heads : num_heads;
+  const long long item = (long long)blockIdx.x * QK_WARPS + warp;
+  if (item >= (long long)num_tokens * heads_per_token) return;
+  const int t = (int)(item / heads_per_token);
+  const int h = (int)(item - (long long)t * heads_per_token);
+  const T* src = qkv + ((size_t)t * heads_per_token + h) * head_dim;
+  T* dst;
+  const T* weight = nullptr;
+  if (h < num_heads) {
+    dst = q_out + ((size_t)t * num_heads + h) * head_dim;
+    weight = q_weight;
+  } else {
+    const int slot = slots[t];
+    const int page = slot / page_size, off = slot - page * page_size;
+    const bool is_k = h < num_heads + num_kv_heads;
+    const int kvh = is_k ? h - num_heads : h - num_heads - num_kv_heads;
+    dst = (is_k ? k_cache : v_cache) + (((size_t)page * num_kv_heads + kvh) * page_size + off) * head_dim;
+    if (!is_k) {
+      constexpr int VEC = Vec<T>::N;
+      for (int i = lane * VEC; i < head_dim; i += 32 * VEC) {
+        Vec<T> v;
+        v.load(src + i);
+        v.store(dst + i);
+      }
+      return;
+    }
+    weight = k_weight;
+  }
+  const int half = head_dim >> 1;
+  float a[MAXJ][2], b[MAXJ][2];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXJ; ++j) {
+    const int p = 2 * lane + 64 * j;
+    a[j][0] = a[j][1] = b[j][0] = b[j][1] = 0.f;
+    if (p < half) {
+      a[j][0] = to_float(src[p]); a[j][1] = to_float(src[p + 1]);
+      b[j][0] = to_float(src[half + p]); b[j][1] = to_float(src[half + p + 1]);
+      ss += a[j][0] * a[j][0] + a[j][1] * a[j][1] + b[j][0] * b[j][0] + b[j][1] * b[j][1];
+    }
+  }
+  if (weight != nullptr) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)head_dim + eps);
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const int p = 2 * lane + 64 * j;
+      if (p < half) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          a[j][e] = round_to<T>(round_to<T>(a[j][e] * rstd) * to_float(weight[p + e]));
+          b[j][e] = round_to<T>(round_to<T>(b[j][e] * rstd) * to_float(weight[half + p + e]));
+        }
+      }
+    }
+  }
+  const float* c = cos_t + (size_t)t * half;
+  const float* s = sin_t + (size_t)t * half;
+#pragma unroll
+  for (int j = 0; j < MAXJ; ++j) {
+    const int p = 2 * lane + 64 * j;
+    if (p < half) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float cv = c[p + e], sv = s[p + e];
+        dst[p + e] = from_float<T>(a[j][e] * cv - b[j][e] * sv);
+        dst[half + p + e] = from_float<T>(b[j][e] * cv + a[j][e] * sv);
+      }
+    }
+  }
+}
+
 }  // namespace ts
 
 using namespace ts;
@@ -106,6 +192,20 @@ extern "C" int ts_qk_norm_rope_write(const void* qkv, void* q_out, const void* q
   const long long items = (long long)num_tokens * heads_per_token;
   const int blocks = (int)((items + QK_WARPS - 1) / QK_WARPS);
   const size_t smem = (size_t)QK_WARPS * head_dim * sizeof(float);
+  if (rotary_dim == head_dim && !interleaved && head_dim % 8 == 0 && head_dim <= 256 &&
+      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0) {
+    if (dtype == TS_DTYPE_F32)
+      return launch(qk_norm_rope_write_fast_kernel<float, 2>, blocks, QK_WARPS * 32, 0, stream,
+                    (const float*)qkv, (float*)q_out, (const float*)q_weight, (const float*)k_weight, eps, cos_t,
+                    sin_t, slots, (float*)k_cache, (float*)v_cache, page_size, num_tokens, num_heads, num_kv_heads,
+                    head_dim, write_kv);
+    if (dtype == TS_DTYPE_BF16)
+      return launch(qk_norm_rope_write_fast_kernel<bf16, 2>, blocks, QK_WARPS * 32, 0, stream,
+                    (const bf16*)qkv, (bf16*)q_out, (const bf16*)q_weight, (const bf16*)k_weight, eps, cos_t,
+                    sin_t, slots, (bf16*)k_cache, (bf16*)v_cache, page_size, num_tokens, num_heads, num_kv_heads,
+                    head_dim, write_kv);
+    return TS_ERR_BAD_ARGUMENT;
+  }
   if (dtype == TS_DTYPE_F32)
     return launch(qk_norm_rope_write_kernel<float>, blocks, QK_WARPS * 32, smem, stream,
         (const float*)qkv, (float*)q_out, (const float*)q_weight, (const float*)k_weight, eps, cos_t, sin_t,

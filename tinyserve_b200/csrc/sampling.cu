@@ -189,26 +189,24 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
     if (threadIdx.x == 0) out[row] = best.i < 0 ? 0 : best.i;
     return;
   }
-  if (threadIdx.x == 0) {
-    g_chunk_best[row * SM_MAX_CHUNKS + chunk] = best;
-    __threadfence();
-    const unsigned int old = atomicAdd(&g_row_arrivals[row], 1u);
-    is_last = (old == (unsigned int)chunks - 1u);
-  }
-  __syncthreads();
-  if (!is_last) return;
-  if (threadIdx.x == 0) {
-    __threadfence();
+  if (threadIdx.x == 0) g_chunk_best[row * SM_MAX_CHUNKS + chunk] = best;
+  if (!cta_arrives_last(&g_row_arrivals[row], (unsigned int)chunks, &is_last)) return;
+  if (threadIdx.x < 32) {
+    // one lane per chunk (chunks <= 32): independent loads, then a warp reduction
     Best b;
     b.v = 0.f; b.i = -1;
-    for (int c = 0; c < chunks; ++c) {
-      Best o;
-      o.v = __ldcg(&g_chunk_best[row * SM_MAX_CHUNKS + c].v);
-      o.i = __ldcg(&g_chunk_best[row * SM_MAX_CHUNKS + c].i);
-      b = better(b, o);
+    if ((int)threadIdx.x < chunks) {
+      b.v = __ldcg(&g_chunk_best[row * SM_MAX_CHUNKS + threadIdx.x].v);
+      b.i = __ldcg(&g_chunk_best[row * SM_MAX_CHUNKS + threadIdx.x].i);
     }
-    out[row] = b.i < 0 ? 0 : b.i;
-    g_row_arrivals[row] = 0u;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best y;
+      y.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+      y.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+      b = better(b, y);
+    }
+    if (threadIdx.x == 0) out[row] = b.i < 0 ? 0 : b.i;
   }
 }
 

@@ -196,6 +196,23 @@ def decode_splits(num_decode: int, num_kv_heads: int, group: int, max_context_le
     return max(1, min(want, most, MAX_SPLITS))
 
 
+def choose_splits(ctas: int, slots: int, most: int) -> int:
+    """Key ranges per request for a kernel of which ``slots`` CTAs run at once and that would
+    launch ``ctas`` CTAs unsplit: few CTAs are cut until they fill the machine; many CTAs are
+    cut so that the last, partly filled round of CTAs costs little. Depends only on the shape of
+    the step, so a recorded step always replays the same grid."""
+    most = max(1, min(most, MAX_SPLITS))
+    if ctas * 2 <= slots:
+        return max(1, min(slots // ctas, most))
+    best, best_cost = 1, float("inf")
+    for s in range(1, min(most, 8) + 1):
+        rounds = -(-ctas * s // slots)
+        cost = rounds / s + 0.03 * s          # time in units of an unsplit CTA, plus merge work
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                     block_tables: torch.Tensor, ctx: Any, scale: float, window: int, out: torch.Tensor) -> None:
     """Causal attention of this step's queries over each request's cached keys and values.
@@ -233,7 +250,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if dt == torch.bfloat16 and d <= 128:
         # decode rows on the tensor cores too: one CTA per (request, kv group, key range)
         ctas = ctx.num_decode * hkv * (-(-(hq // hkv) // 16))
-        splits = max(1, min(_mma_decode_slots(d) // ctas, ctx.max_context_len // 64, MAX_SPLITS))
+        splits = choose_splits(ctas, _mma_decode_slots(d), ctx.max_context_len // 64)
         part_acc = part_ml = None
         if splits > 1:
             part_acc = ctx.arena.take((ctx.num_decode, hq, splits, d), torch.float32)
