@@ -112,6 +112,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between kernels")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                    help="run a small case kernel by kernel between cudaProfilerStart/Stop and exit "
+                         "(for ncu --profile-from-start off); combine with --layers, --batch")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -214,6 +217,33 @@ def main() -> int:
         h2d = 4 * (batch * (8 + width) + 16)
         return ms, h2d, 4 * batch
 
+    if args.profile:
+        # A small, eager case for a profiler: nothing is timed and no JSON line is printed.
+        args.no_graphs = True
+        if args.profile == "decode":
+            e = prefilled(args.batch, 8)
+            for _ in range(2):
+                e.step()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            for _ in range(2):
+                e.step()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        else:
+            e = new_engine(1, 2048 + 8)
+            toks = prompts(1, 2048)[0]
+            for it in range(3):
+                req = e.cache.new_request()
+                e.cache.append(req, 2048)
+                if it == 2:
+                    torch.cuda.profiler.start()
+                e.runner.step([StepEntry(req, toks)])
+                torch.cuda.synchronize()
+                e.cache.free(req)
+            torch.cuda.profiler.stop()
+        print(f"profiled {args.profile}: batch {args.batch}, layers {cfg.num_layers}")
+        return 0
     sampler = ClockSampler()
     sampler.start()
     ms, ctx, launches = device_decode(args.batch, args.warmup, args.steps)

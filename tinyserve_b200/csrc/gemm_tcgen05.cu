@@ -4,14 +4,16 @@
 // accumulator. The library product that this replaces is upstream's F.linear
 // (src/tinyserve/model.py:156,173,178-179,208).
 //
-// One CTA computes a 128 x BN tile. Both operands are K-major in memory ([rows, K] row-major),
+// A CTA computes 128 x BN tiles, one after the other. Both operands are K-major in memory ([rows, K] row-major),
 // which is the layout the instruction wants, so a stage is two TMA boxes: 128 rows x 64 k of x
 // and BN rows x 64 k of w. Out-of-range rows and the K tail read as zeros (TMA fill), so any
 // M, N and any K that is a multiple of 8 (16-byte row pitch) are taken.
 //   warp 0, one lane : TMA producer        (waits "empty", arms "full" with the byte count)
 //   warp 1, one lane : MMA issuer          (waits "full", 4 x tcgen05.mma of K = 16 per stage,
-//                                           tcgen05.commit frees the stage; last commit -> "done")
-//   warps 0-3        : epilogue            (tcgen05.ld of the warp's 32 TMEM lanes, cast, store)
+//                                           tcgen05.commit frees the stage; last commit of a tile
+//                                           marks its accumulator "full")
+//   warps 2-5        : epilogue            (tcgen05.ld of the warp's 32 TMEM lanes, cast, store,
+//                                           then the accumulator buffer is handed back)
 // Every wait on an mbarrier is bounded: when the bound is hit the kernel records it in
 // *error_flag, stops waiting and still frees its tensor memory, so a fault in the pipeline
 // shows as an error code on the host and never as a hang.
@@ -23,13 +25,16 @@ namespace ts {
 
 constexpr int TG_BM = 128;
 constexpr int TG_BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
-constexpr int TG_THREADS = 128;
+constexpr int TG_THREADS = 192;     // TMA warp, MMA warp, four epilogue warps
 constexpr long long TG_WAIT_CYCLES = 2000000000ll;   // about a second: far beyond any real wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -101,6 +106,10 @@ __device__ __forceinline__ uint64_t sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Persistent, warp-specialised: a CTA loops over output tiles (tile = blockIdx.x + i * gridDim.x,
+// rows fastest, so CTAs that run together share weight tiles in L2). The accumulator is double-
+// buffered in tensor memory (2 x BN columns): while the four epilogue warps drain tile i, the
+// MMA warp already accumulates tile i + 1.
 template <int BN, int STAGES, typename TOut>
 __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
@@ -109,103 +118,130 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
   constexpr uint32_t A_BYTES = TG_BM * TG_BK * 2, B_BYTES = BN * TG_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   // instruction descriptor: D = f32, A = B = bf16, both K-major, N = BN, M = 128
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = 2 * BN;      // a power of two >= 32: BN in {64, 128, 256}
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
-  __shared__ __align__(8) uint64_t done_bar;
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TG_BM, n0 = blockIdx.x * BN;
+  const int tiles_m = (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + TG_BK - 1) / TG_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(&done_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(&tmem_base_slot, BN);
+  if (warp == 1) tmem_alloc(&tmem_base_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   pdl_wait();      // barriers and tensor memory are set up; x may now be read, out written
 
-  if (warp == 0 && lane == 0) {
-    // ---------------- TMA producer
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t phase = (kb / STAGES) & 1;
-      if (!mbar_wait(&empty_bar[s], phase ^ 1)) { failed = 1; break; }
-      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-      unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
-      tma_load_2d(a, &map_x, &full_bar[s], kb * TG_BK, m0);
-      tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
-    }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- MMA issuer
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t phase = (kb / STAGES) & 1;
-      if (!mbar_wait(&full_bar[s], phase)) { failed = 1; break; }
-      tc_fence_after();
-      const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-      const uint64_t adesc = sw128_desc(a_addr), bdesc = sw128_desc(a_addr + A_BYTES);
-#pragma unroll
-      for (int k = 0; k < TG_BK / 16; ++k) {
-        // 16 k = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
-        umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
-      }
-      umma_commit(&empty_bar[s]);     // the stage is free once these MMAs have read it
-    }
-    umma_commit(&done_bar);           // the accumulator is complete once every MMA has finished
-  }
-  __syncwarp();
-
-  // ---------------- epilogue: warp w owns TMEM lanes 32 w .. 32 w + 31 = rows m0 + 32 w + lane
-  bool ok = mbar_wait(&done_bar, 0);
-  tc_fence_after();
-  if (!ok || failed) {
-    if (lane == 0) atomicExch(error_flag, 1);
-  } else {
-    const int row = m0 + warp * 32 + lane;
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
-      if (row < M) {
-        TOut* dst = out + (size_t)row * N + n0 + c * 32;
-        if (n0 + c * 32 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
-          if constexpr (sizeof(TOut) == 2) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float f[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]);
-              Vec<bf16> v;
-              v.pack(f);
-              v.store((bf16*)dst + j);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>((float*)dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                      __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-          }
-        } else {
-          for (int j = 0; j < 32; ++j)
-            if (n0 + c * 32 + j < N) dst[j] = from_float<TOut>(__uint_as_float(r[j]));
+  if (warp == 0) {
+    // ---------------- TMA producer (one lane)
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], phase ^ 1)) { failed = 1; break; }
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
+          tma_load_2d(a, &map_x, &full_bar[s], kb * TG_BK, m0);
+          tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
         }
       }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (one lane)
+    if (lane == 0) {
+      int it = 0, t = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x, ++t) {
+        const int b = t & 1;
+        // the epilogue must have drained this accumulator (two tiles ago)
+        if (!mbar_wait(&acc_empty[b], ((t >> 1) & 1) ^ 1)) { failed = 1; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], phase)) { failed = 1; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const uint64_t adesc = sw128_desc(a_addr), bdesc = sw128_desc(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TG_BK / 16; ++k) {
+            // 16 k = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
+            umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[s]);   // the stage is free once these MMAs have read it
+        }
+        umma_commit(&acc_full[b]);      // the accumulator is complete once every MMA has finished
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5; warp w may touch TMEM lanes 32 (w % 4) .. + 31
+    const int quad = warp & 3;
+    int t = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int b = t & 1;
+      const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+      if (!mbar_wait(&acc_full[b], (t >> 1) & 1) || failed) {
+        if (lane == 0) atomicExch(error_flag, 1);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN + c * 32), r);
+        if (row < M) {
+          TOut* dst = out + (size_t)row * N + n0 + c * 32;
+          if (n0 + c * 32 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+            if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]);
+                Vec<bf16> v;
+                v.pack(f);
+                v.store((bf16*)dst + j);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>((float*)dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                        __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c * 32 + j < N) dst[j] = from_float<TOut>(__uint_as_float(r[j]));
+          }
+        }
+      }
+      // this warp has read its part of the accumulator: hand the buffer back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, BN);
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // ---------------------------------------------------------------- host side
@@ -245,8 +281,9 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, in
   auto kern = gemm_tcgen05_kernel<BN, STAGES, TOut>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((N + BN - 1) / BN, (M + TG_BM - 1) / TG_BM);
-  return launch(kern, grid, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag);
+  const int num_tiles = ((N + BN - 1) / BN) * ((M + TG_BM - 1) / TG_BM);
+  const int ctas = num_tiles < 148 ? num_tiles : 148;     // one persistent CTA per SM
+  return launch(kern, ctas, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag);
 }
 
 }  // namespace ts
@@ -267,8 +304,8 @@ extern "C" int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, i
 #define TS_TC(BN_, ST_)                                                                               \
   return f32 ? launch_tc<BN_, ST_, float>(mx, mw, (float*)out, M, N, K, error_flag, stream)           \
              : launch_tc<BN_, ST_, bf16>(mx, mw, (bf16*)out, M, N, K, error_flag, stream)
-  if (tile_n == 64) { TS_TC(64, 4); }
-  if (tile_n == 128) { TS_TC(128, 3); }
+  if (tile_n == 64) { TS_TC(64, 6); }
+  if (tile_n == 128) { TS_TC(128, 6); }
   TS_TC(256, 4);
 #undef TS_TC
 }
