@@ -207,7 +207,7 @@ def choose_splits(ctas: int, slots: int, most: int) -> int:
     best, best_cost = 1, float("inf")
     for s in range(1, min(most, 8) + 1):
         rounds = -(-ctas * s // slots)
-        cost = rounds / s + 0.03 * s          # time in units of an unsplit CTA, plus merge work
+        cost = rounds / s + 0.08 * s          # time in units of an unsplit CTA, plus per-CTA overhead
         if cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
