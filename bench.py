@@ -33,6 +33,12 @@ QWEN3_0_6B = {
     "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
     "max_position_embeddings": 4096, "tie_word_embeddings": True, "hidden_act": "silu",
 }
+# BASELINE configs[3] and configs[4]: the Qwen3-8B and Qwen3-32B layer sizes (untied heads).
+QWEN3_8B = {**QWEN3_0_6B, "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 36,
+            "num_attention_heads": 32, "num_key_value_heads": 8, "tie_word_embeddings": False}
+QWEN3_32B = {**QWEN3_0_6B, "hidden_size": 5120, "intermediate_size": 25600, "num_hidden_layers": 64,
+             "num_attention_heads": 64, "num_key_value_heads": 8, "tie_word_embeddings": False}
+MODELS = {"0.6b": QWEN3_0_6B, "8b": QWEN3_8B, "32b": QWEN3_32B}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -107,6 +113,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--model", choices=sorted(MODELS), default="0.6b",
+                    help="layer sizes: the headline configuration (0.6b) or the larger BASELINE ones")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
@@ -135,7 +143,7 @@ def main() -> int:
     from tinyserve_b200.model import DecoderModel
 
     ops.set_programmatic_launch(not args.no_pdl)
-    cfg_dict = dict(QWEN3_0_6B)
+    cfg_dict = dict(MODELS[args.model])
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
@@ -253,17 +261,18 @@ def main() -> int:
     achieved = decode_bytes(args.batch, ctx) / (ms * 1e-3) / 1e9
 
     result = {
-        "metric": "decode tok/s at batch 8 (Qwen3-0.6B sizes, bf16, 1,024-token prompts)",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.model.upper()} sizes, bf16, "
+                  f"{args.prompt_len:,}-token prompts)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic token ids, random-init weights", "impl": "ours",
         "config": {
-            "model": "Qwen3-0.6B sizes", "layers": cfg.num_layers, "layers_of_configuration": full_layers,
+            "model": f"Qwen3-{args.model.upper()} sizes", "layers": cfg.num_layers, "layers_of_configuration": full_layers,
             "hidden": cfg.hidden_size, "q_heads": cfg.num_heads, "kv_heads": cfg.num_kv_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "tied_embeddings": cfg.tie_word_embeddings, "global_batch": args.batch, "seq_len": args.prompt_len,
             "context_limit": cfg.max_position_embeddings, "mean_context": round(ctx, 1), "page_size": page,
-            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 1.19 GB read every step)",
+            "parallelism": "single GPU", "l2": f"inputs larger than L2 (weights {model.weight_bytes() / 1e9:.2f} GB read every step)",
             "peaks": pk_src,
         },
         "e2e": {"value": round(args.batch * 1e3 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),

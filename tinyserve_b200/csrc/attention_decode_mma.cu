@@ -17,7 +17,10 @@
 
 namespace ts {
 
-constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_TK = 16, DM_STAGES = 2;
+#ifndef DM_STAGES_N
+#define DM_STAGES_N 2
+#endif
+constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_TK = 16, DM_STAGES = DM_STAGES_N;
 constexpr int DM_MAX_COUNTERS = 1 << 16;
 constexpr long long DM_WAIT_CYCLES = 2000000000ll;
 

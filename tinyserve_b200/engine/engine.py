@@ -144,7 +144,7 @@ class Engine:
         entries, want = [], []
         for r in reqs:
             end = r.cache.num_tokens
-            toks = r.tokens[end - r.num_scheduled: end]
+            toks = r.token_slice(end - r.num_scheduled, end)
             entries.append(StepEntry(r.cache, toks))
             want.append([] if r.in_prefill() else [len(toks) - 1])
         context = sum(r.cache.num_tokens for r in reqs)

@@ -45,6 +45,15 @@ class Request:
     def tokens(self) -> list[int]:
         return self.prompt + self.output
 
+    def token_slice(self, start: int, end: int) -> list[int]:
+        """``tokens[start:end]`` without building the whole list (a decode step needs one token)."""
+        n = len(self.prompt)
+        if end <= n:
+            return self.prompt[start:end]
+        if start >= n:
+            return self.output[start - n: end - n]
+        return self.prompt[start:] + self.output[: end - n]
+
     @property
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.output)
