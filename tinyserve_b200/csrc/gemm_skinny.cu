@@ -28,7 +28,6 @@ namespace ts {
 
 constexpr int SK_WARPS = 8;
 constexpr int SK_THREADS = SK_WARPS * 32;
-constexpr int SK_PF = 4;                   // k blocks of a warp whose weights are in flight
 constexpr int SK_KSTEP = SK_WARPS * 32;    // distance between a warp's k blocks
 constexpr int SK_MAX_SPLIT = 8;
 constexpr int SK_SPLIT_MAX_ROWS = 16;      // K is split across CTAs only for M up to this
@@ -60,9 +59,10 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// NT = column tiles of 8 rows of x (M <= 8 * NT); RT = weight row tiles of 16 per CTA;
+// NT = column tiles of 8 rows of x (M <= 8 * NT); RT = weight row tiles of 16 per CTA (each x
+// fragment is used for all of them); SK_PF = k blocks of a warp whose weights are in flight;
 // FUSE: w holds 2 N rows (gate rows, then up rows) and out = silu(gate) * up, [M, N].
-template <typename TOut, int NT, int RT, bool FUSE>
+template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool XRING>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                  TOut* __restrict__ out, int M, int N, int K) {
   constexpr int TILES = FUSE ? 2 * RT : RT;
@@ -115,6 +115,19 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
     xok[j] = m < M;
     xrow[j] = x + (size_t)(xok[j] ? m : 0) * K + 8 * t;
   }
+  // XRING: the fragments of x are fetched as far ahead as the weights. Chosen when a warp has so
+  // few k blocks that all its loads go out at once and nothing later waits for L2; with long
+  // loops the extra registers would cost more in occupancy than the prefetch gains.
+  uint4 xring[XRING ? SK_PF : 1][NT];
+  if constexpr (XRING) {
+#pragma unroll
+    for (int p = 0; p < SK_PF; ++p) {
+      const int kb = k_lo + warp * 32 + p * SK_KSTEP;
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+        xring[p][j] = (kb < k_hi && xok[j]) ? ld_cached(xrow[j] + kb) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
 
   for (int kb0 = k_lo + warp * 32; kb0 < k_hi; kb0 += SK_PF * SK_KSTEP) {
 #pragma unroll
@@ -126,13 +139,20 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
         for (int r = 0; r < TILES; ++r) { a[r][0] = ring[p][r][0]; a[r][1] = ring[p][r][1]; }
         uint4 b[NT];
 #pragma unroll
-        for (int j = 0; j < NT; ++j) b[j] = xok[j] ? ld_cached(xrow[j] + kb) : make_uint4(0u, 0u, 0u, 0u);
+        for (int j = 0; j < NT; ++j) {
+          if constexpr (XRING) b[j] = xring[p][j];
+          else b[j] = xok[j] ? ld_cached(xrow[j] + kb) : make_uint4(0u, 0u, 0u, 0u);
+        }
         const int nxt = kb + SK_PF * SK_KSTEP;
         if (nxt < k_hi) {
 #pragma unroll
           for (int r = 0; r < TILES; ++r) {
             ring[p][r][0] = ld_stream(wrow[r][0] + nxt);
             ring[p][r][1] = ld_stream(wrow[r][1] + nxt);
+          }
+          if constexpr (XRING) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) xring[p][j] = xok[j] ? ld_cached(xrow[j] + nxt) : make_uint4(0u, 0u, 0u, 0u);
           }
         }
 #pragma unroll
@@ -216,15 +236,10 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
   }
 }
 
-template <typename TOut, int NT, int RT, bool FUSE>
+template <typename TOut, int NT, int RT, bool FUSE, int SK_PF>
 static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
   constexpr int TILES = FUSE ? 2 * RT : RT;
   const size_t smem = sizeof(float) * SK_WARPS * TILES * 16 * 8 * NT;
-  auto kern = gemm_skinny_kernel<TOut, NT, RT, FUSE>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
   // Split K across CTAs when the row tiles alone leave most SMs idle.
   const int tiles = N / (16 * RT);
   int ksplit = 1;
@@ -232,21 +247,45 @@ static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, 
     while (ksplit < SK_MAX_SPLIT && tiles * ksplit < 148 && K % (64 * ksplit) == 0 && K / (2 * ksplit) >= SK_KSTEP)
       ksplit *= 2;
   }
+  constexpr bool CAN_RING = (!FUSE && RT == 1 && NT == 1);
+  const bool ring = CAN_RING && K / ksplit <= SK_PF * SK_KSTEP;
+  void (*kern)(const bf16*, const bf16*, TOut*, int, int, int) = gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_PF, false>;
+  if constexpr (CAN_RING) {
+    if (ring) kern = gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_PF, true>;
+  }
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
   return launch(kern, dim3(tiles, ksplit), SK_THREADS, smem, stream, x, w, out, M, N, K);
+}
+
+// Weight row tiles per CTA: as many as still leave every SM a CTA (more tiles = each fragment of
+// x is reused more often and less of L2's bandwidth goes to x).
+static int row_tiles_for(int N, int most) {
+  int rt = 1;
+  while (rt * 2 <= most && N % (32 * rt) == 0 && N / (32 * rt) >= 148 * 4) rt *= 2;
+  return rt;
+}
+
+template <typename TOut, int NT>
+static int dispatch_skinny_nt(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
+  const int rt = row_tiles_for(N, 2);
+  if (rt == 2) return launch_skinny<TOut, NT, 2, false, 4>(x, w, out, M, N, K, stream);
+  return launch_skinny<TOut, NT, 1, false, 4>(x, w, out, M, N, K, stream);
 }
 
 template <typename TOut>
 static int dispatch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
-  // Two row tiles per CTA when that still leaves enough CTAs to fill the machine.
-  const bool two = (N % 32 == 0) && (N / 32 >= 148 * 4);
-#define TS_SKINNY(NT_)                                                                        \
-  return two ? launch_skinny<TOut, NT_, 2, false>(x, w, out, M, N, K, stream)                 \
-             : launch_skinny<TOut, NT_, 1, false>(x, w, out, M, N, K, stream)
-  if (M <= 8) { TS_SKINNY(1); }
-  if (M <= 16) { TS_SKINNY(2); }
-  if (M <= 32) { TS_SKINNY(4); }
-  TS_SKINNY(8);
-#undef TS_SKINNY
+  if (M <= 8) return dispatch_skinny_nt<TOut, 1>(x, w, out, M, N, K, stream);
+  if (M <= 16) return dispatch_skinny_nt<TOut, 2>(x, w, out, M, N, K, stream);
+  if (M <= 32) return dispatch_skinny_nt<TOut, 4>(x, w, out, M, N, K, stream);
+  return dispatch_skinny_nt<TOut, 8>(x, w, out, M, N, K, stream);
+}
+
+template <int NT>
+static int dispatch_swiglu_nt(const bf16* x, const bf16* w, bf16* out, int M, int inter, int K, cudaStream_t stream) {
+  return launch_skinny<bf16, NT, 1, true, 4>(x, w, out, M, inter, K, stream);
 }
 
 }  // namespace ts
@@ -276,7 +315,7 @@ extern "C" int ts_gemm_skinny_swiglu(const void* x, const void* w, void* out, in
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)w;
   bf16* op = (bf16*)out;
-  if (M <= 8) return launch_skinny<bf16, 1, 1, true>(xp, wp, op, M, inter, K, stream);
-  if (M <= 16) return launch_skinny<bf16, 2, 1, true>(xp, wp, op, M, inter, K, stream);
-  return launch_skinny<bf16, 4, 1, true>(xp, wp, op, M, inter, K, stream);
+  if (M <= 8) return dispatch_swiglu_nt<1>(xp, wp, op, M, inter, K, stream);
+  if (M <= 16) return dispatch_swiglu_nt<2>(xp, wp, op, M, inter, K, stream);
+  return dispatch_swiglu_nt<4>(xp, wp, op, M, inter, K, stream);
 }

@@ -310,7 +310,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _check(_fn("ts_gemm_simt")(_dev(x, "x"), _dev(w, "w"), _dev(out, "out"), m, n, k, _F32, _F32, _stream()),
                "gemm")
         return
-    if m <= SKINNY_MAX_ROWS and k % 32 == 0 and n % 16 == 0:
+    if m <= SKINNY_MAX_ROWS and k % 32 == 0 and n % 16 == 0 and (n * k <= SKINNY_MAX_WEIGHTS or out.dtype != x.dtype):
         gemm_skinny(x, w, out)
         return
     if m >= TCGEN05_MIN_ROWS and n >= TCGEN05_MIN_COLS and k % 8 == 0:
@@ -323,8 +323,12 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
 
 
-# Up to this many rows a bf16 product streams the weights through the skinny kernel.
+# Up to this many rows a bf16 product streams the weights through the skinny kernel ...
 SKINNY_MAX_ROWS = 16
+# ... if the matrix is not larger than this (measured on B200: at the Qwen3-8B and 32B layer
+# shapes the vendor library streams 15-35% faster; at the 0.6B shapes and for the output head
+# the skinny kernel is level or ahead).
+SKINNY_MAX_WEIGHTS = 1 << 24
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -388,7 +392,8 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
     inter = out.shape[1]
     if tuple(w_gate_up.shape) != (2 * inter, k) or out.shape[0] != m or out.dtype != x.dtype:
         raise KernelError("gemm_swiglu: shape or dtype mismatch")
-    if x.dtype == torch.bfloat16 and m <= SKINNY_MAX_ROWS and k % 32 == 0 and inter % 16 == 0:
+    if (x.dtype == torch.bfloat16 and m <= SKINNY_MAX_ROWS and k % 32 == 0 and inter % 16 == 0
+            and 2 * inter * k <= SKINNY_MAX_WEIGHTS):
         _check(_fn("ts_gemm_skinny_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
                                             _stream()), "gemm_swiglu")
         return
