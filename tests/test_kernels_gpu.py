@@ -170,7 +170,7 @@ def _attention_case(dtype, hq, hkv, d, page, lens, window, seed=0, scale=None, s
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hkv,d,page", [
     (4, 2, 16, 16), (4, 1, 32, 8), (3, 3, 48, 32), (16, 8, 128, 16), (8, 1, 64, 16), (12, 2, 80, 4),
-    (2, 1, 256, 16), (5, 5, 128, 64),
+    (2, 1, 256, 16), (5, 5, 128, 64), (4, 2, 64, 8), (6, 3, 128, 8), (8, 2, 128, 32), (32, 2, 64, 48),
 ])
 def test_attention_mixed_batch(dtype, hq, hkv, d, page) -> None:
     lens = [(1, 1), (16, 1), (17, 1), (33, 33), (64, 2), (300, 1), (129, 40), (96, 96), (500, 3), (1025, 1)]

@@ -1,0 +1,444 @@
+// Paged split-K decode attention on the tensor cores with TMA tile loads (bf16, head sizes 64 and
+// 128, page sizes 8 or a multiple of 16): the variant of attention_decode_mma.cu that fetches a
+// 16-key tile with a few tensor copies instead of one bulk copy per row.
+// one query token per request, all query heads of a kv group as the 16 rows of an mma tile.
+// Math as in attention_simt.cuh (upstream src/tinyserve/attention.py:89-111; the split of a
+// request's keys into ranges that are merged afterwards follows upstream
+// src/tinyserve/triton_attention.py:243-327).
+//
+// The cache of one layer is described to the TMA unit as a matrix of (page, kv head, offset) rows
+// by head_dim columns. A tile is 16 consecutive positions of one kv head, which lie in one page
+// (or two pages of 8): one lane fetches it with cp.async.bulk.tensor boxes of 16 (or 8) rows by
+// 64 columns, 128-byte swizzled, completion counted by an mbarrier; ldmatrix reads the swizzled
+// rows without bank conflicts and without padding. Rows of a tile that lie outside the request's
+// range hold whatever the page holds there; their scores are masked and their values zeroed
+// before use. Every warp runs its own two-stage pipeline of tiles;
+// S = Q K^T and O += P V are mma.sync m16n8k16 with 32-bit accumulators; the softmax is
+// online, 32-bit, base 2. A CTA is one (request, kv group, key range); its four warps take
+// tiles in turn and merge at the end; the CTA that finishes a request's last range merges the
+// ranges (arrival counter), so there is no second kernel.
+// Every mbarrier wait is bounded; a wait that runs out sets *error_flag and the CTA leaves.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "attention.cuh"
+
+namespace ts {
+
+#ifndef DM_STAGES_N
+#define DM_STAGES_N 2
+#endif
+constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_TK = 16, DM_STAGES = DM_STAGES_N;
+constexpr int DM_MAX_COUNTERS = 1 << 16;
+constexpr long long DM_WAIT_CYCLES = 2000000000ll;
+
+static __device__ unsigned int g_dt_arrivals[DM_MAX_COUNTERS];
+
+__device__ __forceinline__ uint32_t dm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void dm_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(dm_smem(p)));
+}
+__device__ __forceinline__ void dm_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(dm_smem(p)));
+}
+__device__ __forceinline__ void dm_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t dm_pack(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void dm_bar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(dm_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void dm_bar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(dm_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void dm_bar_arrive_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(dm_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool dm_bar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = dm_smem(bar);
+  const long long start = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if ((i & 1023u) == 1023u && clock64() - start > DM_WAIT_CYCLES) return false;
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+}
+// A box of rows x 64 columns of the cache matrix -> shared memory, 128-byte swizzled.
+__device__ __forceinline__ void dm_tensor_copy(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dm_smem(dst)), "l"(map), "r"(dm_smem(bar)), "r"(x), "r"(y) : "memory");
+}
+// Address of the 16-byte chunk `chunk` (of head_dim / 8) of row `row` (0..15) of a swizzled tile:
+// sub-tiles of 64 columns are 2 KiB apart; within one, a row is 128 bytes and its chunks are
+// permuted by the row's low three bits.
+__device__ __forceinline__ const unsigned char* dm_swizzled(const unsigned char* tile, int row, int chunk) {
+  return tile + (chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+// D64 = head_dim / 64 (1 or 2). BR = rows of a tensor box: 16 (page size a multiple of 16) or 8.
+// blockIdx = (request in the list, kv head * passes + pass, key range); a pass covers up to 16
+// query heads of the group.
+template <int D64, int BR>
+__global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                     const __grid_constant__ CUtensorMap map_v,
+                                                                     AttnArgs a, int passes, int* error_flag) {
+  constexpr int D = D64 * 64, D16 = D / 16;
+  constexpr int TILE_BYTES = DM_TK * D * 2;                 // one K (or V) tile: 16 rows, unpadded
+  extern __shared__ __align__(16) unsigned char dm_raw[];
+  __shared__ __align__(8) uint64_t bars[DM_WARPS][DM_STAGES];
+  __shared__ int is_last;
+  pdl_trigger();
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)dm_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  unsigned char* my = tiles + (size_t)warp * DM_STAGES * 2 * TILE_BYTES;      // [stage][K|V][tile]
+  const int G = a.num_heads / a.num_kv_heads;
+  const int si = blockIdx.x;
+  const int kvh = blockIdx.y / passes;
+  const int g0 = (blockIdx.y - kvh * passes) * 16;
+  const int ng = min(16, G - g0);
+  const int split = blockIdx.z;
+  if (lane == 0) {
+    for (int s = 0; s < DM_STAGES; ++s) dm_bar_init(&bars[warp][s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  pdl_wait();
+
+  const int seq = a.seq_ids[si];
+  const int ctx = a.ctx_lens[seq];
+  const int qrow = a.cu_q[seq];
+  const int lo = (a.window > 0) ? max(0, ctx - a.window) : 0;
+  const int lo_al = lo & ~(DM_TK - 1);
+  const int ntiles_all = (ctx - lo_al + DM_TK - 1) / DM_TK;
+  const int tiles_per = (ntiles_all + a.num_splits - 1) / a.num_splits;
+  const int tile_begin = split * tiles_per;
+  const int tile_end = min(ntiles_all, tile_begin + tiles_per);
+  const int* table = a.block_tables + (size_t)seq * a.table_width;
+
+  // ---- Q fragments: row r = query head g0 + r of the group (rows beyond the group are zero)
+  uint32_t qf[D16][4];
+  {
+    const bf16* qbase = (const bf16*)a.q + ((size_t)qrow * a.num_heads + kvh * G + g0) * D;
+#pragma unroll
+    for (int kk = 0; kk < D16; ++kk) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = g + 8 * h;
+        uint32_t lo_w = 0u, hi_w = 0u;
+        if (r < ng) {
+          lo_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + kk * 16 + 2 * t);
+          hi_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + kk * 16 + 8 + 2 * t);
+        }
+        qf[kk][h] = lo_w;
+        qf[kk][2 + h] = hi_w;
+      }
+    }
+  }
+
+  // One lane fetches a tile: the 16 positions from k0 lie in one page (BR = 16) or in two pages
+  // of 8. Row of the cache matrix = (page * kv_heads + kvh) * page_size + offset in the page.
+  auto load_tile = [&](int tile, int stage) {
+    if (lane != 0) return;
+    const int k0 = lo_al + tile * DM_TK;
+    unsigned char* kd = my + (size_t)stage * 2 * TILE_BYTES;
+    unsigned char* vd = kd + TILE_BYTES;
+    uint64_t* bar = &bars[warp][stage];
+    dm_bar_arrive_tx(bar, 2u * TILE_BYTES);
+#pragma unroll
+    for (int part = 0; part < DM_TK / BR; ++part) {
+      int kpos = k0 + part * BR;
+      if (kpos >= ctx) kpos = k0;      // a part wholly past the end: fetch any valid rows, they are masked
+      int page, off;
+      if (a.page_shift >= 0) { page = table[kpos >> a.page_shift]; off = kpos & (a.page_size - 1); }
+      else { const int idx = kpos / a.page_size; page = table[idx]; off = kpos - idx * a.page_size; }
+      const int y = (page * a.num_kv_heads + kvh) * a.page_size + off;
+#pragma unroll
+      for (int h = 0; h < D64; ++h) {
+        dm_tensor_copy(kd + h * 2048 + part * BR * 128, &map_k, h * 64, y, bar);
+        dm_tensor_copy(vd + h * 2048 + part * BR * 128, &map_v, h * 64, y, bar);
+      }
+    }
+  };
+
+  float o[2 * D16][4];
+#pragma unroll
+  for (int i = 0; i < 2 * D16; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  bool failed = false;
+
+  // this warp's tiles: tile_begin + warp, + DM_WARPS, ...
+  const int first = tile_begin + warp;
+  for (int s = 0; s < DM_STAGES; ++s) {
+    const int tile = first + s * DM_WARPS;
+    if (tile < tile_end) load_tile(tile, s);
+  }
+  int n = 0;
+  for (int tile = first; tile < tile_end; tile += DM_WARPS, ++n) {
+    const int stage = n % DM_STAGES;
+    const uint32_t parity = (n / DM_STAGES) & 1;
+    if (!dm_bar_wait(&bars[warp][stage], parity)) { failed = true; break; }
+    unsigned char* kt = my + (size_t)stage * 2 * TILE_BYTES;
+    unsigned char* vt = kt + TILE_BYTES;
+    const int k0 = lo_al + tile * DM_TK;
+    // positions of the tile outside [lo, ctx): their value rows may hold anything; zero them
+    if (k0 < lo || k0 + DM_TK > ctx) {
+      const int row = lane & 15;
+      const int kpos = k0 + row;
+      if (kpos < lo || kpos >= ctx) {
+        for (int c = (lane >> 4); c < D / 8; c += 2)
+          *reinterpret_cast<uint4*>(vt + (c >> 3) * 2048 + row * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncwarp();
+    }
+    // ---- S = Q K^T: 2 key tiles of 8
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D16; ++kk) {
+      uint32_t bfr[4];
+      const int key = (lane & 7) + (lane >> 4) * 8;
+      const int chunk = kk * 2 + ((lane >> 3) & 1);
+      dm_ldmatrix_x4(bfr, dm_swizzled(kt, key, chunk));
+      dm_mma(s[0], qf[kk], bfr[0], bfr[1]);
+      dm_mma(s[1], qf[kk], bfr[2], bfr[3]);
+    }
+    // ---- scale, mask (keys outside [lo, ctx)), online softmax for rows g and g + 8
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kpos = k0 + i * 8 + 2 * t + (e & 1);
+        const bool ok = kpos >= lo && kpos < ctx;
+        const float v = ok ? s[i][e] * a.scale_log2 : -INFINITY;
+        s[i][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m[h], mx[h]);
+      corr[h] = (m_new == -INFINITY) ? 1.f : exp2f(m[h] - m_new);
+      m[h] = m_new;
+      l[h] *= corr[h];
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = (s[i][e] == -INFINITY) ? 0.f : exp2f(s[i][e] - m[e >> 1]);
+        s[i][e] = p;
+        l[e >> 1] += p;
+      }
+#pragma unroll
+    for (int i = 0; i < 2 * D16; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0];
+      o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    // ---- O += P V: one step of 16 keys
+    {
+      uint32_t pf[4];
+      pf[0] = dm_pack(s[0][0], s[0][1]);
+      pf[1] = dm_pack(s[0][2], s[0][3]);
+      pf[2] = dm_pack(s[1][0], s[1][1]);
+      pf[3] = dm_pack(s[1][2], s[1][3]);
+#pragma unroll
+      for (int dp = 0; dp < D16; ++dp) {
+        uint32_t vfr[4];
+        const int key = (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int chunk = dp * 2 + (lane >> 4);
+        dm_ldmatrix_x4_trans(vfr, dm_swizzled(vt, key, chunk));
+        dm_mma(o[2 * dp], pf, vfr[0], vfr[1]);
+        dm_mma(o[2 * dp + 1], pf, vfr[2], vfr[3]);
+      }
+    }
+    __syncwarp();                                  // every lane is done with this stage
+    // order this warp's accesses to the stage (reads, and the zeroing above) before the copy
+    // engine's next write into it
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const int nxt = tile + DM_STAGES * DM_WARPS;
+    if (nxt < tile_end) load_tile(nxt, stage);
+  }
+  if (failed && lane == 0) atomicExch(error_flag, 1);
+
+  // ---- row sums across the quad; then merge the warps through shared memory
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  __syncthreads();                                 // all warps are done with their tiles
+  float* red = reinterpret_cast<float*>(tiles);    // [DM_WARPS][16][D + 2], reusing the tile memory
+  constexpr int WS = D + 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + 8 * h;
+    if (r < ng) {
+      float* w = red + ((size_t)warp * 16 + r) * WS;
+#pragma unroll
+      for (int i = 0; i < 2 * D16; ++i) {
+        w[i * 8 + 2 * t] = o[i][2 * h];
+        w[i * 8 + 2 * t + 1] = o[i][2 * h + 1];
+      }
+      if (t == 0) { w[D] = m[h]; w[D + 1] = l[h]; }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < ng * D; idx += DM_THREADS) {
+    const int r = idx / D, d = idx - r * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) mm = fmaxf(mm, red[((size_t)w * 16 + r) * WS + D]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) {
+      const float* ws = red + ((size_t)w * 16 + r) * WS;
+      const float c = (ws[D] == -INFINITY) ? 0.f : exp2f(ws[D] - mm);
+      num += ws[d] * c;
+      den += ws[D + 1] * c;
+    }
+    const int head = kvh * G + g0 + r;
+    if (a.num_splits == 1) {
+      ((bf16*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = __float2bfloat16_rn(num / den);
+    } else {
+      const size_t pidx = ((size_t)si * a.num_heads + head) * a.num_splits + split;
+      a.part_acc[pidx * D + d] = num;
+      if (d == 0) { a.part_ml[pidx * 2] = mm; a.part_ml[pidx * 2 + 1] = den; }
+    }
+  }
+  if (a.num_splits == 1) return;
+  // ---- the CTA that arrives last for this (request, heads) merges the ranges
+  unsigned int* counter = &g_dt_arrivals[((size_t)si * gridDim.y + blockIdx.y) % DM_MAX_COUNTERS];
+  if (!cta_arrives_last(counter, (unsigned int)a.num_splits, &is_last)) return;
+  merge_splits<bf16>(a, si, qrow, kvh * G + g0, ng, red);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*DtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static DtEncodeFn dt_encode_fn() {
+  static DtEncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (DtEncodeFn)p;
+  }
+  return fn;
+}
+
+// The descriptor of one cache tensor ([rows, head_dim] bf16, boxes of box_rows x 64, 128-byte
+// swizzle). Descriptors are kept per (address, rows, head_dim, box_rows): a cache tensor is
+// allocated once and used for every step.
+static const CUtensorMap* cache_map(const void* base, long long rows, int head_dim, int box_rows) {
+  static std::mutex mu;
+  static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> maps;
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_tuple(base, rows, head_dim, box_rows);
+  auto it = maps.find(key);
+  if (it != maps.end()) return &it->second;
+  DtEncodeFn fn = dt_encode_fn();
+  if (fn == nullptr) return nullptr;
+  CUtensorMap m;
+  cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return nullptr;
+  return &maps.emplace(key, m).first->second;
+}
+
+template <int D64, int BR>
+static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, cudaStream_t stream) {
+  constexpr int D = D64 * 64;
+  const CUtensorMap* mk = cache_map(a.k_cache, cache_rows, D, BR);
+  const CUtensorMap* mv = cache_map(a.v_cache, cache_rows, D, BR);
+  if (mk == nullptr || mv == nullptr) return TS_ERR_UNSUPPORTED;
+  const size_t tiles = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TK * D * 2 + 1024;
+  const size_t red = sizeof(float) * (size_t)DM_WARPS * 16 * (D + 2) + 1024;
+  const size_t smem = tiles > red ? tiles : red;
+  auto kern = decode_attn_tma_kernel<D64, BR>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int G = a.num_heads / a.num_kv_heads;
+  const int passes = (G + 15) / 16;
+  if (a.num_splits > 1 && (long long)a.num_seqs * a.num_kv_heads * passes > DM_MAX_COUNTERS) return TS_ERR_UNSUPPORTED;
+  dim3 grid(a.num_seqs, a.num_kv_heads * passes, a.num_splits);
+  return launch(kern, grid, DM_THREADS, smem, stream, *mk, *mv, a, passes, error_flag);
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+// bf16 decode attention with TMA tile loads. head_dim 64 or 128; page_size 8 or a multiple of 16;
+// num_pages_total = pages of the cache tensors (the pad page included). Other arguments as
+// ts_decode_attention_mma. Returns TS_ERR_UNSUPPORTED for sizes it does not take.
+extern "C" int ts_decode_attention_tma(
+    const void* q, void* out, const void* k_cache, const void* v_cache, long long num_pages_total,
+    const int* block_tables, int table_width, const int* cu_q, const int* ctx_lens, const int* decode_seqs,
+    int num_decode, int num_heads, int num_kv_heads, int head_dim, int page_size, float scale, int window,
+    int num_splits, float* part_acc, float* part_ml, int* error_flag, cudaStream_t stream) {
+  if (num_decode <= 0) return 0;
+  if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
+  if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || num_splits < 1 || num_pages_total <= 0)
+    return TS_ERR_BAD_ARGUMENT;
+  if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return TS_ERR_BAD_ARGUMENT;
+  if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache)) & 15) return TS_ERR_UNSUPPORTED;
+  const long long rows = num_pages_total * num_kv_heads * page_size;
+  if (rows >= (1ll << 31)) return TS_ERR_UNSUPPORTED;
+  AttnArgs a;
+  a.q = q; a.out = out; a.k_cache = k_cache; a.v_cache = v_cache;
+  a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
+  a.seq_ids = decode_seqs; a.num_seqs = num_decode;
+  a.num_heads = num_heads; a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.page_size = page_size;
+  a.page_shift = page_shift_of(page_size);
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.window = window;
+  a.num_splits = num_splits; a.part_acc = part_acc; a.part_ml = part_ml;
+  if (head_dim == 64) {
+    return page_size == 8 ? launch_dt<1, 8>(a, rows, error_flag, stream) : launch_dt<1, 16>(a, rows, error_flag, stream);
+  }
+  return page_size == 8 ? launch_dt<2, 8>(a, rows, error_flag, stream) : launch_dt<2, 16>(a, rows, error_flag, stream);
+}
+
+// How many CTAs of this kernel fit the machine at once (for the split choice).
+extern "C" int ts_decode_attention_tma_slots(int head_dim) {
+  const size_t smem = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TK * head_dim * 2 + 2048;
+  int per_sm = (int)((227 * 1024) / smem);
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 3) per_sm = 3;       // registers: 160 per thread
+  return 148 * per_sm;
+}

@@ -91,6 +91,23 @@ __global__ void qk_norm_rope_write_kernel(
 }
 
 
+// Two adjacent elements with one access (the element index is even, rows are 16-byte aligned).
+__device__ __forceinline__ void load2(const float* p, float (&f)[2]) {
+  const float2 v = *reinterpret_cast<const float2*>(p);
+  f[0] = v.x; f[1] = v.y;
+}
+__device__ __forceinline__ void load2(const bf16* p, float (&f)[2]) {
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+  f[0] = __uint_as_float(w << 16); f[1] = __uint_as_float(w & 0xffff0000u);
+}
+__device__ __forceinline__ void store2(float* p, const float (&f)[2]) {
+  *reinterpret_cast<float2*>(p) = make_float2(f[0], f[1]);
+}
+__device__ __forceinline__ void store2(bf16* p, const float (&f)[2]) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(f[0], f[1]);
+  *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<uint32_t*>(&h);
+}
+
 // Register-only variant for the common case: the whole head is rotated with the "half" pairing
 // (rotary_dim == head_dim, head_dim % 4 == 0). A lane owns pairs p = 2 lane, 2 lane + 1 (+ 64 j):
 // elements p, p + 1 and their partners p + D/2, p + 1 + D/2, each fetched with one access.
@@ -140,8 +157,8 @@ __global__ void qk_norm_rope_write_fast_kernel(
     const int p = 2 * lane + 64 * j;
     a[j][0] = a[j][1] = b[j][0] = b[j][1] = 0.f;
     if (p < half) {
-      a[j][0] = to_float(src[p]); a[j][1] = to_float(src[p + 1]);
-      b[j][0] = to_float(src[half + p]); b[j][1] = to_float(src[half + p + 1]);
+      load2(src + p, a[j]);
+      load2(src + half + p, b[j]);
       ss += a[j][0] * a[j][0] + a[j][1] * a[j][1] + b[j][0] * b[j][0] + b[j][1] * b[j][1];
     }
   }
@@ -152,10 +169,13 @@ __global__ void qk_norm_rope_write_fast_kernel(
     for (int j = 0; j < MAXJ; ++j) {
       const int p = 2 * lane + 64 * j;
       if (p < half) {
+        float wa[2], wb[2];
+        load2(weight + p, wa);
+        load2(weight + half + p, wb);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          a[j][e] = round_to<T>(round_to<T>(a[j][e] * rstd) * to_float(weight[p + e]));
-          b[j][e] = round_to<T>(round_to<T>(b[j][e] * rstd) * to_float(weight[half + p + e]));
+          a[j][e] = round_to<T>(round_to<T>(a[j][e] * rstd) * wa[e]);
+          b[j][e] = round_to<T>(round_to<T>(b[j][e] * rstd) * wb[e]);
         }
       }
     }
@@ -166,12 +186,12 @@ __global__ void qk_norm_rope_write_fast_kernel(
   for (int j = 0; j < MAXJ; ++j) {
     const int p = 2 * lane + 64 * j;
     if (p < half) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float cv = c[p + e], sv = s[p + e];
-        dst[p + e] = from_float<T>(a[j][e] * cv - b[j][e] * sv);
-        dst[half + p + e] = from_float<T>(b[j][e] * cv + a[j][e] * sv);
-      }
+      const float2 cv = *reinterpret_cast<const float2*>(c + p);
+      const float2 sv = *reinterpret_cast<const float2*>(s + p);
+      const float ra[2] = {a[j][0] * cv.x - b[j][0] * sv.x, a[j][1] * cv.y - b[j][1] * sv.y};
+      const float rb[2] = {b[j][0] * cv.x + a[j][0] * sv.x, b[j][1] * cv.y + a[j][1] * sv.y};
+      store2(dst + p, ra);
+      store2(dst + half + p, rb);
     }
   }
 }

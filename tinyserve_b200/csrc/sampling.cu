@@ -103,10 +103,30 @@ __device__ __forceinline__ Best scan_range(const float* __restrict__ l, int begi
   Best best;
   best.v = 0.f; best.i = -1;
   if (!(temp > 0.f)) {
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-      Best c; c.v = l[i]; c.i = i;
-      best = better(best, c);
+    // greedy: a thread's indices only grow, so "strictly greater" keeps the first maximum.
+    float bv = -INFINITY;
+    int bi = -1;
+    if ((((uintptr_t)l) & 15) == 0) {
+      const float4* l4 = reinterpret_cast<const float4*>(l);
+      for (int i4 = begin / 4 + threadIdx.x; i4 * 4 < end; i4 += blockDim.x) {
+        const int i = i4 * 4;
+        if (i + 4 <= end) {
+          const float4 v = l4[i4];
+          if (v.x > bv) { bv = v.x; bi = i; }
+          if (v.y > bv) { bv = v.y; bi = i + 1; }
+          if (v.z > bv) { bv = v.z; bi = i + 2; }
+          if (v.w > bv) { bv = v.w; bi = i + 3; }
+        } else {
+          for (int e = i; e < end; ++e)
+            if (l[e] > bv) { bv = l[e]; bi = e; }
+        }
+      }
+    } else {
+      for (int i = begin + threadIdx.x; i < end; i += blockDim.x)
+        if (l[i] > bv) { bv = l[i]; bi = i; }
     }
+    if (bi < 0 && begin + (int)threadIdx.x < end) { bv = l[begin + threadIdx.x]; bi = begin + threadIdx.x; }  // all -inf / NaN
+    best.v = bv; best.i = bi;
     return best;
   }
   const float inv_t = 1.f / temp;
@@ -221,8 +241,9 @@ extern "C" int ts_sample(const float* logits, int num_rows, int vocab, const flo
   if (num_rows <= 0) return 0;
   if (vocab <= 0 || num_rows > SM_MAX_ROWS) return TS_ERR_BAD_ARGUMENT;
   if (temperature != nullptr && (seeds == nullptr || draws == nullptr)) return TS_ERR_BAD_ARGUMENT;
-  // enough CTAs to fill the machine, each with at least a few thousand tokens
-  int chunks = (148 * 2 + num_rows - 1) / num_rows;
+  // as many CTAs as run at once (two of 1024 threads per SM), never a partly filled second
+  // round, each with at least a few thousand tokens
+  int chunks = (148 * 2) / num_rows;
   const int most = (vocab + 4095) / 4096;
   if (chunks > most) chunks = most;
   if (chunks > SM_MAX_CHUNKS) chunks = SM_MAX_CHUNKS;

@@ -38,6 +38,9 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_decode_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
                                 _vp, _vp],
     "ts_decode_attention_mma_slots": [_i],
+    "ts_decode_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
+                                _i, _vp, _vp, _vp, _vp],
+    "ts_decode_attention_tma_slots": [_i],
     "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
@@ -198,19 +201,13 @@ def decode_splits(num_decode: int, num_kv_heads: int, group: int, max_context_le
 
 def choose_splits(ctas: int, slots: int, most: int) -> int:
     """Key ranges per request for a kernel of which ``slots`` CTAs run at once and that would
-    launch ``ctas`` CTAs unsplit: few CTAs are cut until they fill the machine; many CTAs are
-    cut so that the last, partly filled round of CTAs costs little. Depends only on the shape of
-    the step, so a recorded step always replays the same grid."""
-    most = max(1, min(most, MAX_SPLITS))
-    if ctas * 2 <= slots:
-        return max(1, min(slots // ctas, most))
-    best, best_cost = 1, float("inf")
-    for s in range(1, min(most, 8) + 1):
-        rounds = -(-ctas * s // slots)
-        cost = rounds / s + 0.08 * s          # time in units of an unsplit CTA, plus per-CTA overhead
-        if cost < best_cost - 1e-9:
-            best, best_cost = s, cost
-    return best
+    launch ``ctas`` CTAs unsplit. A step that already gives most of the machine a CTA is not cut
+    (the merge of the ranges costs more than a partly filled last round of CTAs); fewer CTAs are
+    cut until they fill the machine, up to 12 ranges (measured on B200 at batch 1 to 64). Depends
+    only on the shape of the step, so a recorded step always replays the same grid."""
+    if 2 * ctas > slots:
+        return 1
+    return max(1, min(slots // ctas, most, 12, MAX_SPLITS))
 
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
@@ -250,20 +247,29 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if dt == torch.bfloat16 and d <= 128:
         # decode rows on the tensor cores too: one CTA per (request, kv group, key range)
         ctas = ctx.num_decode * hkv * (-(-(hq // hkv) // 16))
-        splits = choose_splits(ctas, _mma_decode_slots(d), ctx.max_context_len // 64)
+        tma = d in (64, 128) and (page_size == 8 or page_size % 16 == 0) and k_cache.shape[0] * hkv * page_size < 2 ** 31
+        slots = _decode_slots(d, tma)
+        splits = choose_splits(ctas, slots, ctx.max_context_len // 64)
         part_acc = part_ml = None
         if splits > 1:
             part_acc = ctx.arena.take((ctx.num_decode, hq, splits, d), torch.float32)
             part_ml = ctx.arena.take((ctx.num_decode, hq, splits, 2), torch.float32)
-        _check(_fn("ts_decode_attention_mma")(
-            _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
-            _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
-            _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
-            _dev(ctx.context_lens_dev, "context_lens", torch.int32),
-            _dev(ctx.decode_seqs, "decode_seqs", torch.int32), ctx.num_decode,
-            hq, hkv, d, page_size, float(scale), int(window), splits,
-            _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _error_word(q.device).data_ptr(), _stream()),
-            "decode_attention_mma")
+        common = (_dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
+                  _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+                  _dev(ctx.context_lens_dev, "context_lens", torch.int32),
+                  _dev(ctx.decode_seqs, "decode_seqs", torch.int32), ctx.num_decode,
+                  hq, hkv, d, page_size, float(scale), int(window), splits,
+                  _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _error_word(q.device).data_ptr(), _stream())
+        if tma:
+            # tiles fetched by the TMA unit (tensor copies, 128-byte swizzle)
+            _check(_fn("ts_decode_attention_tma")(
+                _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+                k_cache.shape[0], *common), "decode_attention_tma")
+        else:
+            # tiles fetched row by row with bulk copies
+            _check(_fn("ts_decode_attention_mma")(
+                _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), *common),
+                "decode_attention_mma")
         return
     splits, part_acc, part_ml = 1, None, None
     if ctx.num_decode:
@@ -283,13 +289,14 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         kernels=(1 if num_prefill else 0) + (1 if ctx.num_decode else 0))
 
 
-_slots_cache: dict[int, int] = {}
+_slots_cache: dict[tuple[int, bool], int] = {}
 
 
-def _mma_decode_slots(head_dim: int) -> int:
-    n = _slots_cache.get(head_dim)
+def _decode_slots(head_dim: int, tma: bool) -> int:
+    n = _slots_cache.get((head_dim, tma))
     if n is None:
-        n = _slots_cache[head_dim] = int(_fn("ts_decode_attention_mma_slots")(head_dim))
+        name = "ts_decode_attention_tma_slots" if tma else "ts_decode_attention_mma_slots"
+        n = _slots_cache[(head_dim, tma)] = int(_fn(name)(head_dim))
     return n
 
 
