@@ -41,6 +41,8 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_decode_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
                                 _i, _vp, _vp, _vp, _vp],
     "ts_decode_attention_tma_slots": [_i],
+    "ts_prefill_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
+                                 _i, _vp, _vp],
     "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
@@ -232,22 +234,34 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
         raise KernelError("paged_attention: block_tables must be [requests, width]")
     num_prefill = ctx.num_prefill
+    tma_ok = (dt == torch.bfloat16 and d in (64, 128) and (page_size == 8 or page_size % 16 == 0)
+              and k_cache.shape[0] * hkv * page_size < 2 ** 31)
     if num_prefill and dt == torch.bfloat16 and d <= 128:
         # prefill rows on the tensor cores; the decode rows follow below
-        _check(_fn("ts_prefill_attention_mma")(
-            _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
-            _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
-            _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
-            _dev(ctx.context_lens_dev, "context_lens", torch.int32),
-            _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
-            hq, hkv, d, page_size, float(scale), int(window), _stream()), "prefill_attention_mma")
+        if tma_ok:
+            _check(_fn("ts_prefill_attention_tma")(
+                _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), k_cache.shape[0],
+                _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
+                _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+                _dev(ctx.context_lens_dev, "context_lens", torch.int32),
+                _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
+                hq, hkv, d, page_size, float(scale), int(window), _error_word(q.device).data_ptr(), _stream()),
+                "prefill_attention_tma")
+        else:
+            _check(_fn("ts_prefill_attention_mma")(
+                _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"),
+                _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
+                _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+                _dev(ctx.context_lens_dev, "context_lens", torch.int32),
+                _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
+                hq, hkv, d, page_size, float(scale), int(window), _stream()), "prefill_attention_mma")
         num_prefill = 0
         if not ctx.num_decode:
             return
     if dt == torch.bfloat16 and d <= 128:
         # decode rows on the tensor cores too: one CTA per (request, kv group, key range)
         ctas = ctx.num_decode * hkv * (-(-(hq // hkv) // 16))
-        tma = d in (64, 128) and (page_size == 8 or page_size % 16 == 0) and k_cache.shape[0] * hkv * page_size < 2 ** 31
+        tma = tma_ok
         slots = _decode_slots(d, tma)
         splits = choose_splits(ctas, slots, ctx.max_context_len // 64)
         part_acc = part_ml = None
