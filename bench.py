@@ -118,6 +118,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--pdl", type=int, default=None,
+                    help="mask of kernel classes launched with programmatic dependent launch (default: the engine's)")
     ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between kernels")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
@@ -138,11 +140,13 @@ def main() -> int:
     from tinyserve_b200.cache import CacheManager
     from tinyserve_b200.config import config_from_dict
     from tinyserve_b200.engine import Engine
-    from tinyserve_b200.engine.step import StepEntry
+    from tinyserve_b200.engine.step import ModelRunner, StepEntry
     from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
-    ops.set_programmatic_launch(not args.no_pdl)
+    fixed_pdl = args.no_pdl or args.pdl is not None
+    if fixed_pdl:
+        ops.set_programmatic_launch(0 if args.no_pdl else args.pdl)
     cfg_dict = dict(MODELS[args.model])
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
@@ -163,8 +167,10 @@ def main() -> int:
         pages = max(batch * (-(-tokens_per_seq // page) + 1), cfg.max_position_embeddings // page)
         cache = CacheManager(model.cache_needs(), page_size=page, num_pages=pages, max_requests=batch,
                              dtype=torch.bfloat16, device=dev)
+        runner = ModelRunner(model, cache)
+        runner.tune_launch_overlap = not fixed_pdl
         return Engine(model, cache, max_num_seqs=batch, max_batch_tokens=max(2048, batch), chunked_prefill=True,
-                      decode_graphs=not args.no_graphs, graph_max_context=cfg.max_position_embeddings)
+                      decode_graphs=not args.no_graphs, graph_max_context=cfg.max_position_embeddings, runner=runner)
 
     def decode_bytes(batch: int, ctx: float) -> float:
         kv = CacheManager.bytes_per_token(model.cache_needs(), 2)

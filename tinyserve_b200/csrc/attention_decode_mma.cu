@@ -13,6 +13,7 @@
 // tiles in turn and merge at the end; the CTA that finishes a request's last range merges the
 // ranges (arrival counter), so there is no second kernel.
 // Every mbarrier wait is bounded; a wait that runs out sets *error_flag and the CTA leaves.
+#define TS_PDL_CLASS PDL_ATTENTION
 #include "attention.cuh"
 
 namespace ts {

@@ -10,6 +10,7 @@
 // memory (row stride head_dim + 8 elements: ldmatrix reads without bank conflicts for every head
 // size) and double-buffered. S = Q K^T and O += P V are mma.sync m16n8k16 with 32-bit
 // accumulators; the softmax is online, in 32-bit, base 2.
+#define TS_PDL_CLASS PDL_ATTENTION
 #include <cuda_pipeline_primitives.h>
 
 #include "attention.cuh"

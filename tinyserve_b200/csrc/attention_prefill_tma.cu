@@ -11,6 +11,7 @@
 //    so under the causal mask every CTA of a request does the same amount of work.
 // A row of a query tile is a (token, query head of the kv group) pair, as in attention_mma.cu.
 // Every mbarrier wait is bounded; a wait that runs out sets *error_flag and the CTA leaves.
+#define TS_PDL_CLASS PDL_ATTENTION
 #include <cuda.h>
 
 #include <map>

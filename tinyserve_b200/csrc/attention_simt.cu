@@ -1,4 +1,5 @@
 // Entry point of the CUDA-core paged attention kernels (see attention_simt.cuh).
+#define TS_PDL_CLASS PDL_ATTENTION
 #include "attention_simt.cuh"
 
 using namespace ts;

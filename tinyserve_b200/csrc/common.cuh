@@ -117,7 +117,13 @@ static inline int launch_status() {
 // of the chain has finished and its writes are visible, so ordering is what it was; only the
 // launch latency and the part of a kernel that needs no input (index arithmetic, prefetch of
 // weights) overlap the predecessor. Off, the two calls do nothing.
+// The switch is a mask of kernel classes, so that the overlap can be limited to the kernels that
+// gain from it.
 extern int g_programmatic_launch;   // defined in elementwise.cu, set by ts_set_programmatic_launch
+constexpr int PDL_ELEMENTWISE = 1, PDL_SKINNY = 2, PDL_ATTENTION = 4, PDL_TCGEN05 = 8, PDL_SAMPLING = 16, PDL_OTHER = 32;
+#ifndef TS_PDL_CLASS
+#define TS_PDL_CLASS PDL_OTHER
+#endif
 
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -134,7 +140,7 @@ static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = g_programmatic_launch ? 1 : 0;
+  cfg.numAttrs = (g_programmatic_launch & TS_PDL_CLASS) ? 1 : 0;
   return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -2,6 +2,7 @@
 // an entry point for callers that may not allocate (see decode_attention_static_scratch.h,
 // which states the limits). The kernels are the ones of attention_simt.cuh; only where the
 // partial results live differs from ts_paged_attention_simt.
+#define TS_PDL_CLASS PDL_ATTENTION
 #include "decode_attention_static_scratch.h"
 
 #include "attention_simt.cuh"

@@ -4,6 +4,7 @@
 // src/tinyserve/model.py:178-179): the norm is computed in 32-bit, cast to the model dtype,
 // then multiplied by the weight in the model dtype; silu(gate) is rounded before the product.
 // The residual stream itself is kept in 32-bit, so the residual sum is a 32-bit sum.
+#define TS_PDL_CLASS PDL_ELEMENTWISE
 #include "common.cuh"
 
 namespace ts {
@@ -196,7 +197,9 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
 using namespace ts;
 
 // Turn programmatic dependent launch of this library's kernels on (1) or off (0).
-extern "C" void ts_set_programmatic_launch(int on) { g_programmatic_launch = on ? 1 : 0; }
+// `mask` selects the kernel classes (1 elementwise, 2 skinny product, 4 attention, 8 tcgen05
+// product, 16 sampling, 32 others); 0 turns it off, -1 turns it on for all.
+extern "C" void ts_set_programmatic_launch(int mask) { g_programmatic_launch = mask; }
 extern "C" int ts_get_programmatic_launch() { return g_programmatic_launch; }
 
 extern "C" int ts_embed(const int* tokens, const void* table, float* out, int num_tokens, int hidden,

@@ -5,6 +5,7 @@
 // 64 x 64 output tile per CTA, K in steps of 16, 256 threads with a 4 x 4 register tile each.
 // The sum over K runs in index order for every output, whatever M is, so a row's result does
 // not depend on which other rows share the batch.
+#define TS_PDL_CLASS PDL_OTHER
 #include "common.cuh"
 
 namespace ts {

@@ -22,6 +22,7 @@
 //
 // Needs K % 32 == 0 and N % 16 == 0 (the launcher reports TS_ERR_UNSUPPORTED otherwise and the
 // caller takes another kernel).
+#define TS_PDL_CLASS PDL_SKINNY
 #include "common.cuh"
 
 namespace ts {

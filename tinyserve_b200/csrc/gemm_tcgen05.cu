@@ -17,6 +17,7 @@
 // Every wait on an mbarrier is bounded: when the bound is hit the kernel records it in
 // *error_flag, stops waiting and still frees its tensor memory, so a fault in the pipeline
 // shows as an error code on the host and never as a hang.
+#define TS_PDL_CLASS PDL_TCGEN05
 #include <cuda.h>
 
 #include "common.cuh"

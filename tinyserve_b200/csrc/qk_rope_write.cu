@@ -7,6 +7,7 @@
 // Norm: 32-bit mean of squares over head_dim, value cast to T, times the weight, rounded to T.
 // Rotation in 32-bit on the rounded values, result rounded to T once.
 // Cache layout: [page, kv_head, offset_in_page, head_dim]; slot = page * page_size + offset.
+#define TS_PDL_CLASS PDL_ELEMENTWISE
 #include "common.cuh"
 
 namespace ts {

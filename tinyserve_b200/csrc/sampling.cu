@@ -13,6 +13,7 @@
 // A row without top-p is cut into chunks, one CTA each; the CTA that arrives last picks the
 // winner among the chunks' winners. A row with top-p needs sums over the whole row and is done
 // by one CTA.
+#define TS_PDL_CLASS PDL_SAMPLING
 #include "common.cuh"
 
 namespace ts {

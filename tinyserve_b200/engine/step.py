@@ -165,6 +165,9 @@ class ModelRunner:
         self.cache = cache
         self.device = model.device
         self.arena = Arena(self.device)
+        # choose the launch-overlap mask per step (prefill or decode); a caller that sets the
+        # mask itself (measurements) turns this off
+        self.tune_launch_overlap = True
         self.graphs: dict[int, DecodeGraph] = {}
         self.graph_max_context = 0
         self.num_graph_steps = 0
@@ -302,6 +305,8 @@ class ModelRunner:
         if not all(layer.block.mixer.graph_safe for layer in self.model.parts.layers):
             raise RuntimeError("a mixer of this model reads the step on the host; its decode step cannot be recorded")
         self.graph_max_context = max_context
+        if self.tune_launch_overlap:
+            ops.use_pdl_mask(ops.DEFAULT_PDL_MASK)
         for rows in sorted(set(buckets or default_buckets(max_batch))):
             g = DecodeGraph(self, rows, max_context)
             g.record(self)
@@ -333,6 +338,8 @@ class ModelRunner:
             self.num_graph_steps += 1
             return graph.logits[: len(entries)]
         ctx, rows, r = self.build_context(entries, want)
+        if self.tune_launch_overlap and self.device.type == "cuda":
+            ops.use_pdl_mask(ops.PREFILL_PDL_MASK if ctx.num_prefill else ops.DEFAULT_PDL_MASK)
         logits = self.model.forward(ctx, self.cache.entries, rows, r)
         self.num_steps += 1
         return logits

@@ -51,6 +51,23 @@ _SIGNATURES: dict[str, list[Any]] = {
 }
 _fns: dict[str, Any] = {}
 
+# Kernel classes launched with programmatic dependent launch by default: the skinny product
+# (its weight prefetch runs while the predecessor drains) and the attention kernels. Measured on
+# B200 in the recorded decode step of Qwen3-0.6B at batch 8: 1.195 ms with this mask, 1.263 ms
+# with none, 1.330 ms with all classes (the small elementwise kernels lose from starting early).
+DEFAULT_PDL_MASK = 2 | 4
+# Steps that carry prompt portions run large kernels, where starting early costs nothing and
+# hides the launch: all classes (2,048-token prefill of Qwen3-0.6B: 7.7 ms against 8.1 ms).
+PREFILL_PDL_MASK = -1
+_pdl_mask = DEFAULT_PDL_MASK
+
+
+def use_pdl_mask(mask: int) -> None:
+    """Switch the launch-overlap mask if it differs from the current one (cheap to call per step)."""
+    global _pdl_mask
+    if mask != _pdl_mask:
+        set_programmatic_launch(mask)
+
 # Kernels of this library launched so far (library matrix products are not counted).
 launch_count = 0
 
@@ -59,6 +76,11 @@ def _fn(name: str) -> Any:
     f = _fns.get(name)
     if f is None:
         lib = build.library()
+        if not _fns:
+            # first use of the library: overlap the launches of the kernel classes that gain from it
+            lib.ts_set_programmatic_launch.argtypes = [_i]
+            lib.ts_set_programmatic_launch.restype = None
+            lib.ts_set_programmatic_launch(DEFAULT_PDL_MASK)
         f = getattr(lib, name)
         f.argtypes = _SIGNATURES[name]
         f.restype = _i
@@ -423,14 +445,21 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
     silu_mul(gate_up, out)
 
 
-def set_programmatic_launch(on: bool) -> None:
+PDL_ELEMENTWISE, PDL_SKINNY, PDL_ATTENTION, PDL_TCGEN05, PDL_SAMPLING, PDL_OTHER = 1, 2, 4, 8, 16, 32
+
+
+def set_programmatic_launch(on: bool | int) -> None:
     """Launch this library's kernels so that each may start while its predecessor on the stream
     is draining (programmatic dependent launch); every kernel waits for its predecessor before
-    it touches data. Off by default."""
+    it touches data. ``True`` / ``False`` turn it on / off for all kernels; an int is a mask of
+    the ``PDL_*`` kernel classes. Off by default."""
     lib = build.library()
     lib.ts_set_programmatic_launch.argtypes = [_i]
     lib.ts_set_programmatic_launch.restype = None
-    lib.ts_set_programmatic_launch(1 if on else 0)
+    global _pdl_mask
+    mask = (-1 if on else 0) if isinstance(on, bool) else int(on)
+    lib.ts_set_programmatic_launch(mask)
+    _pdl_mask = mask
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
