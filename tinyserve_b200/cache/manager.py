@@ -86,6 +86,7 @@ class RequestCache:
     state_slot: int = -1
     num_tokens: int = 0
     released: bool = field(default=False)
+    uid: int = 0            # unique over the manager's life (object ids may be reused)
 
 
 class CacheManager:
@@ -99,6 +100,7 @@ class CacheManager:
             raise ValueError(f"page_size must be positive, got {page_size}")
         self.page_size, self.num_pages = page_size, num_pages
         self.dtype, self.device = dtype, torch.device(device)
+        self._next_uid = 0
         self.groups: list[PageGroup] = []
         self.entries: list[KVCacheEntry | StateCacheEntry | None] = [None] * len(needs)
         by_need: dict[KVNeed, PageGroup] = {}
@@ -157,7 +159,8 @@ class CacheManager:
                 if isinstance(e, StateCacheEntry):
                     e.state[slot].zero_()
         tables = [BlockTable(g.allocator, g.page_size, g.need.window) for g in self.groups]
-        return RequestCache(tables, slot)
+        self._next_uid += 1
+        return RequestCache(tables, slot, uid=self._next_uid)
 
     def can_admit(self) -> bool:
         return not self.has_state or self.state_pool.num_free > 0
@@ -182,8 +185,10 @@ class CacheManager:
         """Reserve room for ``n`` more tokens in every group, or in none."""
         if req.released:
             raise ValueError("append() on a request whose cache was freed")
-        if self.pages_short(req, n):
-            raise OutOfPagesError(f"{self.pages_short(req, n)} pages short for {n} tokens")
+        if len(req.tables) > 1:            # one group alone is all-or-nothing by itself
+            short = self.pages_short(req, n)
+            if short:
+                raise OutOfPagesError(f"{short} pages short for {n} tokens")
         for t in req.tables:
             t.append(n)
         req.num_tokens += n

@@ -90,6 +90,8 @@ class DecodeGraph:
         self.dev.copy_(self.host)
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
+        self._row_owner: dict[tuple[int, int], tuple[int, int, int]] = {}   # (group, row) -> what its table row holds
+        self._live_rows = 0
 
     def _fill_padding(self, runner: "ModelRunner", live: int) -> None:
         buf, n = self.host_np, self.rows
@@ -146,15 +148,27 @@ class DecodeGraph:
         buf[self.s_ctx][:b] = totals
         buf[self.s_pos][:b] = np.asarray(totals, dtype=np.int32) - 1
         buf[self.s_state][:b] = [e.cache.state_slot for e in entries]
+        owners = self._row_owner
         for g, ss, st in zip(runner.cache.groups, self.s_slots, self.s_tables):
             ps = g.page_size
             slots, table = buf[ss], buf[st].reshape(n, self.width)
             for i, e in enumerate(entries):
-                pages = e.cache.tables[g.index].pages_array()
-                table[i, : pages.shape[0]] = pages
+                bt = e.cache.tables[g.index]
+                pages = bt.pages
                 p = totals[i] - 1
                 slots[i] = pages[p // ps] * ps + p % ps
-        self._fill_padding(runner, b)
+                # A row that still belongs to the same request with as many pages as it had is
+                # already right in the buffer (decoding adds a page every page_size steps).
+                key = (e.cache.uid, len(pages), bt._first_live)
+                if owners.get((g.index, i)) != key:
+                    arr = bt.pages_array()
+                    table[i, : arr.shape[0]] = arr
+                    owners[(g.index, i)] = key
+        if b != self._live_rows:
+            self._fill_padding(runner, b)
+            for key in [k for k in owners if k[1] >= b]:
+                del owners[key]
+            self._live_rows = b
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
 
