@@ -122,6 +122,8 @@ def main() -> int:
                     help="mask of kernel classes launched with programmatic dependent launch (default: the engine's)")
     ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between kernels")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--fused-decode-rows", type=int, default=None,
+                    help="largest decode batch that takes the fused norm+rotation+attention kernel (0: never)")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="run a small case kernel by kernel between cudaProfilerStart/Stop and exit "
                          "(for ncu --profile-from-start off); combine with --layers, --batch")
@@ -144,6 +146,8 @@ def main() -> int:
     from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
+    if args.fused_decode_rows is not None:
+        ops.FUSED_DECODE_MAX_ROWS = args.fused_decode_rows
     fixed_pdl = args.no_pdl or args.pdl is not None
     if fixed_pdl:
         ops.set_programmatic_launch(0 if args.no_pdl else args.pdl)

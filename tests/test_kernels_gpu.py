@@ -205,6 +205,85 @@ def test_attention_far_key_dominates(dtype, new, pos) -> None:
     torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("hq,hkv,d,page", [(16, 8, 128, 16), (14, 2, 64, 8), (5, 5, 64, 32), (40, 2, 128, 16),
+                                           (3, 1, 128, 8)])
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("norm,rot", [(True, True), (False, True), (True, False)])
+def test_decode_attention_fused(hq, hkv, d, page, window, norm, rot) -> None:
+    """Norm, rotation, cache write and attention of decode tokens in one kernel, against the
+    plain references of the two steps. The slot of the new token holds NaN before the call, the
+    newest key is made to matter (scaled up), and the context lengths put it at the start, the
+    end and the middle of a tile and of a page."""
+    dtype = torch.bfloat16
+    lens = [1, 2, 15, 16, 17, 33, 64, 300, 777, 1025, 2048]
+    b = len(lens)
+    need = [-(-c // page) for c in lens]
+    pages = sum(need) + 3
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(3)).tolist()
+    tables = torch.zeros(b, max(need) + 1, dtype=torch.int32)
+    caches = [torch.full((pages, hkv, page, d), float("nan"), device="cuda", dtype=dtype) for _ in range(4)]
+    slots, at = [], 0
+    for i, c in enumerate(lens):
+        mine = perm[at: at + need[i]]
+        at += need[i]
+        tables[i, : need[i]] = torch.tensor(mine)
+        k = rnd(c - 1, hkv, d, dtype=dtype, seed=100 + i)
+        v = rnd(c - 1, hkv, d, dtype=dtype, seed=150 + i)
+        for p_ in range(c - 1):
+            for kc, vc in ((caches[0], caches[1]), (caches[2], caches[3])):
+                kc[mine[p_ // page], :, p_ % page] = k[p_]
+                vc[mine[p_ // page], :, p_ % page] = v[p_]
+        slots.append(mine[(c - 1) // page] * page + (c - 1) % page)
+    tables = tables.cuda()
+    slots = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    qkv = rnd(b, (hq + 2 * hkv) * d, dtype=dtype, seed=9, scale=1.5)
+    for h in range(hkv):      # the new key equals the group's first query: that head looks at it alone
+        qkv[:, (hq + h) * d: (hq + h + 1) * d] = qkv[:, h * (hq // hkv) * d: (h * (hq // hkv) + 1) * d]
+    qw = (1 + rnd(d, seed=5, scale=0.2)).to(dtype) if norm else None
+    kw = (1 + rnd(d, seed=6, scale=0.2)).to(dtype) if norm else None
+    cos = sin = None
+    if rot:
+        pos = torch.tensor([c - 1 for c in lens], device="cuda", dtype=torch.int32)
+        inv = (1e4 ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)).cuda()
+        cos, sin = torch.empty(b, d // 2, device="cuda"), torch.empty(b, d // 2, device="cuda")
+        ref.rope_tables(pos, inv, cos, sin)
+    ar = torch.arange(b, dtype=torch.int32, device="cuda")
+    ctx = SimpleNamespace(
+        num_seqs=b, cu_query_lens=torch.arange(b + 1, dtype=torch.int32, device="cuda"),
+        context_lens_dev=torch.tensor(lens, dtype=torch.int32, device="cuda"), decode_seqs=ar, prefill_seqs=ar * 0,
+        num_decode=b, num_prefill=0, max_query_len=1, max_context_len=max(lens), arena=Arena("cuda"))
+    ops.FUSED_DECODE_MIN_CTAS, saved = 0, ops.FUSED_DECODE_MIN_CTAS
+    try:
+        assert ops.can_fuse_decode(ctx, dtype, hq, hkv, d, page, pages, d if rot else 0, False, qkv.device)
+    finally:
+        ops.FUSED_DECODE_MIN_CTAS = saved
+    out = torch.full((b, hq * d), float("nan"), device="cuda", dtype=dtype)
+    want = torch.empty(b, hq * d, device="cuda", dtype=dtype)
+    ops.decode_attention_fused(qkv, qw, kw, 1e-6, cos, sin, slots, caches[0], caches[1], page, tables, ctx,
+                               d ** -0.5, window, hq, out)
+    q = torch.empty(b, hq, d, device="cuda", dtype=dtype)
+    ref.qk_norm_rope_write(qkv, q, qw, kw, 1e-6, cos, sin, d if rot else 0, False, slots, caches[2], caches[3],
+                           page, hq, hkv, d, True)
+    ref.paged_attention(q, caches[2], caches[3], page, tables, ctx, d ** -0.5, window, want)
+    ops.check_device_errors()
+    assert not out.isnan().any()
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    for a, w in ((caches[0], caches[2]), (caches[1], caches[3])):
+        assert torch.equal(a.isnan(), w.isnan()), "wrote outside the tokens' slots (or missed one)"
+        torch.testing.assert_close(a.float().nan_to_num(0), w.float().nan_to_num(0), **tol(dtype))
+    # the same step through the two separate kernels gives the same rows up to rounding
+    two = torch.empty_like(out)
+    for kc, vc in ((caches[0], caches[1]),):
+        for i, c in enumerate(lens):
+            s_ = int(slots[i])
+            kc[s_ // page, :, s_ % page] = float("nan")
+            vc[s_ // page, :, s_ % page] = float("nan")
+    ops.qk_norm_rope_write(qkv, q, qw, kw, 1e-6, cos, sin, d if rot else 0, False, slots, caches[0], caches[1],
+                           page, hq, hkv, d, True)
+    ops.paged_attention(q, caches[0], caches[1], page, tables, ctx, d ** -0.5, window, two)
+    torch.testing.assert_close(out.float(), two.float(), **tol(dtype))
+
+
 @pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                                 (torch.bfloat16, torch.float32)])
 @pytest.mark.parametrize("m,n,k", [(1, 301, 72), (7, 80, 176), (64, 64, 16), (65, 130, 33), (200, 1000, 1024)])

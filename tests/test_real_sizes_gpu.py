@@ -38,10 +38,20 @@ def real(tmp_path_factory):
     return folder, reqs, want
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_real_layer_sizes_under_every_cut(real, dtype) -> None:
+@pytest.mark.parametrize("dtype,fuse_every_decode", [(torch.float32, False), (torch.bfloat16, False),
+                                                     (torch.bfloat16, True)])
+def test_real_layer_sizes_under_every_cut(real, dtype, fuse_every_decode, monkeypatch) -> None:
+    """``fuse_every_decode``: steps of decode tokens alone take the fused norm + rotation +
+    cache write + attention kernel whatever their grid (the engine picks it only for grids that
+    gain from it, which these short requests never make)."""
+    from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
+    if fuse_every_decode:
+        monkeypatch.setattr(ops, "FUSED_DECODE_MIN_CTAS", 0)
+        calls = []
+        fused = ops.decode_attention_fused
+        monkeypatch.setattr(ops, "decode_attention_fused", lambda *a, **k: (calls.append(1), fused(*a, **k))[1])
     folder, reqs, want = real
     model = DecoderModel.from_folder(folder, dtype, "cuda")
     plans = [cases.mixed(reqs, 5)]
@@ -50,3 +60,5 @@ def test_real_layer_sizes_under_every_cut(real, dtype) -> None:
     for steps in plans:
         got = run_steps(model, 16, steps, cases.max_live_tokens(steps))
         check(got, want, {r: reqs[r] for r in got}, dtype)
+    if fuse_every_decode:
+        assert calls, "no step took the fused kernel"

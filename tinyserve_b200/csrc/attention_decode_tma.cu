@@ -91,18 +91,110 @@ __device__ __forceinline__ const unsigned char* dm_swizzled(const unsigned char*
   return tile + (chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
+// What the fused variant needs besides the attention arguments: the raw output of the qkv
+// product and what turns it into queries, keys and values (per-head RMSNorm weights, rotary
+// tables, cache slots). With it the kernel does the work of qk_rope_write.cu itself: every CTA
+// normalises and rotates its own query heads; the CTA that owns a request's last key range also
+// normalises, rotates and stores the new key and value, and patches them into its tile.
+struct FusedQkv {
+  const bf16* qkv;         // [tokens, (num_heads + 2 num_kv_heads) * head_dim]
+  const bf16* q_weight;    // [head_dim] or null (no norm)
+  const bf16* k_weight;
+  float eps;
+  const float* cos_t;      // [tokens, head_dim / 2] or null (no rotation)
+  const float* sin_t;
+  const int* slots;        // [tokens] cache slot of each new token
+  bf16* k_cache;           // writable views of the cache
+  bf16* v_cache;
+};
+
+// One head row (head_dim elements at src): optional RMSNorm with weight, optional rotate-half
+// rotation with the token's tables; result rounded to bf16 into dst0 and, if given, dst1.
+// Executed by a whole warp. Rounding points as in qk_rope_write.cu.
+template <int D>
+__device__ __forceinline__ void fused_head_row(const bf16* src, const bf16* weight, float eps, const float* c,
+                                               const float* s, bf16* dst0, bf16* dst1, int lane) {
+  constexpr int HALF = D / 2, MAXJ = (HALF + 63) / 64;
+  // every load first (row, weights, tables), so that they travel together
+  uint32_t xa[MAXJ], xb[MAXJ], wa[MAXJ], wb[MAXJ];
+  float2 cv[MAXJ], sv[MAXJ];
+#pragma unroll
+  for (int j = 0; j < MAXJ; ++j) {
+    const int p = 2 * lane + 64 * j;
+    xa[j] = xb[j] = 0u;
+    wa[j] = wb[j] = 0x3f803f80u;                 // bf16 ones
+    cv[j] = make_float2(1.f, 1.f);
+    sv[j] = make_float2(0.f, 0.f);
+    if (p < HALF) {
+      xa[j] = *reinterpret_cast<const uint32_t*>(src + p);
+      xb[j] = *reinterpret_cast<const uint32_t*>(src + HALF + p);
+      if (weight != nullptr) {
+        wa[j] = *reinterpret_cast<const uint32_t*>(weight + p);
+        wb[j] = *reinterpret_cast<const uint32_t*>(weight + HALF + p);
+      }
+      if (c != nullptr) {
+        cv[j] = *reinterpret_cast<const float2*>(c + p);
+        sv[j] = *reinterpret_cast<const float2*>(s + p);
+      }
+    }
+  }
+  float a[MAXJ][2], b[MAXJ][2];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXJ; ++j) {
+    a[j][0] = __uint_as_float(xa[j] << 16); a[j][1] = __uint_as_float(xa[j] & 0xffff0000u);
+    b[j][0] = __uint_as_float(xb[j] << 16); b[j][1] = __uint_as_float(xb[j] & 0xffff0000u);
+    ss += a[j][0] * a[j][0] + a[j][1] * a[j][1] + b[j][0] * b[j][0] + b[j][1] * b[j][1];
+  }
+  if (weight != nullptr) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const float fa[2] = {__uint_as_float(wa[j] << 16), __uint_as_float(wa[j] & 0xffff0000u)};
+      const float fb[2] = {__uint_as_float(wb[j] << 16), __uint_as_float(wb[j] & 0xffff0000u)};
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        a[j][e] = round_to<bf16>(round_to<bf16>(a[j][e] * rstd) * fa[e]);
+        b[j][e] = round_to<bf16>(round_to<bf16>(b[j][e] * rstd) * fb[e]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < MAXJ; ++j) {
+    const int p = 2 * lane + 64 * j;
+    if (p < HALF) {
+      float ra[2] = {a[j][0], a[j][1]}, rb[2] = {b[j][0], b[j][1]};
+      if (c != nullptr) {
+        ra[0] = a[j][0] * cv[j].x - b[j][0] * sv[j].x; ra[1] = a[j][1] * cv[j].y - b[j][1] * sv[j].y;
+        rb[0] = b[j][0] * cv[j].x + a[j][0] * sv[j].x; rb[1] = b[j][1] * cv[j].y + a[j][1] * sv[j].y;
+      }
+      const uint32_t pa = dm_pack(ra[0], ra[1]), pb = dm_pack(rb[0], rb[1]);
+      *reinterpret_cast<uint32_t*>(dst0 + p) = pa;
+      *reinterpret_cast<uint32_t*>(dst0 + HALF + p) = pb;
+      if (dst1 != nullptr) {
+        *reinterpret_cast<uint32_t*>(dst1 + p) = pa;
+        *reinterpret_cast<uint32_t*>(dst1 + HALF + p) = pb;
+      }
+    }
+  }
+}
+
 // D64 = head_dim / 64 (1 or 2). BR = rows of a tensor box: 16 (page size a multiple of 16) or 8.
 // blockIdx = (request in the list, kv head * passes + pass, key range); a pass covers up to 16
 // query heads of the group.
-template <int D64, int BR>
+template <int D64, int BR, bool FUSED>
 __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                      const __grid_constant__ CUtensorMap map_v,
-                                                                     AttnArgs a, int passes, int* error_flag) {
+                                                                     AttnArgs a, FusedQkv f, int passes,
+                                                                     int* error_flag) {
   constexpr int D = D64 * 64, D16 = D / 16;
   constexpr int TILE_BYTES = DM_TK * D * 2;                 // one K (or V) tile: 16 rows, unpadded
   extern __shared__ __align__(16) unsigned char dm_raw[];
   __shared__ __align__(8) uint64_t bars[DM_WARPS][DM_STAGES];
   __shared__ int is_last;
+  __shared__ __align__(16) bf16 q_stage[FUSED ? 16 * 128 : 8];     // this CTA's query heads, ready for the mma
+  __shared__ __align__(16) bf16 new_kv[FUSED ? 2 * 128 : 8];       // the new token's key and value rows
   pdl_trigger();
   unsigned char* tiles = (unsigned char*)(((uintptr_t)dm_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,26 +223,6 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
   const int tile_begin = split * tiles_per;
   const int tile_end = min(ntiles_all, tile_begin + tiles_per);
   const int* table = a.block_tables + (size_t)seq * a.table_width;
-
-  // ---- Q fragments: row r = query head g0 + r of the group (rows beyond the group are zero)
-  uint32_t qf[D16][4];
-  {
-    const bf16* qbase = (const bf16*)a.q + ((size_t)qrow * a.num_heads + kvh * G + g0) * D;
-#pragma unroll
-    for (int kk = 0; kk < D16; ++kk) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int r = g + 8 * h;
-        uint32_t lo_w = 0u, hi_w = 0u;
-        if (r < ng) {
-          lo_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + kk * 16 + 2 * t);
-          hi_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + kk * 16 + 8 + 2 * t);
-        }
-        qf[kk][h] = lo_w;
-        qf[kk][2 + h] = hi_w;
-      }
-    }
-  }
 
   // One lane fetches a tile: the 16 positions from k0 lie in one page (BR = 16) or in two pages
   // of 8. Row of the cache matrix = (page * kv_heads + kvh) * page_size + offset in the page.
@@ -191,6 +263,63 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
     const int tile = first + s * DM_WARPS;
     if (tile < tile_end) load_tile(tile, s);
   }
+
+  // (the first tiles are on their way; the work on the queries overlaps their flight)
+  const bool owns_last = tile_begin < tile_end && tile_end == ntiles_all;   // this range ends at the newest key
+  if constexpr (FUSED) {
+    const int width = (a.num_heads + 2 * a.num_kv_heads) * D;
+    const bf16* row = f.qkv + (size_t)qrow * width;
+    const float* c = f.cos_t ? f.cos_t + (size_t)qrow * (D / 2) : nullptr;
+    const float* sn = f.sin_t ? f.sin_t + (size_t)qrow * (D / 2) : nullptr;
+    for (int r = warp; r < 16; r += DM_WARPS) {
+      if (r < ng) {
+        fused_head_row<D>(row + (size_t)(kvh * G + g0 + r) * D, f.q_weight, f.eps, c, sn, q_stage + r * D, nullptr, lane);
+      } else {
+        for (int i = lane * 8; i < D; i += 256) *reinterpret_cast<uint4*>(q_stage + r * D + i) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    if (owns_last) {
+      // the new key (normalised, rotated) and value: into the cache for later steps (once per
+      // kv head: the CTA of the first pass writes) and into shared memory for this step
+      const int slot = f.slots[qrow];
+      const int page = slot / a.page_size, off = slot - page * a.page_size;
+      const size_t at = kv_offset(page, kvh, off, a);
+      const bool writer = (g0 == 0);
+      if (warp == (ng % DM_WARPS)) {
+        fused_head_row<D>(row + (size_t)(a.num_heads + kvh) * D, f.k_weight, f.eps, c, sn, new_kv,
+                          writer ? f.k_cache + at : nullptr, lane);
+      } else if (warp == ((ng + 1) % DM_WARPS)) {
+        const bf16* vsrc = row + (size_t)(a.num_heads + a.num_kv_heads + kvh) * D;
+        for (int i = lane * 8; i < D; i += 256) {
+          const uint4 v = *reinterpret_cast<const uint4*>(vsrc + i);
+          *reinterpret_cast<uint4*>(new_kv + D + i) = v;
+          if (writer) *reinterpret_cast<uint4*>(f.v_cache + at + i) = v;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- Q fragments: row r = query head g0 + r of the group (rows beyond the group are zero)
+  uint32_t qf[D16][4];
+  {
+    const bf16* qbase = FUSED ? q_stage : (const bf16*)a.q + ((size_t)qrow * a.num_heads + kvh * G + g0) * D;
+#pragma unroll
+    for (int kk = 0; kk < D16; ++kk) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = g + 8 * h;
+        uint32_t lo_w = 0u, hi_w = 0u;
+        if (FUSED || r < ng) {
+          lo_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + kk * 16 + 2 * t);
+          hi_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + kk * 16 + 8 + 2 * t);
+        }
+        qf[kk][h] = lo_w;
+        qf[kk][2 + h] = hi_w;
+      }
+    }
+  }
+
   int n = 0;
   for (int tile = first; tile < tile_end; tile += DM_WARPS, ++n) {
     const int stage = n % DM_STAGES;
@@ -208,6 +337,21 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
           *reinterpret_cast<uint4*>(vt + (c >> 3) * 2048 + row * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
       }
       __syncwarp();
+    }
+    if constexpr (FUSED) {
+      // the newest position is not in the cache yet (another CTA or this one writes it during
+      // this very step): its rows of the tile come from shared memory
+      const int r = ctx - 1 - k0;
+      if (r >= 0 && r < DM_TK) {
+        const int c = lane & 15;
+        if (c < D / 8) {
+          unsigned char* dst_t = (lane < 16) ? kt : vt;
+          const bf16* srcp = new_kv + (lane < 16 ? 0 : D) + c * 8;
+          *reinterpret_cast<uint4*>(dst_t + (c >> 3) * 2048 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
+              *reinterpret_cast<const uint4*>(srcp);
+        }
+        __syncwarp();
+      }
     }
     // ---- S = Q K^T: 2 key tiles of 8
     float s[2][4];
@@ -378,8 +522,9 @@ static const CUtensorMap* cache_map(const void* base, long long rows, int head_d
   return &maps.emplace(key, m).first->second;
 }
 
-template <int D64, int BR>
-static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, cudaStream_t stream) {
+template <int D64, int BR, bool FUSED = false>
+static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, cudaStream_t stream,
+                     const FusedQkv& f = FusedQkv()) {
   constexpr int D = D64 * 64;
   const CUtensorMap* mk = cache_map(a.k_cache, cache_rows, D, BR);
   const CUtensorMap* mv = cache_map(a.v_cache, cache_rows, D, BR);
@@ -387,7 +532,7 @@ static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, c
   const size_t tiles = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TK * D * 2 + 1024;
   const size_t red = sizeof(float) * (size_t)DM_WARPS * 16 * (D + 2) + 1024;
   const size_t smem = tiles > red ? tiles : red;
-  auto kern = decode_attn_tma_kernel<D64, BR>;
+  auto kern = decode_attn_tma_kernel<D64, BR, FUSED>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -396,7 +541,7 @@ static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, c
   const int passes = (G + 15) / 16;
   if (a.num_splits > 1 && (long long)a.num_seqs * a.num_kv_heads * passes > DM_MAX_COUNTERS) return TS_ERR_UNSUPPORTED;
   dim3 grid(a.num_seqs, a.num_kv_heads * passes, a.num_splits);
-  return launch(kern, grid, DM_THREADS, smem, stream, *mk, *mv, a, passes, error_flag);
+  return launch(kern, grid, DM_THREADS, smem, stream, *mk, *mv, a, f, passes, error_flag);
 }
 
 }  // namespace ts
@@ -433,6 +578,48 @@ extern "C" int ts_decode_attention_tma(
     return page_size == 8 ? launch_dt<1, 8>(a, rows, error_flag, stream) : launch_dt<1, 16>(a, rows, error_flag, stream);
   }
   return page_size == 8 ? launch_dt<2, 8>(a, rows, error_flag, stream) : launch_dt<2, 16>(a, rows, error_flag, stream);
+}
+
+// The same attention for a step of decode tokens only, fed with the raw output of the qkv product:
+// the kernel normalises (per-head RMSNorm; a null weight skips it) and rotates (rotate-half over
+// the whole head; null tables skip it) the queries and the new key itself, stores the new key and
+// value at `slots`, and attends over the cache with them. qkv is [tokens, (num_heads +
+// 2 num_kv_heads) * head_dim]; cos_t/sin_t are [tokens, head_dim / 2]; a request's token is row
+// cu_q[request]. Replaces ts_qk_norm_rope_write followed by ts_decode_attention_tma.
+extern "C" int ts_decode_attention_tma_fused(
+    const void* qkv, const void* q_weight, const void* k_weight, float eps, const float* cos_t, const float* sin_t,
+    const int* slots, void* out, void* k_cache, void* v_cache, long long num_pages_total, const int* block_tables,
+    int table_width, const int* cu_q, const int* ctx_lens, const int* decode_seqs, int num_decode, int num_heads,
+    int num_kv_heads, int head_dim, int page_size, float scale, int window, int num_splits, float* part_acc,
+    float* part_ml, int* error_flag, cudaStream_t stream) {
+  if (num_decode <= 0) return 0;
+  if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
+  if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || num_splits < 1 || num_pages_total <= 0)
+    return TS_ERR_BAD_ARGUMENT;
+  if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return TS_ERR_BAD_ARGUMENT;
+  if ((cos_t == nullptr) != (sin_t == nullptr) || slots == nullptr || qkv == nullptr) return TS_ERR_BAD_ARGUMENT;
+  if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache) | ((uintptr_t)qkv)) & 15) return TS_ERR_UNSUPPORTED;
+  const long long rows = num_pages_total * num_kv_heads * page_size;
+  if (rows >= (1ll << 31)) return TS_ERR_UNSUPPORTED;
+  AttnArgs a;
+  a.q = nullptr; a.out = out; a.k_cache = k_cache; a.v_cache = v_cache;
+  a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
+  a.seq_ids = decode_seqs; a.num_seqs = num_decode;
+  a.num_heads = num_heads; a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.page_size = page_size;
+  a.page_shift = page_shift_of(page_size);
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.window = window;
+  a.num_splits = num_splits; a.part_acc = part_acc; a.part_ml = part_ml;
+  FusedQkv f;
+  f.qkv = (const bf16*)qkv; f.q_weight = (const bf16*)q_weight; f.k_weight = (const bf16*)k_weight; f.eps = eps;
+  f.cos_t = cos_t; f.sin_t = sin_t; f.slots = slots; f.k_cache = (bf16*)k_cache; f.v_cache = (bf16*)v_cache;
+  if (head_dim == 64) {
+    return page_size == 8 ? launch_dt<1, 8, true>(a, rows, error_flag, stream, f)
+                          : launch_dt<1, 16, true>(a, rows, error_flag, stream, f);
+  }
+  return page_size == 8 ? launch_dt<2, 8, true>(a, rows, error_flag, stream, f)
+                        : launch_dt<2, 16, true>(a, rows, error_flag, stream, f);
 }
 
 // How many CTAs of this kernel fit the machine at once (for the split choice).

@@ -40,6 +40,8 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_decode_attention_mma_slots": [_i],
     "ts_decode_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
                                 _i, _vp, _vp, _vp, _vp],
+    "ts_decode_attention_tma_fused": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp,
+                                      _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp],
     "ts_decode_attention_tma_slots": [_i],
     "ts_prefill_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
                                  _i, _vp, _vp],
@@ -323,6 +325,72 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         hq, hkv, d, page_size, float(scale), int(window), splits,
         _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _code(dt), _stream()), "paged_attention",
         kernels=(1 if num_prefill else 0) + (1 if ctx.num_decode else 0))
+
+
+# The fused decode kernel takes steps of up to this many decode tokens (0 turns it off), and
+# only grids of at least this many CTAs that fit the machine at once. Measured on B200 (Qwen3-0.6B
+# sizes, 1,024-token contexts): batches 4 to 48 gain 1 to 5 % of the step; smaller grids (batch 1,
+# 2) are bound by the latency of a single CTA, which the extra work at its start lengthens, and
+# larger ones (batch 56, 64) repeat that work in a second round of CTAs; both lose 1 to 4 %.
+FUSED_DECODE_MAX_ROWS = 1 << 30
+FUSED_DECODE_MIN_CTAS = 256
+
+
+def can_fuse_decode(ctx: Any, dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                    pages: int, rotary_dim: int, interleaved: bool, device: torch.device) -> bool:
+    """Whether :func:`decode_attention_fused` takes this step and gains from it: decode tokens
+    only, bf16, a head of 64 or 128, pages of 8 or a multiple of 16 positions, the whole head
+    rotated with the rotate-half pairing (or no rotation at all), and a grid that fills the machine
+    once. Depends only on the shape of the step, as the choice of the key ranges does."""
+    if not (device.type == "cuda" and ctx.num_prefill == 0 and 0 < ctx.num_decode <= FUSED_DECODE_MAX_ROWS
+            and dtype == torch.bfloat16 and head_dim in (64, 128) and (page_size == 8 or page_size % 16 == 0)
+            and pages * num_kv_heads * page_size < 2 ** 31
+            and (rotary_dim == 0 or (rotary_dim == head_dim and not interleaved))):
+        return False
+    ctas = ctx.num_decode * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
+    slots = _decode_slots(head_dim, True)
+    grid = ctas * choose_splits(ctas, slots, ctx.max_context_len // 64)
+    return min(FUSED_DECODE_MIN_CTAS, slots) <= grid <= slots
+
+
+def decode_attention_fused(qkv: torch.Tensor, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+                           eps: float, cos: torch.Tensor | None, sin: torch.Tensor | None, slots: torch.Tensor,
+                           k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
+                           block_tables: torch.Tensor, ctx: Any, scale: float, window: int, num_heads: int,
+                           out: torch.Tensor) -> None:
+    """:func:`qk_norm_rope_write` and :func:`paged_attention` of a step of decode tokens in one
+    kernel: ``qkv`` ``[T, (Hq + 2 Hkv) * D]`` bf16 is the raw output of the qkv product; the new
+    keys and values go to the cache at ``slots``; ``out`` ``[T, Hq * D]``. One query per request,
+    no intermediate query tensor. Call only when :func:`can_fuse_decode` says so."""
+    t = qkv.shape[0]
+    hkv, d = k_cache.shape[1], k_cache.shape[3]
+    dt = torch.bfloat16
+    if qkv.dtype != dt or k_cache.dtype != dt or v_cache.dtype != dt or out.dtype != dt:
+        raise KernelError("decode_attention_fused: bfloat16 only")
+    if tuple(k_cache.shape[1:]) != (hkv, page_size, d) or k_cache.shape != v_cache.shape:
+        raise KernelError("decode_attention_fused: cache layout must be [pages, kv_heads, page_size, head_dim]")
+    if num_heads % hkv or qkv.shape != (t, (num_heads + 2 * hkv) * d) or out.numel() != t * num_heads * d:
+        raise KernelError("decode_attention_fused: qkv/out shape or head grouping")
+    if ctx.num_prefill or ctx.num_decode != t or block_tables.shape[0] != ctx.num_seqs or slots.shape != (t,):
+        raise KernelError("decode_attention_fused: a step of decode tokens only, one token per request")
+    if (cos is None) != (sin is None) or (cos is not None and tuple(cos.shape) != (t, d // 2)):
+        raise KernelError("decode_attention_fused: rotary tables must be [tokens, head_dim / 2]")
+    ctas = t * hkv * (-(-(num_heads // hkv) // 16))
+    splits = choose_splits(ctas, _decode_slots(d, True), ctx.max_context_len // 64)
+    part_acc = part_ml = None
+    if splits > 1:
+        part_acc = ctx.arena.take((t, num_heads, splits, d), torch.float32)
+        part_ml = ctx.arena.take((t, num_heads, splits, 2), torch.float32)
+    _check(_fn("ts_decode_attention_tma_fused")(
+        _dev(qkv, "qkv"), _opt(q_weight, "q_weight", dt), _opt(k_weight, "k_weight", dt), float(eps),
+        _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), _dev(slots, "slots", torch.int32),
+        _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), k_cache.shape[0],
+        _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
+        _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+        _dev(ctx.context_lens_dev, "context_lens", torch.int32),
+        _dev(ctx.decode_seqs, "decode_seqs", torch.int32), t, num_heads, hkv, d, page_size, float(scale),
+        int(window), splits, _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"),
+        _error_word(qkv.device).data_ptr(), _stream()), "decode_attention_tma_fused")
 
 
 _slots_cache: dict[tuple[int, bool], int] = {}

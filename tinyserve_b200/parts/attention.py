@@ -72,19 +72,25 @@ class GQAAttention(Mixer):
         width = self.q_size + 2 * self.kv_size if writes_cache else self.q_size
         qkv = arena.take((t, width), ctx.dtype)
         ops.gemm(x, self.w_qkv if writes_cache else self.w_q, qkv)
-        q = arena.take((t, self.num_heads, self.head_dim), ctx.dtype)
-        ops.qk_norm_rope_write(
-            qkv, q, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
-            None if position is None else position.cos,
-            None if position is None else position.sin,
-            0 if position is None else position.rotary_dim,
-            False if position is None else position.interleaved,
-            group.slots, cache.k, cache.v, cache.page_size,
-            self.num_heads, self.num_kv_heads, self.head_dim, writes_cache,
-        )
+        cos = None if position is None else position.cos
+        sin = None if position is None else position.sin
+        rotary_dim = 0 if position is None else position.rotary_dim
+        interleaved = False if position is None else position.interleaved
         attn = arena.take((t, self.q_size), ctx.dtype)
-        ops.paged_attention(q, cache.k, cache.v, cache.page_size, group.block_tables, ctx,
-                            self.scale, self.window or 0, attn)
+        if writes_cache and ops.can_fuse_decode(ctx, ctx.dtype, self.num_heads, self.num_kv_heads, self.head_dim,
+                                                cache.page_size, cache.k.shape[0], rotary_dim, interleaved,
+                                                x.device):
+            # decode tokens only: norm, rotation, cache write and attention in one kernel
+            ops.decode_attention_fused(qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, cos, sin, group.slots,
+                                       cache.k, cache.v, cache.page_size, group.block_tables, ctx, self.scale,
+                                       self.window or 0, self.num_heads, attn)
+        else:
+            q = arena.take((t, self.num_heads, self.head_dim), ctx.dtype)
+            ops.qk_norm_rope_write(qkv, q, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, cos, sin, rotary_dim,
+                                   interleaved, group.slots, cache.k, cache.v, cache.page_size,
+                                   self.num_heads, self.num_kv_heads, self.head_dim, writes_cache)
+            ops.paged_attention(q, cache.k, cache.v, cache.page_size, group.block_tables, ctx,
+                                self.scale, self.window or 0, attn)
         out = arena.take((t, self.hidden_size), ctx.dtype)
         ops.gemm(attn, self.w_o, out)
         return out
