@@ -1,0 +1,476 @@
+// Varlen causal prefill attention over the paged cache on the 5th-generation tensor cores (bf16,
+// head sizes 64 and 128, page sizes 8 or a multiple of 16). Same math as attention_mma.cu
+// (upstream src/tinyserve/attention.py:89-111, src/tinyserve/triton_prefill.py:50-125):
+// S = Q K^T * scale, causal (and window) mask, softmax in 32-bit, O = P V.
+//
+// A CTA owns 128 consecutive tokens of one request for NQ query heads of one kv group (NQ = 1 or
+// 2; the heads of a group share the key and value tiles). Both products run as tcgen05.mma with
+// the accumulators in tensor memory:
+//   S_q = Q_q K^T : A = Q_q  [128 x D]   K-major, shared memory, 128-byte swizzle
+//                   B = K    [BN x D]    K-major, the cache rows as TMA delivers them
+//   O_q += P_q V  : A = P_q  [128 x BN]  K-major, written to shared memory by the softmax warps
+//                   B = V    [BN x D]    read as it lies in the cache: MN-major (D contiguous)
+// Roles:
+//   warps 0 .. 4 NQ - 1 : softmax; four warps per query head, one thread per row: reads its row of
+//                         S from tensor memory (tcgen05.ld), masks, keeps the running maximum and
+//                         sum, writes P as bf16 into the swizzled operand layout, and scales O in
+//                         tensor memory only when the maximum has grown by more than 2^8 (the
+//                         sum and O then simply carry a common factor that the final division
+//                         removes); at the end divides O by the sum and stores it
+//   warp 4 NQ           : TMA producer: K and V tiles of BN positions, double-buffered, a box per
+//                         page part and 64 columns, one lane per box
+//   warp 4 NQ + 1       : allocates tensor memory; one lane issues every tcgen05.mma and the
+//                         tcgen05.commit that tells the other roles what has finished; zeroes V
+//                         rows outside the live key range (0 x garbage would not be 0)
+// Every wait is bounded and gives up at once when another role has: the CTA then records the
+// failure in *error_flag, waits for its copies in flight, frees its tensor memory and returns.
+#define TS_PDL_CLASS PDL_ATTENTION
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "attention.cuh"
+#include "tcgen05.cuh"
+
+namespace ts {
+
+constexpr int FA_BM = 128;
+constexpr int FA_KV_STAGES = 2;
+constexpr int FA_PBUF = 2;
+constexpr float FA_RESCALE_STEP = 8.f;      // log2 of the growth of a row maximum that is tolerated without scaling O
+
+__device__ __forceinline__ float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// A wait of a whole warp with one outcome for all its lanes.
+__device__ __forceinline__ bool fa_warp_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  return __all_sync(0xffffffffu, mbar_wait_or_fail(bar, parity, failed) ? 1 : 0) != 0;
+}
+
+template <int D64, int BR, int NQ, int BN>
+struct FaLayout {
+  static constexpr int D = 64 * D64;
+  static constexpr uint32_t Q_BYTES = FA_BM * D * 2;          // per query head
+  static constexpr uint32_t KV_BYTES = BN * D * 2;            // one K or V tile
+  static constexpr uint32_t P_BYTES = FA_BM * BN * 2;
+  static constexpr uint32_t OFF_Q = 0;
+  static constexpr uint32_t OFF_K = OFF_Q + NQ * Q_BYTES;
+  static constexpr uint32_t OFF_V = OFF_K + FA_KV_STAGES * KV_BYTES;
+  static constexpr uint32_t OFF_P = OFF_V + FA_KV_STAGES * KV_BYTES;
+  static constexpr uint32_t TOTAL = OFF_P + NQ * FA_PBUF * P_BYTES;
+  static constexpr uint32_t TMEM_PER_Q = BN + D;              // S then O
+  static constexpr uint32_t TMEM_NEED = NQ * TMEM_PER_Q;
+  static constexpr uint32_t TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
+  static constexpr int THREADS = (4 * NQ + 2) * 32;
+};
+
+template <int D64, int BR, int NQ, int BN>
+__global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                            const __grid_constant__ CUtensorMap map_v,
+                                                                            AttnArgs a, int* error_flag) {
+  using L = FaLayout<D64, BR, NQ, BN>;
+  constexpr int D = L::D;
+  constexpr int SOFTMAX_WARPS = 4 * NQ;
+  // instruction descriptors: D = f32, A = B = bf16, M = 128; S: N = BN, both operands K-major;
+  // PV: N = D, B MN-major (bit 16)
+  constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
+  constexpr uint32_t IDESC_PV =
+      (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
+  extern __shared__ unsigned char fa_raw[];
+  __shared__ __align__(8) uint64_t k_full[FA_KV_STAGES], k_empty[FA_KV_STAGES], v_full[FA_KV_STAGES], v_empty[FA_KV_STAGES];
+  __shared__ __align__(8) uint64_t s_full[NQ], s_free[NQ], p_full[NQ][FA_PBUF], pv_done[NQ][FA_PBUF], q_ready;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int failed_flag;
+  volatile int* failed = &failed_flag;
+
+  // ---- which rows and keys (uniform over the CTA); a CTA without rows leaves before any set-up
+  const int seq = a.seq_ids[blockIdx.z];
+  const int ctx = a.ctx_lens[seq];
+  const int q_start = a.cu_q[seq];
+  const int q_len = a.cu_q[seq + 1] - q_start;
+  const int ntq = (q_len + FA_BM - 1) / FA_BM;
+  if ((int)blockIdx.x >= ntq) return;
+  const int tile_q = ntq - 1 - (int)blockIdx.x;               // the longest rows first
+  const int q0 = tile_q * FA_BM;
+  const int valid = min(FA_BM, q_len - q0);
+  const int p_lo = ctx - q_len + q0;                          // position of row 0
+  const int p_hi = p_lo + valid - 1;                          // position of the last live row
+  const int lo = a.window > 0 ? max(0, p_lo - a.window + 1) : 0;   // first key any row sees
+  const int t_begin = lo / BN;
+  const int n_tiles = (p_hi + 1 + BN - 1) / BN - t_begin;     // >= 1
+  const int head0 = (int)blockIdx.y * NQ;
+  const int kvh = head0 / (a.num_heads / a.num_kv_heads);
+
+  pdl_trigger();
+  unsigned char* smem = (unsigned char*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < FA_KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    for (int q = 0; q < NQ; ++q) {
+      mbar_init(&s_full[q], 1); mbar_init(&s_free[q], 4);
+      for (int b = 0; b < FA_PBUF; ++b) { mbar_init(&p_full[q][b], 4); mbar_init(&pv_done[q][b], 1); }
+    }
+    mbar_init(&q_ready, SOFTMAX_WARPS);
+    failed_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == SOFTMAX_WARPS + 1) tmem_alloc(&tmem_base_slot, L::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  pdl_wait();      // q and the cache rows of this step are written by the kernels before
+
+  if (warp < SOFTMAX_WARPS) {
+    // =========================================================== softmax warps of query head q
+    const int q = warp >> 2, quad = warp & 3;
+    const int r = quad * 32 + lane;                            // this thread's row
+    const int head = head0 + q;
+    unsigned char* q_tile = smem + L::OFF_Q + q * L::Q_BYTES;
+    {
+      // Q rows into the swizzled operand layout: 16 (or 8) lanes fetch a row, 16 bytes each
+      constexpr int CPR = D / 8;                               // 16-byte chunks per row
+      const int tq = threadIdx.x & 127;
+      const int c = tq % CPR;
+      for (int row = tq / CPR; row < FA_BM; row += 128 / CPR) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < valid)
+          v = *reinterpret_cast<const uint4*>((const bf16*)a.q + ((size_t)(q_start + q0 + row) * a.num_heads + head) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_tile + (c >> 3) * (FA_BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_ready);
+    }
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_addr + (uint32_t)(q * L::TMEM_PER_Q);
+    const uint32_t tmem_o = tmem_s + BN;
+    const int p_abs = p_lo + r;
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!fa_warp_wait(&s_full[q], j & 1, failed)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sraw[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tmem_ld_32_nowait(tmem_s + c * 32, sraw + c * 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[q]);                  // S may be overwritten by the next tile's product
+      const int k0 = (t_begin + j) * BN;
+      const bool edge = (k0 + BN - 1 > p_lo) || (a.window > 0 && k0 < p_lo + FA_BM - a.window);
+      float mx = -INFINITY;
+      if (edge) {
+        const int first = a.window > 0 ? p_abs - a.window + 1 : 0;
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const int kpos = k0 + i;
+          const float v = (kpos <= p_abs && kpos >= first) ? __uint_as_float(sraw[i]) : -INFINITY;
+          sraw[i] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) mx = fmaxf(mx, __uint_as_float(sraw[i]));
+      }
+      const float m_new = fmaxf(m_used, mx * a.scale_log2);
+      if (j == 0) {
+        m_used = m_new;
+      } else {
+        const bool grow = m_new > m_used + FA_RESCALE_STEP;    // also when nothing was seen before (-inf)
+        if (__any_sync(0xffffffffu, grow)) {
+          // O of this head is final up to tile j - 1 before it is scaled
+          if (!fa_warp_wait(&pv_done[q][(j - 1) % FA_PBUF], ((j - 1) / FA_PBUF) & 1, failed)) { ok = false; break; }
+          tc_fence_after();
+          const float alpha = grow ? (m_used == -INFINITY ? 0.f : fa_exp2(m_used - m_new)) : 1.f;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32(tmem_o + c * 32, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32(tmem_o + c * 32, o);
+          }
+          tc_fence_before();
+          if (grow) { l_sum *= alpha; m_used = m_new; }
+        }
+      }
+      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      float add = 0.f;
+#pragma unroll
+      for (int i = 0; i < BN; ++i) {
+        const float p = fa_exp2(fmaf(__uint_as_float(sraw[i]), a.scale_log2, -m_sub));
+        add += p;
+        sraw[i] = __float_as_uint(p);
+      }
+      l_sum += add;
+      const int pb = j % FA_PBUF;
+      if (j >= FA_PBUF) {
+        // the product that read this P buffer two tiles ago must be done
+        if (!fa_warp_wait(&pv_done[q][pb], ((j / FA_PBUF) - 1) & 1, failed)) { ok = false; break; }
+      }
+      unsigned char* p_tile = smem + L::OFF_P + (q * FA_PBUF + pb) * L::P_BYTES;
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) {
+        uint4 v;
+        v.x = fa_pack(__uint_as_float(sraw[c * 8 + 0]), __uint_as_float(sraw[c * 8 + 1]));
+        v.y = fa_pack(__uint_as_float(sraw[c * 8 + 2]), __uint_as_float(sraw[c * 8 + 3]));
+        v.z = fa_pack(__uint_as_float(sraw[c * 8 + 4]), __uint_as_float(sraw[c * 8 + 5]));
+        v.w = fa_pack(__uint_as_float(sraw[c * 8 + 6]), __uint_as_float(sraw[c * 8 + 7]));
+        *reinterpret_cast<uint4*>(p_tile + (c >> 3) * (FA_BM * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[q][pb]);
+    }
+    if (ok) {
+      const int last = n_tiles - 1;
+      ok = fa_warp_wait(&pv_done[q][last % FA_PBUF], (last / FA_PBUF) & 1, failed);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.f / l_sum;
+      bf16* dst = (bf16*)a.out + ((size_t)(q_start + q0 + r) * a.num_heads + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32(tmem_o + c * 32, o);
+        if (r < valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = fa_pack(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
+            v.y = fa_pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            v.z = fa_pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            v.w = fa_pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+          }
+        }
+      }
+    }
+  } else if (warp == SOFTMAX_WARPS) {
+    // =========================================================== TMA producer
+    const int* table = a.block_tables + (size_t)seq * a.table_width;
+    constexpr int PARTS = BN / BR;
+    constexpr int COPIES = PARTS * D64;                         // per tile; one lane each, in rounds of 32
+    const int kmin = lo & ~(BR - 1), kmax = (ctx - 1) & ~(BR - 1);
+    bool ok = true;
+    int issued_k = 0, issued_v = 0;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j % FA_KV_STAGES;
+      const uint32_t ph = (j / FA_KV_STAGES) & 1;
+      const int k0 = (t_begin + j) * BN;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        uint64_t* full = which == 0 ? &k_full[st] : &v_full[st];
+        uint64_t* empty = which == 0 ? &k_empty[st] : &v_empty[st];
+        int good = 1;
+        if (lane == 0) {
+          good = mbar_wait_or_fail(empty, ph ^ 1, failed) ? 1 : 0;
+          if (good) mbar_expect_tx(full, L::KV_BYTES);
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) { ok = false; break; }
+        unsigned char* dst = smem + (which == 0 ? L::OFF_K : L::OFF_V) + st * L::KV_BYTES;
+        for (int cpy = lane; cpy < COPIES; cpy += 32) {
+          const int part = cpy / D64, h = cpy - part * D64;
+          // a part wholly outside the live keys is fetched from the nearest live part (its
+          // scores are masked and its value rows zeroed); every part lies within one page
+          int kpos = min(max(k0 + part * BR, kmin), kmax);
+          int page, off;
+          if (a.page_shift >= 0) { page = table[kpos >> a.page_shift]; off = kpos & (a.page_size - 1); }
+          else { const int idx = kpos / a.page_size; page = table[idx]; off = kpos - idx * a.page_size; }
+          const int y = (page * a.num_kv_heads + kvh) * a.page_size + off;
+          tma_load_2d(dst + h * (BN * 128) + part * (BR * 128), which == 0 ? &map_k : &map_v, full, h * 64, y);
+        }
+        if (which == 0) issued_k = j + 1; else issued_v = j + 1;
+      }
+    }
+    if (!ok && lane == 0) {
+      // leave no copy in flight: the last phases armed on every stage must complete
+      for (int back = 0; back < FA_KV_STAGES; ++back) {
+        const int jk = issued_k - 1 - back, jv = issued_v - 1 - back;
+        if (jk >= 0) mbar_wait(&k_full[jk % FA_KV_STAGES], (jk / FA_KV_STAGES) & 1);
+        if (jv >= 0) mbar_wait(&v_full[jv % FA_KV_STAGES], (jv / FA_KV_STAGES) & 1);
+      }
+    }
+  } else {
+    // =========================================================== MMA issuer
+    bool ok = fa_warp_wait(&q_ready, 0, failed);
+    const uint32_t q_addr = smem_u32(smem + L::OFF_Q);
+    const uint32_t k_addr = smem_u32(smem + L::OFF_K), v_addr = smem_u32(smem + L::OFF_V);
+    const uint32_t p_addr = smem_u32(smem + L::OFF_P);
+    // S_q = Q_q K^T of tile j (all query heads), then the K stage is handed back
+    auto issue_s = [&](int j) -> bool {
+      const int st = j % FA_KV_STAGES;
+      if (!fa_warp_wait(&k_full[st], (j / FA_KV_STAGES) & 1, failed)) return false;
+      for (int q = 0; q < NQ; ++q) {
+        if (j > 0 && !fa_warp_wait(&s_free[q], (j - 1) & 1, failed)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint64_t ad = sw128_desc(q_addr + q * L::Q_BYTES + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32);
+            const uint64_t bd = sw128_desc(k_addr + st * L::KV_BYTES + (ks >> 2) * (BN * 128) + (ks & 3) * 32);
+            umma_bf16(tmem_base + (uint32_t)(q * L::TMEM_PER_Q), ad, bd, IDESC_S, ks != 0);
+          }
+          umma_commit(&s_full[q]);
+        }
+        __syncwarp();
+      }
+      if (lane == 0) umma_commit(&k_empty[st]);
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_s(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles) {
+        ok = issue_s(j + 1);
+        if (!ok) break;
+      }
+      const int st = j % FA_KV_STAGES;
+      if (!fa_warp_wait(&v_full[st], (j / FA_KV_STAGES) & 1, failed)) { ok = false; break; }
+      const int k0 = (t_begin + j) * BN;
+      if (k0 < lo || k0 + BN > ctx) {
+        // value rows of positions outside [lo, ctx) may hold anything: zero them (their P is 0)
+        unsigned char* v_tile = smem + L::OFF_V + st * L::KV_BYTES;
+        for (int idx = lane; idx < BN * D64 * 8; idx += 32) {
+          const int row = idx / (D64 * 8), c = idx - row * (D64 * 8);
+          const int kpos = k0 + row;
+          if (kpos < lo || kpos >= ctx)
+            *reinterpret_cast<uint4*>(v_tile + (c >> 3) * (BN * 128) + row * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
+      for (int q = 0; q < NQ && ok; ++q) {
+        const int pb = j % FA_PBUF;
+        if (!fa_warp_wait(&p_full[q][pb], (j / FA_PBUF) & 1, failed)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+#pragma unroll
+          for (int ks = 0; ks < BN / 16; ++ks) {
+            const uint64_t ad = sw128_desc(p_addr + (q * FA_PBUF + pb) * L::P_BYTES + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32);
+            const uint64_t bd = sw128_desc_mn(v_addr + st * L::KV_BYTES + ks * (16 * 128), BN * 128);
+            umma_bf16(tmem_base + (uint32_t)(q * L::TMEM_PER_Q + BN), ad, bd, IDESC_PV, (j | ks) != 0);
+          }
+          umma_commit(&pv_done[q][pb]);
+        }
+        __syncwarp();
+      }
+      if (lane == 0) umma_commit(&v_empty[st]);
+      __syncwarp();
+    }
+  }
+  if (*failed && (threadIdx.x & 31) == 0) atomicExch(error_flag, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The descriptor of one cache tensor ([rows, head_dim] bf16, boxes of box_rows x 64, 128-byte
+// swizzle), kept per (address, rows, head_dim, box_rows): a cache tensor is allocated once.
+static const CUtensorMap* fa_cache_map(const void* base, long long rows, int head_dim, int box_rows) {
+  static std::mutex mu;
+  static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> maps;
+  static FaEncodeFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_tuple(base, rows, head_dim, box_rows);
+  auto it = maps.find(key);
+  if (it != maps.end()) return &it->second;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = (FaEncodeFn)p;
+  }
+  CUtensorMap m;
+  cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return nullptr;
+  return &maps.emplace(key, m).first->second;
+}
+
+template <int D64, int BR, int NQ, int BN>
+static int launch_fa(const AttnArgs& a, long long cache_rows, int max_query_len, int* error_flag, cudaStream_t stream) {
+  using L = FaLayout<D64, BR, NQ, BN>;
+  const CUtensorMap* mk = fa_cache_map(a.k_cache, cache_rows, L::D, BR);
+  const CUtensorMap* mv = fa_cache_map(a.v_cache, cache_rows, L::D, BR);
+  if (mk == nullptr || mv == nullptr) return TS_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)L::TOTAL + 1024;
+  auto kern = prefill_attn_tc_kernel<D64, BR, NQ, BN>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid((max_query_len + FA_BM - 1) / FA_BM, a.num_heads / NQ, a.num_seqs);
+  return launch(kern, grid, L::THREADS, smem, stream, *mk, *mv, a, error_flag);
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+// bf16 prefill attention on tcgen05 for the requests listed in prefill_seqs. head_dim 64 or 128;
+// page_size 8 or a multiple of 16; num_pages_total = pages of the cache tensors (the pad page
+// included). heads_per_cta: 1 or 2 query heads of a kv group share a CTA's key and value tiles
+// (2 needs an even group); 0 picks 2 where it can. Returns TS_ERR_UNSUPPORTED for sizes it does
+// not take.
+extern "C" int ts_prefill_attention_tcgen05(
+    const void* q, void* out, const void* k_cache, const void* v_cache, long long num_pages_total,
+    const int* block_tables, int table_width, const int* cu_q, const int* ctx_lens, const int* prefill_seqs,
+    int num_prefill, int max_query_len, int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
+    int window, int heads_per_cta, int* error_flag, cudaStream_t stream) {
+  if (num_prefill <= 0 || max_query_len <= 0) return 0;
+  if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
+  if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || num_pages_total <= 0) return TS_ERR_BAD_ARGUMENT;
+  if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache) | ((uintptr_t)q) | ((uintptr_t)out)) & 15) return TS_ERR_UNSUPPORTED;
+  const long long rows = num_pages_total * num_kv_heads * page_size;
+  if (rows >= (1ll << 31)) return TS_ERR_UNSUPPORTED;
+  const int group = num_heads / num_kv_heads;
+  if (heads_per_cta == 0) heads_per_cta = (group % 2 == 0) ? 2 : 1;
+  if (heads_per_cta != 1 && heads_per_cta != 2) return TS_ERR_BAD_ARGUMENT;
+  if (heads_per_cta == 2 && group % 2 != 0) return TS_ERR_UNSUPPORTED;
+  AttnArgs a;
+  a.q = q; a.out = out; a.k_cache = k_cache; a.v_cache = v_cache;
+  a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
+  a.seq_ids = prefill_seqs; a.num_seqs = num_prefill;
+  a.num_heads = num_heads; a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.page_size = page_size;
+  a.page_shift = page_shift_of(page_size);
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.window = window;
+  a.num_splits = 1; a.part_acc = nullptr; a.part_ml = nullptr;
+#define TS_FA(D64_, BR_)                                                                                   \
+  return heads_per_cta == 2 ? launch_fa<D64_, BR_, 2, 64>(a, rows, max_query_len, error_flag, stream)      \
+                            : launch_fa<D64_, BR_, 1, 128>(a, rows, max_query_len, error_flag, stream)
+  if (head_dim == 64) {
+    if (page_size == 8) { TS_FA(1, 8); }
+    TS_FA(1, 16);
+  }
+  if (page_size == 8) { TS_FA(2, 8); }
+  TS_FA(2, 16);
+#undef TS_FA
+}

@@ -45,6 +45,8 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_decode_attention_tma_slots": [_i],
     "ts_prefill_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
                                  _i, _vp, _vp],
+    "ts_prefill_attention_tcgen05": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                     _f, _i, _i, _vp, _vp],
     "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
@@ -210,6 +212,12 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: torch.T
 
 
 # -------------------------------------------------------------------- attention
+# The bf16 prefill kernel for head sizes 64 / 128: "tcgen05" (tensor memory accumulators) or "mma"
+# (mma.sync with TMA tiles); and how many query heads of a kv group share a CTA of the former
+# (0: two where the group is even; measured on B200 at 16 / 8 heads of 128: one head with tiles of
+# 128 keys beats two heads with tiles of 64 by 10 to 20 %).
+PREFILL_ATTENTION = "tcgen05"
+PREFILL_HEADS_PER_CTA = 1
 TARGET_DECODE_CTAS = 148 * 4
 MIN_KEYS_PER_SPLIT = 64
 MAX_SPLITS = 32
@@ -262,7 +270,18 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
               and k_cache.shape[0] * hkv * page_size < 2 ** 31)
     if num_prefill and dt == torch.bfloat16 and d <= 128:
         # prefill rows on the tensor cores; the decode rows follow below
-        if tma_ok:
+        if tma_ok and PREFILL_ATTENTION == "tcgen05":
+            # both products as tcgen05.mma with the accumulators in tensor memory
+            _check(_fn("ts_prefill_attention_tcgen05")(
+                _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), k_cache.shape[0],
+                _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
+                _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+                _dev(ctx.context_lens_dev, "context_lens", torch.int32),
+                _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
+                hq, hkv, d, page_size, float(scale), int(window),
+                PREFILL_HEADS_PER_CTA if (hq // hkv) % 2 == 0 else 1,
+                _error_word(q.device).data_ptr(), _stream()), "prefill_attention_tcgen05")
+        elif tma_ok:
             _check(_fn("ts_prefill_attention_tma")(
                 _dev(q, "q"), _dev(out, "out"), _dev(k_cache, "k_cache"), _dev(v_cache, "v_cache"), k_cache.shape[0],
                 _dev(block_tables, "block_tables", torch.int32), block_tables.shape[1],
