@@ -51,6 +51,13 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+#ifdef TS_FA_TIMING
+__device__ unsigned long long fa_prof[16];
+#define FA_T(i) do { const long long now_ = clock64(); t_acc[i] += now_ - t_prev; t_prev = now_; } while (0)
+#else
+#define FA_T(i) do { } while (0)
+#endif
+
 // A wait of a whole warp with one outcome for all its lanes.
 __device__ __forceinline__ bool fa_warp_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
   return __all_sync(0xffffffffu, mbar_wait_or_fail(bar, parity, failed) ? 1 : 0) != 0;
@@ -98,8 +105,8 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
   const int q_start = a.cu_q[seq];
   const int q_len = a.cu_q[seq + 1] - q_start;
   const int ntq = (q_len + FA_BM - 1) / FA_BM;
-  if ((int)blockIdx.x >= ntq) return;
-  const int tile_q = ntq - 1 - (int)blockIdx.x;               // the longest rows first
+  if ((int)blockIdx.y >= ntq) return;
+  const int tile_q = ntq - 1 - (int)blockIdx.y;               // the longest rows first, for every head
   const int q0 = tile_q * FA_BM;
   const int valid = min(FA_BM, q_len - q0);
   const int p_lo = ctx - q_len + q0;                          // position of row 0
@@ -107,10 +114,15 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
   const int lo = a.window > 0 ? max(0, p_lo - a.window + 1) : 0;   // first key any row sees
   const int t_begin = lo / BN;
   const int n_tiles = (p_hi + 1 + BN - 1) / BN - t_begin;     // >= 1
-  const int head0 = (int)blockIdx.y * NQ;
+  const int head0 = (int)blockIdx.x * NQ;
   const int kvh = head0 / (a.num_heads / a.num_kv_heads);
 
   pdl_trigger();
+#ifdef TS_FA_TIMING
+  long long t_acc[13] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  long long t_prev = clock64();
+  const long long t_enter = t_prev;
+#endif
   unsigned char* smem = (unsigned char*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -131,6 +143,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   pdl_wait();      // q and the cache rows of this step are written by the kernels before
+  FA_T(8);
 
   if (warp < SOFTMAX_WARPS) {
     // =========================================================== softmax warps of query head q
@@ -141,13 +154,21 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
     {
       // Q rows into the swizzled operand layout: 16 (or 8) lanes fetch a row, 16 bytes each
       constexpr int CPR = D / 8;                               // 16-byte chunks per row
+      constexpr int RPP = 128 / CPR, PASSES = FA_BM / RPP;     // rows per pass of the 128 threads
       const int tq = threadIdx.x & 127;
-      const int c = tq % CPR;
-      for (int row = tq / CPR; row < FA_BM; row += 128 / CPR) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      const int c = tq % CPR, row0 = tq / CPR;
+      uint4 v[PASSES];
+#pragma unroll
+      for (int i = 0; i < PASSES; ++i) {                       // every load in flight before the first store
+        const int row = row0 + i * RPP;
+        v[i] = make_uint4(0u, 0u, 0u, 0u);
         if (row < valid)
-          v = *reinterpret_cast<const uint4*>((const bf16*)a.q + ((size_t)(q_start + q0 + row) * a.num_heads + head) * D + c * 8);
-        *reinterpret_cast<uint4*>(q_tile + (c >> 3) * (FA_BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+          v[i] = *reinterpret_cast<const uint4*>((const bf16*)a.q + ((size_t)(q_start + q0 + row) * a.num_heads + head) * D + c * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < PASSES; ++i) {
+        const int row = row0 + i * RPP;
+        *reinterpret_cast<uint4*>(q_tile + (c >> 3) * (FA_BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v[i];
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -159,9 +180,12 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
     const int p_abs = p_lo + r;
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
+    FA_T(9);
     for (int j = 0; j < n_tiles; ++j) {
+      FA_T(0);
       if (!fa_warp_wait(&s_full[q], j & 1, failed)) { ok = false; break; }
       tc_fence_after();
+      FA_T(1);
       uint32_t sraw[BN];
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld_32_nowait(tmem_s + c * 32, sraw + c * 32);
@@ -169,9 +193,10 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[q]);                  // S may be overwritten by the next tile's product
+      FA_T(2);
       const int k0 = (t_begin + j) * BN;
       const bool edge = (k0 + BN - 1 > p_lo) || (a.window > 0 && k0 < p_lo + FA_BM - a.window);
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: the maxima do not wait on one another
       if (edge) {
         const int first = a.window > 0 ? p_abs - a.window + 1 : 0;
 #pragma unroll
@@ -179,13 +204,15 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
           const int kpos = k0 + i;
           const float v = (kpos <= p_abs && kpos >= first) ? __uint_as_float(sraw[i]) : -INFINITY;
           sraw[i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          mx4[i & 3] = fmaxf(mx4[i & 3], v);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < BN; ++i) mx = fmaxf(mx, __uint_as_float(sraw[i]));
+        for (int i = 0; i < BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sraw[i]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * a.scale_log2);
+      FA_T(3);
       if (j == 0) {
         m_used = m_new;
       } else {
@@ -207,20 +234,24 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
           if (grow) { l_sum *= alpha; m_used = m_new; }
         }
       }
+      FA_T(4);
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      float add = 0.f;
+      float add4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < BN; ++i) {
         const float p = fa_exp2(fmaf(__uint_as_float(sraw[i]), a.scale_log2, -m_sub));
-        add += p;
+        add4[i & 3] += p;
         sraw[i] = __float_as_uint(p);
       }
+      const float add = (add4[0] + add4[1]) + (add4[2] + add4[3]);
       l_sum += add;
+      FA_T(5);
       const int pb = j % FA_PBUF;
       if (j >= FA_PBUF) {
         // the product that read this P buffer two tiles ago must be done
         if (!fa_warp_wait(&pv_done[q][pb], ((j / FA_PBUF) - 1) & 1, failed)) { ok = false; break; }
       }
+      FA_T(6);
       unsigned char* p_tile = smem + L::OFF_P + (q * FA_PBUF + pb) * L::P_BYTES;
 #pragma unroll
       for (int c = 0; c < BN / 8; ++c) {
@@ -234,11 +265,13 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[q][pb]);
+      FA_T(7);
     }
     if (ok) {
       const int last = n_tiles - 1;
       ok = fa_warp_wait(&pv_done[q][last % FA_PBUF], (last / FA_PBUF) & 1, failed);
     }
+    FA_T(10);
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l_sum;
@@ -374,10 +407,18 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       __syncwarp();
     }
   }
+  FA_T(11);
   if (*failed && (threadIdx.x & 31) == 0) atomicExch(error_flag, 1);
   tc_fence_before();
   __syncthreads();
   if (warp == SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
+  FA_T(12);
+#ifdef TS_FA_TIMING
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 13; ++i) atomicAdd(&fa_prof[i], (unsigned long long)t_acc[i]);
+    atomicAdd(&fa_prof[14], (unsigned long long)(clock64() - t_enter)); atomicAdd(&fa_prof[15], 1ull);
+  }
+#endif
 }
 
 // ---------------------------------------------------------------- host side
@@ -425,13 +466,24 @@ static int launch_fa(const AttnArgs& a, long long cache_rows, int max_query_len,
   auto kern = prefill_attn_tc_kernel<D64, BR, NQ, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((max_query_len + FA_BM - 1) / FA_BM, a.num_heads / NQ, a.num_seqs);
+  dim3 grid(a.num_heads / NQ, (max_query_len + FA_BM - 1) / FA_BM, a.num_seqs);
   return launch(kern, grid, L::THREADS, smem, stream, *mk, *mv, a, error_flag);
 }
 
 }  // namespace ts
 
 using namespace ts;
+
+#ifdef TS_FA_TIMING
+extern "C" int ts_fa_timing_read(unsigned long long* host16, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host16, fa_prof, sizeof(unsigned long long) * 16);
+  if (e == cudaSuccess && reset) {
+    unsigned long long z[16] = {0};
+    e = cudaMemcpyToSymbol(fa_prof, z, sizeof(z));
+  }
+  return (int)e;
+}
+#endif
 
 // bf16 prefill attention on tcgen05 for the requests listed in prefill_seqs. head_dim 64 or 128;
 // page_size 8 or a multiple of 16; num_pages_total = pages of the cache tensors (the pad page
@@ -466,6 +518,9 @@ extern "C" int ts_prefill_attention_tcgen05(
 #define TS_FA(D64_, BR_)                                                                                   \
   return heads_per_cta == 2 ? launch_fa<D64_, BR_, 2, 64>(a, rows, max_query_len, error_flag, stream)      \
                             : launch_fa<D64_, BR_, 1, 128>(a, rows, max_query_len, error_flag, stream)
+#ifdef TS_FA_BIG_BOX
+  if (head_dim == 128 && page_size % 128 == 0 && heads_per_cta == 1) return launch_fa<2, 128, 1, 128>(a, rows, max_query_len, error_flag, stream);
+#endif
   if (head_dim == 64) {
     if (page_size == 8) { TS_FA(1, 8); }
     TS_FA(1, 16);
