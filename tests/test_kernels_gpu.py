@@ -362,6 +362,59 @@ def test_gemm_swiglu(dtype, m, inter, k) -> None:
     torch.testing.assert_close(out.float(), want.float(), **t)
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(1024, 2048), (1024, 3072), (96, 64), (2048, 1024), (48, 1024)])
+def test_gemm_to_stream_and_normed(m, n, k) -> None:
+    """The two halves of the norm fusion against the separate steps: a product that adds its
+    bf16 result to the 32-bit stream and leaves the rows' sums of squares, then a product (plain
+    and SwiGLU) that normalises the stream while it loads it."""
+    bf = torch.bfloat16
+    x = rnd(m, k, dtype=bf, seed=1)
+    w = rnd(n, k, dtype=bf, seed=2, scale=0.05)
+    resid = rnd(m, n, seed=3, scale=2.0)
+    before = resid.clone()
+    sumsq = torch.full((n,), float("nan"), device="cuda")
+    resid16 = torch.full((m, n), float("nan"), device="cuda", dtype=bf)
+    ops.gemm_to_stream(x, w, resid, resid16, sumsq)
+    delta = torch.empty(m, n, device="cuda", dtype=bf)
+    ref.gemm(x, w, delta)
+    want_resid = before + delta.float()
+    torch.testing.assert_close(resid, want_resid, atol=2e-2, rtol=2e-2)
+    assert torch.equal(resid16, resid.to(bf))
+    parts = sumsq[: m * (n // 16)].view(m, n // 16).sum(1)
+    torch.testing.assert_close(parts, (resid * resid).sum(1), atol=1e-3, rtol=1e-4)
+    if n % 32:
+        return      # the consumer contracts over n: it needs a multiple of 32
+    # consumer: norm of the stream inside the next product. The fused kernel rounds at other
+    # points than the separate kernels, so both are held against the exact result: the fused error
+    # may not exceed that of the separate bf16 path by more than a quarter (rms) / a factor 2 (max)
+    nw = (1 + rnd(n, seed=5, scale=0.2)).to(bf)
+    normed = torch.empty(m, n, device="cuda", dtype=bf)
+    ref.add_rms_norm(resid.clone(), None, nw, 1e-6, normed)
+    exact = resid.double() * torch.rsqrt(resid.double().pow(2).mean(-1, keepdim=True) + 1e-6) * nw.double()
+
+    def held(out, want, truth):
+        err, err_ref = (out.double() - truth).abs(), (want.double() - truth).abs()
+        assert err.pow(2).mean().sqrt() <= 1.25 * err_ref.pow(2).mean().sqrt() + 1e-3
+        assert err.max() <= 2 * err_ref.max() + 1e-2
+
+    for n2 in (64, 1536):
+        w2 = rnd(n2, n, dtype=bf, seed=6, scale=0.05)
+        for out_dtype in (bf, torch.float32):
+            out = torch.full((m, n2), float("nan"), device="cuda", dtype=out_dtype)
+            want = torch.empty(m, n2, device="cuda", dtype=out_dtype)
+            ops.gemm_normed(resid16, sumsq, nw, 1e-6, w2, out)
+            ref.gemm(normed, w2, want)
+            held(out, want, exact @ w2.double().t())
+        wgu = rnd(2 * n2, n, dtype=bf, seed=7, scale=0.05)
+        out = torch.full((m, n2), float("nan"), device="cuda", dtype=bf)
+        want = torch.empty(m, n2, device="cuda", dtype=bf)
+        ops.gemm_normed(resid16, sumsq, nw, 1e-6, wgu, out, swiglu=True)
+        ref.gemm_swiglu(normed, wgu, want)
+        gu = exact @ wgu.double().t()
+        held(out, want, torch.nn.functional.silu(gu[:, :n2]) * gu[:, n2:])
+
+
 def test_gemm_skinny_refuses_what_it_cannot_take() -> None:
     x, w = rnd(4, 80, dtype=torch.bfloat16), rnd(32, 80, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="not supported"):

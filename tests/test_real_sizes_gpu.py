@@ -38,15 +38,22 @@ def real(tmp_path_factory):
     return folder, reqs, want
 
 
-@pytest.mark.parametrize("dtype,fuse_every_decode", [(torch.float32, False), (torch.bfloat16, False),
-                                                     (torch.bfloat16, True)])
-def test_real_layer_sizes_under_every_cut(real, dtype, fuse_every_decode, monkeypatch) -> None:
+@pytest.mark.parametrize("dtype,variant", [(torch.float32, "default"), (torch.bfloat16, "default"),
+                                           (torch.bfloat16, "fuse_every_decode"), (torch.bfloat16, "fused_norms")])
+def test_real_layer_sizes_under_every_cut(real, dtype, variant, monkeypatch) -> None:
     """``fuse_every_decode``: steps of decode tokens alone take the fused norm + rotation +
     cache write + attention kernel whatever their grid (the engine picks it only for grids that
-    gain from it, which these short requests never make)."""
+    gain from it, which these short requests never make). ``fused_norms``: the RMSNorms of decode
+    steps run inside the products around them instead of as kernels of their own."""
+    fuse_every_decode = variant == "fuse_every_decode"
     from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
+    fused_norm_calls = []
+    if variant == "fused_norms":
+        monkeypatch.setattr(ops, "FUSE_STREAM_NORM", True)
+        normed = ops.gemm_normed
+        monkeypatch.setattr(ops, "gemm_normed", lambda *a, **k: (fused_norm_calls.append(1), normed(*a, **k))[1])
     if fuse_every_decode:
         monkeypatch.setattr(ops, "FUSED_DECODE_MIN_CTAS", 0)
         calls = []
@@ -62,3 +69,5 @@ def test_real_layer_sizes_under_every_cut(real, dtype, fuse_every_decode, monkey
         check(got, want, {r: reqs[r] for r in got}, dtype)
     if fuse_every_decode:
         assert calls, "no step took the fused kernel"
+    if dtype == torch.bfloat16:
+        assert bool(fused_norm_calls) == (variant == "fused_norms")

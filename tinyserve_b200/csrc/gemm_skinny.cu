@@ -20,6 +20,19 @@
 // result. The scratch and the arrival counters are fixed arrays of the library, so products on
 // different streams must not overlap.
 //
+// Two optional fusions with the RMSNorm around the product (decode steps, where a norm kernel of
+// its own costs more than its work):
+//  * NORMX: x is not given; the kernel forms it from a bf16 copy r16 of the residual stream
+//    and the norm weight as bf16(r16 * weight), and scales the finished sums by the row's rstd =
+//    rsqrt(mean(r^2) + eps) in 32-bit (the norm of upstream src/tinyserve/layers.py:35-38; the
+//    scale is a factor of the whole row, so it commutes with the product). The sums of squares
+//    (of the 32-bit stream) come in parts from the producer of the stream and are added in a
+//    fixed order, off the critical path. The copy is bf16 because every CTA reads all of it from
+//    L2: a 32-bit read was measured to cost more than the norm kernel it saves.
+//  * RESID: the result is not stored; rounded to bf16 it is added to the residual stream in
+//    place, and the bf16 copy of the new stream and the sum of its squares over this CTA's 16
+//    columns are written per row for the next NORMX consumer.
+//
 // Needs K % 32 == 0 and N % 16 == 0 (the launcher reports TS_ERR_UNSUPPORTED otherwise and the
 // caller takes another kernel).
 #define TS_PDL_CLASS PDL_SKINNY
@@ -63,13 +76,51 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 // NT = column tiles of 8 rows of x (M <= 8 * NT); RT = weight row tiles of 16 per CTA (each x
 // fragment is used for all of them); SK_PF = k blocks of a warp whose weights are in flight;
 // FUSE: w holds 2 N rows (gate rows, then up rows) and out = silu(gate) * up, [M, N].
-template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool XRING>
+struct SkinnyNorm {
+  const bf16* resid16;    // NORMX: [M, K] bf16 copy of the residual stream
+  const float* sumsq;     // NORMX: [M][parts] partial sums of squares of the rows of the stream
+  int parts;
+  const bf16* weight;     // NORMX: [K] norm weight
+  float eps;
+  float* resid_out;       // RESID: [M, N] the 32-bit stream, added to in place
+  bf16* resid16_out;      // RESID: [M, N] its bf16 copy
+  float* sumsq_out;       // RESID: [M][N / 16]
+};
+
+__device__ __forceinline__ uint4 ld_cg(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+// bf16(r16 * weight) for 8 consecutive k: the B fragment of a NORMX product.
+__device__ __forceinline__ uint4 normed_fragment(const uint4& rv, const uint4& wv) {
+  const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float r0 = __uint_as_float(rr[i] << 16), r1 = __uint_as_float(rr[i] & 0xffff0000u);
+    const float w0 = __uint_as_float(ww[i] << 16), w1 = __uint_as_float(ww[i] & 0xffff0000u);
+    __nv_bfloat162 h = __floats2bfloat162_rn(r0 * w0, r1 * w1);
+    o[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool XRING, bool NORMX = false, bool RESID = false>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                                                 TOut* __restrict__ out, int M, int N, int K) {
+                                                                 TOut* __restrict__ out, int M, int N, int K,
+                                                                 SkinnyNorm nrm) {
+  static_assert(!(RESID && FUSE), "the fused activation is not added to the stream");
   constexpr int TILES = FUSE ? 2 * RT : RT;
   constexpr int COLS = 8 * NT;
   extern __shared__ float red[];   // [SK_WARPS][TILES][16][COLS]
   __shared__ int is_last;
+  __shared__ float rstd_s[16];
   pdl_trigger();
   // this CTA's slice of K (the whole of it unless grid.y > 1)
   const int ksplit = gridDim.y;
@@ -109,24 +160,40 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[r][j][e] = 0.f;
   const bf16* xrow[NT];
+  const bf16* rrow[NT];
   bool xok[NT];
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
     const int m = 8 * j + g;
     xok[j] = m < M;
     xrow[j] = x + (size_t)(xok[j] ? m : 0) * K + 8 * t;
+    rrow[j] = NORMX ? nrm.resid16 + (size_t)(xok[j] ? m : 0) * K + 8 * t : nullptr;
+  }
+  // NORMX: the parts of the rows' sums of squares are fetched now and added when the products are
+  // done (nothing waits for them meanwhile): warp w takes rows w and w + 8, a lane up to four parts
+  float ssq[2][4];
+  if constexpr (NORMX) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int m = warp + 8 * h, p = lane + 32 * i;
+        ssq[h][i] = (m < M && p < nrm.parts) ? ld_cg_f32(nrm.sumsq + m * nrm.parts + p) : 0.f;
+      }
   }
   // XRING: the fragments of x are fetched as far ahead as the weights. Chosen when a warp has so
   // few k blocks that all its loads go out at once and nothing later waits for L2; with long
   // loops the extra registers would cost more in occupancy than the prefetch gains.
   uint4 xring[XRING ? SK_PF : 1][NT];
+  uint4 wring[(XRING && NORMX) ? SK_PF : 1];      // NORMX: the norm weight of the same k, converted at use
   if constexpr (XRING) {
 #pragma unroll
     for (int p = 0; p < SK_PF; ++p) {
       const int kb = k_lo + warp * 32 + p * SK_KSTEP;
 #pragma unroll
       for (int j = 0; j < NT; ++j)
-        xring[p][j] = (kb < k_hi && xok[j]) ? ld_cached(xrow[j] + kb) : make_uint4(0u, 0u, 0u, 0u);
+        xring[p][j] = !(kb < k_hi && xok[j]) ? make_uint4(0u, 0u, 0u, 0u) : ld_cached((NORMX ? rrow[j] : xrow[j]) + kb);
+      if constexpr (NORMX) wring[p] = kb < k_hi ? ld_cached(nrm.weight + kb + 8 * t) : make_uint4(0u, 0u, 0u, 0u);
     }
   }
 
@@ -141,7 +208,9 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
         uint4 b[NT];
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-          if constexpr (XRING) b[j] = xring[p][j];
+          if constexpr (XRING && NORMX) b[j] = normed_fragment(xring[p][j], wring[p]);
+          else if constexpr (XRING) b[j] = xring[p][j];
+          else if constexpr (NORMX) b[j] = xok[j] ? normed_fragment(ld_cached(rrow[j] + kb), ld_cached(nrm.weight + kb + 8 * t)) : make_uint4(0u, 0u, 0u, 0u);
           else b[j] = xok[j] ? ld_cached(xrow[j] + kb) : make_uint4(0u, 0u, 0u, 0u);
         }
         const int nxt = kb + SK_PF * SK_KSTEP;
@@ -153,7 +222,8 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
           }
           if constexpr (XRING) {
 #pragma unroll
-            for (int j = 0; j < NT; ++j) xring[p][j] = xok[j] ? ld_cached(xrow[j] + nxt) : make_uint4(0u, 0u, 0u, 0u);
+            for (int j = 0; j < NT; ++j) xring[p][j] = xok[j] ? ld_cached((NORMX ? rrow[j] : xrow[j]) + nxt) : make_uint4(0u, 0u, 0u, 0u);
+            if constexpr (NORMX) wring[p] = ld_cached(nrm.weight + nxt + 8 * t);
           }
         }
 #pragma unroll
@@ -167,6 +237,14 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
     }
   }
 
+  if constexpr (NORMX) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = warp + 8 * h;
+      const float ss = warp_sum((ssq[h][0] + ssq[h][1]) + (ssq[h][2] + ssq[h][3]));      // a fixed order
+      if (lane == 0 && m < M) rstd_s[m] = rsqrtf(ss / (float)K + nrm.eps);
+    }
+  }
   // partial sums of this warp -> shared memory; element (row, col) of tile (r, j)
   float* mine = red + (size_t)warp * TILES * 16 * COLS;
 #pragma unroll
@@ -184,10 +262,27 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
   // column of the result is written as one run of out[m, n0 .. n0 + 16 RT).
   const int width = FUSE ? 2 * N : N;                 // columns of a partial row
   float* part = g_skinny_partial + (size_t)blockIdx.y * SK_SPLIT_MAX_ROWS * width;
+  // RESID: add to the stream and leave the row's sum of squares over these 16 columns (RT = 1:
+  // the 16 threads of a row are half a warp; every lane of the warp takes part in the shuffles)
+  auto to_stream = [&](int m, int row, float s) {
+    float r = 0.f;
+    if (m < M) {
+      float* rp = nrm.resid_out + (size_t)m * N + n0 + row;
+      r = *rp + round_to<bf16>(s);
+      *rp = r;
+      nrm.resid16_out[(size_t)m * N + n0 + row] = from_float<bf16>(r);
+    }
+    float sq = r * r;
+    sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+    if (row == 0 && m < M) nrm.sumsq_out[m * gridDim.x + blockIdx.x] = sq;
+  };
   for (int idx = threadIdx.x; idx < RT * 16 * COLS; idx += SK_THREADS) {
     const int m = idx / (RT * 16), row = idx - m * (RT * 16);
+    float s = 0.f, u = 0.f;
     if (m < M) {
-      float s = 0.f, u = 0.f;
 #pragma unroll
       for (int wq = 0; wq < SK_WARPS; ++wq) s += red[(size_t)wq * TILES * 16 * COLS + row * COLS + m];
       if constexpr (FUSE) {
@@ -197,14 +292,22 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
       if (ksplit > 1) {
         part[(size_t)m * width + n0 + row] = s;
         if constexpr (FUSE) part[(size_t)m * width + N + n0 + row] = u;
+      } else if constexpr (NORMX) {
+        s *= rstd_s[m];
+        u *= rstd_s[m];
+      }
+      if (ksplit > 1) {
       } else if constexpr (FUSE) {
         // rounding points of the unfused path: product -> bf16, silu -> bf16, times up -> bf16
         const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
         const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
         out[(size_t)m * N + n0 + row] = from_float<TOut>(sv * uv);
-      } else {
+      } else if constexpr (!RESID) {
         out[(size_t)m * N + n0 + row] = from_float<TOut>(s);
       }
+    }
+    if constexpr (RESID) {
+      if (ksplit == 1) to_stream(m, row, s);
     }
   }
   if (ksplit == 1) return;
@@ -212,6 +315,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
   if (!cta_arrives_last(&g_skinny_arrivals[blockIdx.x], (unsigned int)ksplit, &is_last)) return;
   for (int idx = threadIdx.x; idx < RT * 16 * COLS; idx += SK_THREADS) {
     const int m = idx / (RT * 16), row = idx - m * (RT * 16);
+    float s = 0.f, u = 0.f;
     if (m < M) {
       float sv[SK_MAX_SPLIT], uv[SK_MAX_SPLIT];
 #pragma unroll
@@ -220,25 +324,30 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
         sv[ks] = ks < ksplit ? __ldcg(pp + n0 + row) : 0.f;
         if constexpr (FUSE) uv[ks] = ks < ksplit ? __ldcg(pp + N + n0 + row) : 0.f;
       }
-      float s = 0.f, u = 0.f;
 #pragma unroll
       for (int ks = 0; ks < SK_MAX_SPLIT; ++ks) {
         s += sv[ks];
         if constexpr (FUSE) u += uv[ks];
       }
+      if constexpr (NORMX) {
+        s *= rstd_s[m];
+        u *= rstd_s[m];
+      }
       if constexpr (FUSE) {
         const float gv = round_to<bf16>(s), uvv = round_to<bf16>(u);
         const float act = round_to<bf16>(gv / (1.f + expf(-gv)));
         out[(size_t)m * N + n0 + row] = from_float<TOut>(act * uvv);
-      } else {
+      } else if constexpr (!RESID) {
         out[(size_t)m * N + n0 + row] = from_float<TOut>(s);
       }
     }
+    if constexpr (RESID) to_stream(m, row, s);
   }
 }
 
-template <typename TOut, int NT, int RT, bool FUSE, int SK_PF>
-static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
+template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool NORMX = false, bool RESID = false>
+static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream,
+                         const SkinnyNorm& nrm = SkinnyNorm()) {
   constexpr int TILES = FUSE ? 2 * RT : RT;
   const size_t smem = sizeof(float) * SK_WARPS * TILES * 16 * 8 * NT;
   // Split K across CTAs when the row tiles alone leave most SMs idle.
@@ -250,15 +359,16 @@ static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, 
   }
   constexpr bool CAN_RING = (!FUSE && RT == 1 && NT == 1);
   const bool ring = CAN_RING && K / ksplit <= SK_PF * SK_KSTEP;
-  void (*kern)(const bf16*, const bf16*, TOut*, int, int, int) = gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_PF, false>;
+  void (*kern)(const bf16*, const bf16*, TOut*, int, int, int, SkinnyNorm) =
+      gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_PF, false, NORMX, RESID>;
   if constexpr (CAN_RING) {
-    if (ring) kern = gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_PF, true>;
+    if (ring) kern = gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_PF, true, NORMX, RESID>;
   }
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch(kern, dim3(tiles, ksplit), SK_THREADS, smem, stream, x, w, out, M, N, K);
+  return launch(kern, dim3(tiles, ksplit), SK_THREADS, smem, stream, x, w, out, M, N, K, nrm);
 }
 
 // Weight row tiles per CTA: as many as still leave every SM a CTA (more tiles = each fragment of
@@ -319,4 +429,47 @@ extern "C" int ts_gemm_skinny_swiglu(const void* x, const void* w, void* out, in
   if (M <= 8) return dispatch_swiglu_nt<1>(xp, wp, op, M, inter, K, stream);
   if (M <= 16) return dispatch_swiglu_nt<2>(xp, wp, op, M, inter, K, stream);
   return dispatch_swiglu_nt<4>(xp, wp, op, M, inter, K, stream);
+}
+
+// out = rms_norm(resid) * w^T where the norm is made on the fly (NORMX above): resid16 [M, K] bf16,
+// sumsq [M][parts] float (parts = K / 16 as the producer leaves them), norm_weight [K] bf16. M <= 16.
+// swiglu != 0: w is [2 N, K] (gate rows, then up rows) and out = silu(gate) * up, [M, N] bf16.
+extern "C" int ts_gemm_skinny_normed(const void* resid16, const float* sumsq, int parts, const void* norm_weight,
+                                     float eps, const void* w, void* out, int M, int N, int K, int out_dtype,
+                                     int swiglu, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || K % 32 != 0 || N % 16 != 0 || parts <= 0 || parts > 128) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)resid16 | (uintptr_t)w | (uintptr_t)norm_weight) & 15) return TS_ERR_UNSUPPORTED;
+  SkinnyNorm nrm = SkinnyNorm();
+  nrm.resid16 = (const bf16*)resid16; nrm.sumsq = sumsq; nrm.parts = parts; nrm.weight = (const bf16*)norm_weight; nrm.eps = eps;
+  const bf16* wp = (const bf16*)w;
+  if (swiglu) {
+    if (out_dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
+    if (M <= 8) return launch_skinny<bf16, 1, 1, true, 4, true, false>(nullptr, wp, (bf16*)out, M, N, K, stream, nrm);
+    return launch_skinny<bf16, 2, 1, true, 4, true, false>(nullptr, wp, (bf16*)out, M, N, K, stream, nrm);
+  }
+  if (out_dtype == TS_DTYPE_BF16) {
+    if (M <= 8) return launch_skinny<bf16, 1, 1, false, 4, true, false>(nullptr, wp, (bf16*)out, M, N, K, stream, nrm);
+    return launch_skinny<bf16, 2, 1, false, 4, true, false>(nullptr, wp, (bf16*)out, M, N, K, stream, nrm);
+  }
+  if (out_dtype == TS_DTYPE_F32) {
+    if (M <= 8) return launch_skinny<float, 1, 1, false, 4, true, false>(nullptr, wp, (float*)out, M, N, K, stream, nrm);
+    return launch_skinny<float, 2, 1, false, 4, true, false>(nullptr, wp, (float*)out, M, N, K, stream, nrm);
+  }
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+// resid[M, N] += bf16(x * w^T) in place, resid16 = bf16(resid), and sumsq_out[m * (N / 16) + n / 16]
+// = sum over the 16 columns from n of the new resid[m, .]^2 (RESID above). M <= 16; sumsq_out
+// holds M * N / 16 floats.
+extern "C" int ts_gemm_skinny_to_stream(const void* x, const void* w, float* resid, void* resid16, float* sumsq_out,
+                                        int M, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || K % 32 != 0 || N % 16 != 0) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
+  SkinnyNorm nrm = SkinnyNorm();
+  nrm.resid_out = resid; nrm.resid16_out = (bf16*)resid16; nrm.sumsq_out = sumsq_out;
+  if (M <= 8)
+    return launch_skinny<bf16, 1, 1, false, 4, false, true>((const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, stream, nrm);
+  return launch_skinny<bf16, 2, 1, false, 4, false, true>((const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, stream, nrm);
 }

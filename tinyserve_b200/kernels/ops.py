@@ -47,6 +47,8 @@ _SIGNATURES: dict[str, list[Any]] = {
                                  _i, _vp, _vp],
     "ts_prefill_attention_tcgen05": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                      _f, _i, _i, _vp, _vp],
+    "ts_gemm_skinny_normed": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ts_gemm_skinny_to_stream": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
@@ -84,7 +86,7 @@ def _fn(name: str) -> Any:
             # first use of the library: overlap the launches of the kernel classes that gain from it
             lib.ts_set_programmatic_launch.argtypes = [_i]
             lib.ts_set_programmatic_launch.restype = None
-            lib.ts_set_programmatic_launch(DEFAULT_PDL_MASK)
+            lib.ts_set_programmatic_launch(_pdl_mask)      # the default, or what the caller has set already
         f = getattr(lib, name)
         f.argtypes = _SIGNATURES[name]
         f.restype = _i
@@ -530,6 +532,58 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
     gate_up = arena.take((m, 2 * inter), x.dtype)
     gemm(x, w_gate_up, gate_up)
     silu_mul(gate_up, out)
+
+
+# Steps of a few rows (decode) can fold the RMSNorm into the products around it: the product that
+# writes a sub-layer's output adds it to the residual stream itself and leaves a bf16 copy and the
+# rows' sums of squares, and the next product normalises that copy while it loads it. It saves two
+# of seven launches per layer, and 2.9 us per layer when the four products run back to back; in
+# the whole decode step (Qwen3-0.6B sizes, batch 8, B200) the norm kernels were hidden behind the
+# next product's weight prefetch anyway and the step is 0.6 % slower, so it is off by default.
+FUSE_STREAM_NORM = False
+
+
+STREAM_FUSE_MAX_WIDTH = 2048      # 128 parts of 16 columns: what a warp of the consumer adds up
+
+
+def can_stream_fuse(m: int, n: int, k: int, width: int, dtype: torch.dtype, device: torch.device) -> bool:
+    """Whether a product of ``m`` rows with an ``[n, k]`` weight matrix can take part in the
+    norm fusion (:func:`gemm_to_stream`, :func:`gemm_normed`) on a stream ``width`` wide: what
+    the skinny kernel takes."""
+    return (FUSE_STREAM_NORM and device.type == "cuda" and dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS
+            and k % 32 == 0 and n % 16 == 0 and n * k <= SKINNY_MAX_WEIGHTS
+            and width <= STREAM_FUSE_MAX_WIDTH)
+
+
+def gemm_to_stream(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, resid16: torch.Tensor,
+                   sumsq: torch.Tensor) -> None:
+    """``resid[M, N] += bf16(x[M, K] @ w[N, K]^T)`` in place (float32 stream); ``resid16`` gets
+    the new stream in bf16 and ``sumsq[m * (N / 16) + n // 16]`` the sum of ``resid[m, n : n + 16]^2``,
+    both for the product that normalises the stream next (:func:`gemm_normed`). bf16, ``M <= 16``."""
+    m, k = x.shape
+    n = w.shape[0]
+    if (w.shape[1] != k or tuple(resid.shape) != (m, n) or resid.dtype != torch.float32 or sumsq.dtype != torch.float32
+            or sumsq.numel() < n or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
+            or tuple(resid16.shape) != (m, n) or resid16.dtype != torch.bfloat16):
+        raise KernelError("gemm_to_stream: shape or dtype mismatch")
+    _check(_fn("ts_gemm_skinny_to_stream")(_dev(x, "x"), _dev(w, "w"), _dev(resid, "resid"), _dev(resid16, "resid16"),
+                                           _dev(sumsq, "sumsq"), m, n, k, _stream()), "gemm_to_stream")
+
+
+def gemm_normed(resid16: torch.Tensor, sumsq: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor,
+                out: torch.Tensor, swiglu: bool = False) -> None:
+    """``out = rms_norm(resid) @ w^T`` (or its SwiGLU form, ``w`` = gate rows then up rows) where
+    the norm is applied inside the product: ``resid16`` ``[M, K]`` bf16 and ``sumsq`` as
+    :func:`gemm_to_stream` leaves them (``K / 16`` parts per row), ``norm_weight`` ``[K]`` bf16."""
+    m, k = resid16.shape
+    n = out.shape[1]
+    if (tuple(w.shape) != ((2 * n if swiglu else n), k) or out.shape[0] != m or resid16.dtype != torch.bfloat16
+            or sumsq.dtype != torch.float32 or sumsq.numel() < k or norm_weight.shape != (k,)
+            or w.dtype != torch.bfloat16 or norm_weight.dtype != torch.bfloat16):
+        raise KernelError("gemm_normed: shape or dtype mismatch")
+    _check(_fn("ts_gemm_skinny_normed")(_dev(resid16, "resid16"), _dev(sumsq, "sumsq"), k // 16,
+                                        _dev(norm_weight, "norm_weight"), float(eps), _dev(w, "w"), _dev(out, "out"), m, n,
+                                        k, _code(out.dtype), int(bool(swiglu)), _stream()), "gemm_normed")
 
 
 PDL_ELEMENTWISE, PDL_SKINNY, PDL_ATTENTION, PDL_TCGEN05, PDL_SAMPLING, PDL_OTHER = 1, 2, 4, 8, 16, 32

@@ -17,7 +17,8 @@ from typing import Any, Mapping
 import torch
 
 from ..kernels import ops
-from .base import KVCacheEntry, KVNeed, Mixer, StepContext, TensorSpec, register_mixer
+from .base import (KVCacheEntry, KVNeed, LazyNormed, Mixer, ResidualStream, StepContext, TensorSpec, project,
+                   project_to_stream, register_mixer)
 
 
 class GQAAttention(Mixer):
@@ -64,14 +65,17 @@ class GQAAttention(Mixer):
             self.q_norm_w = tensors[p + "q_norm.weight"]
             self.k_norm_w = tensors[p + "k_norm.weight"]
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheEntry, writes_cache: bool,
-                position: Any) -> torch.Tensor:
+    takes_lazy_input = True
+    adds_to_stream = True
+
+    def forward(self, x: "torch.Tensor | LazyNormed", ctx: StepContext, cache: KVCacheEntry, writes_cache: bool,
+                position: Any, stream: ResidualStream | None = None) -> torch.Tensor | None:
         t = x.shape[0]
         arena = ctx.arena
         group = ctx.kv[cache.group]
         width = self.q_size + 2 * self.kv_size if writes_cache else self.q_size
         qkv = arena.take((t, width), ctx.dtype)
-        ops.gemm(x, self.w_qkv if writes_cache else self.w_q, qkv)
+        project(x, self.w_qkv if writes_cache else self.w_q, qkv, ctx)
         cos = None if position is None else position.cos
         sin = None if position is None else position.sin
         rotary_dim = 0 if position is None else position.rotary_dim
@@ -79,7 +83,7 @@ class GQAAttention(Mixer):
         attn = arena.take((t, self.q_size), ctx.dtype)
         if writes_cache and ops.can_fuse_decode(ctx, ctx.dtype, self.num_heads, self.num_kv_heads, self.head_dim,
                                                 cache.page_size, cache.k.shape[0], rotary_dim, interleaved,
-                                                x.device):
+                                                cache.k.device):
             # decode tokens only: norm, rotation, cache write and attention in one kernel
             ops.decode_attention_fused(qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps, cos, sin, group.slots,
                                        cache.k, cache.v, cache.page_size, group.block_tables, ctx, self.scale,
@@ -91,9 +95,7 @@ class GQAAttention(Mixer):
                                    self.num_heads, self.num_kv_heads, self.head_dim, writes_cache)
             ops.paged_attention(q, cache.k, cache.v, cache.page_size, group.block_tables, ctx,
                                 self.scale, self.window or 0, attn)
-        out = arena.take((t, self.hidden_size), ctx.dtype)
-        ops.gemm(attn, self.w_o, out)
-        return out
+        return project_to_stream(attn, self.w_o, stream, ctx)
 
 
 register_mixer("gqa_attention", GQAAttention)

@@ -131,13 +131,89 @@ class StepContext:
 
 class ResidualStream:
     """The residual stream of one step: ``resid`` is 32-bit ``[T, hidden]``; ``delta`` is the
-    last sub-layer's output in the model dtype, not yet added."""
+    last sub-layer's output in the model dtype, not yet added. ``sumsq``, when set, holds the
+    sums of squares of the rows of ``resid`` in parts, left by the product that last added to the
+    stream (``ops.gemm_to_stream``) together with ``resid16``, a copy of the stream in the model
+    dtype; both are valid only while ``delta`` is None."""
 
-    __slots__ = ("resid", "delta")
+    __slots__ = ("resid", "delta", "sumsq", "resid16", "_sumsq_buf", "_resid16_buf")
 
     def __init__(self, resid: torch.Tensor, delta: torch.Tensor | None = None) -> None:
         self.resid = resid
         self.delta = delta
+        self.sumsq: torch.Tensor | None = None
+        self.resid16: torch.Tensor | None = None
+        self._sumsq_buf: torch.Tensor | None = None
+        self._resid16_buf: torch.Tensor | None = None
+
+    def fusion_buffers(self, ctx: "StepContext") -> tuple[torch.Tensor, torch.Tensor]:
+        """Scratch for the stream's copy in the model dtype and for the parts of the rows' sums
+        of squares (one float per column)."""
+        if self._sumsq_buf is None:
+            self._sumsq_buf = ctx.arena.take_step((self.resid.shape[1],), torch.float32)
+            self._resid16_buf = ctx.arena.take_step(tuple(self.resid.shape), ctx.dtype)
+        return self._resid16_buf, self._sumsq_buf
+
+
+class LazyNormed:
+    """A normalised activation that is not computed yet: a part that can apply the norm while
+    it loads the stream (``project`` below) reads ``stream``, ``weight`` and ``eps``; any other
+    use calls ``tensor()``, which runs the norm's own kernel once."""
+
+    __slots__ = ("stream", "weight", "eps", "_make", "_tensor")
+
+    def __init__(self, stream: ResidualStream, weight: torch.Tensor, eps: float,
+                 make: Callable[[], torch.Tensor]) -> None:
+        self.stream, self.weight, self.eps, self._make = stream, weight, eps, make
+        self._tensor: torch.Tensor | None = None
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.stream.resid.shape
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self._make()
+        return self._tensor
+
+
+def project(x: "torch.Tensor | LazyNormed", w: torch.Tensor, out: torch.Tensor, ctx: "StepContext",
+            swiglu: bool = False) -> None:
+    """``out = x @ w^T`` (``swiglu``: ``silu(x Wgate^T) * (x Wup^T)`` with ``w`` the merged
+    matrix). A lazy ``x`` is normalised inside the product where the kernels allow it."""
+    from ..kernels import ops
+
+    if isinstance(x, LazyNormed):
+        m, k = x.shape
+        st = x.stream
+        if st.delta is None and st.sumsq is not None and ops.can_stream_fuse(m, w.shape[0], k, k, w.dtype, w.device):
+            ops.gemm_normed(st.resid16, st.sumsq, x.weight, x.eps, w, out, swiglu)
+            return
+        x = x.tensor()
+    if swiglu:
+        ops.gemm_swiglu(x, w, out, ctx.arena)
+    else:
+        ops.gemm(x, w, out)
+
+
+def project_to_stream(x: torch.Tensor, w: torch.Tensor, stream: ResidualStream | None,
+                      ctx: "StepContext") -> torch.Tensor | None:
+    """A sub-layer's output product. With a ``stream`` and few rows the product adds its result
+    to the stream itself and returns None; otherwise it returns ``x @ w^T`` for the caller to
+    leave pending on the stream."""
+    from ..kernels import ops
+
+    m, k = x.shape
+    n = w.shape[0]
+    if (stream is not None and stream.delta is None and x.dtype == torch.bfloat16
+            and ops.can_stream_fuse(m, n, k, n, x.dtype, x.device)):
+        copy, parts = stream.fusion_buffers(ctx)
+        ops.gemm_to_stream(x, w, stream.resid, copy, parts)
+        stream.resid16, stream.sumsq = copy, parts
+        return None
+    out = ctx.arena.take((m, n), ctx.dtype)
+    ops.gemm(x, w, out)
+    return out
 
 
 # ------------------------------------------------------------------------- interfaces
@@ -155,6 +231,11 @@ class Part:
 class Norm(Part):
     def forward(self, stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
+
+    def lazy(self, stream: ResidualStream, ctx: StepContext) -> "torch.Tensor | LazyNormed":
+        """For parts that declare ``takes_lazy_input``: the norm as a ``LazyNormed`` where the
+        stream allows it, else its result."""
+        return self.forward(stream, ctx)
 
     def forward_rows(self, stream: ResidualStream, rows: torch.Tensor, num_rows: int,
                      ctx: StepContext) -> torch.Tensor:
@@ -174,6 +255,10 @@ class Mixer(Part):
     # True if ``forward`` reads nothing of the step on the host (no lengths, no slot lists):
     # only then can a decode step with this mixer be recorded once and replayed as a graph.
     graph_safe: bool = False
+    # True if ``forward`` accepts a ``LazyNormed`` for ``x`` (and hands it to ``project``).
+    takes_lazy_input: bool = False
+    # True if ``forward`` has a keyword ``stream`` and may add its output to it (returning None).
+    adds_to_stream: bool = False
 
     def cache_need(self) -> KVNeed | StateNeed | None:
         return None
@@ -184,6 +269,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_lazy_input: bool = False     # as for Mixer
+    adds_to_stream: bool = False
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 

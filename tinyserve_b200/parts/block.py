@@ -16,11 +16,22 @@ class PreNormBlock(Block):
         # Scratch of this layer goes to the other half of the arena than the previous
         # layer's, whose pending output the first norm below still has to read.
         ctx.arena.next_frame()
-        hn = self.mixer_norm.forward(stream, ctx)
-        mixed = self.mixer.forward(hn, ctx, cache, writes_cache, position)
-        stream.delta = mixed
-        hn = self.feed_forward_norm.forward(stream, ctx)
-        stream.delta = self.feed_forward.forward(hn, ctx)
+        mixer, ff = self.mixer, self.feed_forward
+        hn = self.mixer_norm.lazy(stream, ctx) if mixer.takes_lazy_input else self.mixer_norm.forward(stream, ctx)
+        if mixer.adds_to_stream:
+            mixed = mixer.forward(hn, ctx, cache, writes_cache, position, stream=stream)
+        else:
+            mixed = mixer.forward(hn, ctx, cache, writes_cache, position)
+        self._leave(stream, mixed)
+        hn = self.feed_forward_norm.lazy(stream, ctx) if ff.takes_lazy_input else self.feed_forward_norm.forward(stream, ctx)
+        self._leave(stream, ff.forward(hn, ctx, stream=stream) if ff.adds_to_stream else ff.forward(hn, ctx))
+
+    @staticmethod
+    def _leave(stream: ResidualStream, out: Any) -> None:
+        """A sub-layer's output stays pending on the stream, unless the part has added it itself."""
+        if out is not None:
+            stream.delta = out
+            stream.sumsq = None
 
 
 register_block("prenorm", PreNormBlock)

@@ -13,7 +13,8 @@ from typing import Mapping
 import torch
 
 from ..kernels import ops
-from .base import FeedForward, StepContext, TensorSpec, register_feed_forward
+from .base import (FeedForward, LazyNormed, ResidualStream, StepContext, TensorSpec, project, project_to_stream,
+                   register_feed_forward)
 
 
 class SwiGLU(FeedForward):
@@ -36,13 +37,15 @@ class SwiGLU(FeedForward):
         self.w_gate_up = tensors[p + "gate_up_proj.weight"]
         self.w_down = tensors[p + "down_proj.weight"]
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    takes_lazy_input = True
+    adds_to_stream = True
+
+    def forward(self, x: "torch.Tensor | LazyNormed", ctx: StepContext,
+                stream: ResidualStream | None = None) -> torch.Tensor | None:
         t = x.shape[0]
         act = ctx.arena.take((t, self.intermediate_size), ctx.dtype)
-        ops.gemm_swiglu(x, self.w_gate_up, act, ctx.arena)
-        out = ctx.arena.take((t, self.hidden_size), ctx.dtype)
-        ops.gemm(act, self.w_down, out)
-        return out
+        project(x, self.w_gate_up, act, ctx, swiglu=True)
+        return project_to_stream(act, self.w_down, stream, ctx)
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -13,7 +13,7 @@ from typing import Mapping
 import torch
 
 from ..kernels import ops
-from .base import Norm, ResidualStream, StepContext, TensorSpec, register_norm
+from .base import LazyNormed, Norm, ResidualStream, StepContext, TensorSpec, register_norm
 
 
 class RMSNorm(Norm):
@@ -30,8 +30,15 @@ class RMSNorm(Norm):
     def forward(self, stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
         out = ctx.arena.take((stream.resid.shape[0], self.size), ctx.dtype)
         ops.add_rms_norm(stream.resid, stream.delta, self.weight, self.eps, out)
-        stream.delta = None
+        if stream.delta is not None:
+            stream.delta = None
+            stream.sumsq = None          # the stream has changed
         return out
+
+    def lazy(self, stream: ResidualStream, ctx: StepContext) -> "torch.Tensor | LazyNormed":
+        if stream.delta is None and stream.sumsq is not None:
+            return LazyNormed(stream, self.weight, self.eps, lambda: self.forward(stream, ctx))
+        return self.forward(stream, ctx)
 
     def forward_rows(self, stream: ResidualStream, rows: torch.Tensor, num_rows: int,
                      ctx: StepContext) -> torch.Tensor:
