@@ -43,6 +43,31 @@ def test_greedy_float32_equals_plain(tiny, name, graphs, chunked) -> None:
     assert all(g.allocator.num_used == 0 for g in llm.cache.groups)
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_steps_launched_ahead_change_nothing(tiny, name) -> None:
+    """Recorded decode steps launched before the tokens of the step before are read (the
+    default with decode graphs): the same tokens as without, for greedy and seeded sampling,
+    with requests of different lengths and an end token in the middle."""
+    from tinyserve_b200 import LLM, SamplingParams
+
+    folder, page, prompts, want = tiny[name]
+    outs = []
+    for ahead in (False, True):
+        llm = LLM.from_folder(folder, dtype="float32", page_size=page, num_pages=64, max_num_seqs=4,
+                              max_batch_tokens=128, decode_graphs=True, run_ahead=ahead)
+        e = llm.engine
+        eos = frozenset({want[1][3]})
+        ids = [e.add_request(prompts[0], 8), e.add_request(prompts[1], 8, eos_ids=eos),
+               e.add_request(prompts[2], 3, sampling=SamplingParams(temperature=0.9, top_p=0.8, seed=5))]
+        while e.has_work():
+            e.step()
+        outs.append([e.requests[i].output for i in ids])
+        assert (e.num_steps_ahead > 0) == ahead
+        assert all(g.allocator.num_used == 0 for g in llm.cache.groups)
+        assert outs[-1][0] == want[0] and outs[-1][1] == want[1][: want[1].index(want[1][3]) + 1]
+    assert outs[0] == outs[1]
+
+
 def test_greedy_bfloat16_close_to_plain_and_tight_cache(tiny) -> None:
     from tinyserve_b200 import LLM
 

@@ -146,3 +146,60 @@ def test_eos_stops_and_bad_requests_are_refused(setup) -> None:
         assert not e.has_work() and all(g.allocator.num_used == 0 for g in e.cache.groups)
         e.release(rid)
         assert rid not in e.requests
+
+
+class _ReplayingRunner:
+    """Makes the CPU engine believe its decode steps are recorded ones, so that it launches
+    steps ahead: a step launched ahead takes its tokens from the sampler's output tensor, as
+    the recorded step does on the device."""
+
+    @staticmethod
+    def wrap(runner):
+        from tinyserve_b200.engine.step import StepEntry
+
+        plain_step = runner.step
+        runner.graph_max_context = 10 ** 9
+        runner.replays = lambda entries, want=None: (
+            all(len(e.tokens) == 1 for e in entries) and (want is None or all(list(w) == [0] for w in want)))
+
+        def step(entries, want=None, tokens_from=None):
+            if tokens_from is not None:
+                toks = tokens_from[: len(entries)].tolist()
+                entries = [StepEntry(e.cache, [t]) for e, t in zip(entries, toks)]
+            return plain_step(entries, want)
+
+        runner.step = step
+        return runner
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_steps_launched_ahead_change_nothing(setup, name) -> None:
+    """With decode steps launched before the tokens of the step before are read: the same
+    tokens as without, for greedy and seeded sampling, different lengths, an end token in the
+    middle (the token run too many is dropped), a request that joins late and an abort."""
+    model, page, prompts, want = setup[name]
+    outs = []
+    for ahead in (False, True):
+        with use_references():
+            e = engine(model, page, 200, run_ahead=ahead)
+            _ReplayingRunner.wrap(e.runner)
+            eos = frozenset({want[1][3]})
+            ids = [e.add_request(prompts[0], NEW[name]),
+                   e.add_request(prompts[1], NEW[name], eos_ids=eos),
+                   e.add_request(prompts[2], 3, sampling=SamplingParams(temperature=0.9, top_p=0.8, seed=5))]
+            steps = 0
+            late = doomed = None
+            while e.has_work():
+                e.step()
+                steps += 1
+                if steps == 3:
+                    late = e.add_request(prompts[0][:2], 4, sampling=SamplingParams(temperature=0.7, seed=9))
+                    doomed = e.add_request(prompts[1], 50)
+                if steps == 6:
+                    e.abort(doomed)
+            outs.append([e.requests[i].output for i in ids + [late]])
+            assert (e.num_steps_ahead > 0) == ahead
+            assert all(g.allocator.num_used == 0 for g in e.cache.groups)
+            assert e.requests[ids[0]].output == want[0]
+            assert e.requests[ids[1]].output == want[1][: want[1].index(want[1][3]) + 1]
+    assert outs[0] == outs[1]

@@ -194,3 +194,55 @@ def test_random_workloads_finish_right_and_leak_nothing(seed) -> None:
         assert steps < 5000, "livelock"
     assert all(r.status is Status.FINISHED and r.output == expected(r.prompt, r.max_new_tokens) for r in reqs)
     assert all(g.allocator.num_used == 0 for g in s.cache.groups)
+
+
+def test_schedule_ahead_reserves_only_what_needs_no_decision() -> None:
+    """The next decode step may be reserved before this step's tokens are known only if nobody
+    waits, nobody is about to reach its length limit, and a token fits for everybody."""
+    s = make(num_pages=4, page=4, seqs=2)
+    a, b = Request(0, [1, 2, 3], 6), Request(1, [4, 5], 6)
+    s.add(a)
+    s.add(b)
+    s.schedule()
+    assert s.schedule_ahead() is None                       # they ran their prompts (3 and 2 tokens), not one token
+    s.update([a, b], [7, 8])
+    s.schedule()                                            # one token each
+    free = s.cache.groups[0].allocator.num_free
+    ahead = s.schedule_ahead()
+    assert ahead == [a, b] and a.num_pending() == -1 and b.num_pending() == -1
+    assert s.cache.groups[0].allocator.num_free == free - 1   # a's fifth token opens its second page
+    s.update([a, b], [9, 10])                               # the tokens of the step before arrive
+    assert a.num_pending() == 0 and not a.in_prefill() and a.output == [7, 9]
+    # a third request waits: admission is a decision, so nothing is reserved ahead
+    s.add(Request(2, [1], 2))
+    assert s.schedule_ahead() is None
+    s.waiting.clear()
+    s.update([a, b], [11, 12])
+    s.schedule()
+    # pages: a (6 cached) and b (5 cached) hold 2 pages each of the 4; a token more fits both
+    assert s.schedule_ahead() == [a, b]
+    s.update([a, b], [13, 14])
+    s.update([a, b], [15, 16])
+    s.schedule()
+    # both now hold 8 tokens = 2 full pages, no page is free: the next token fits nobody
+    assert s.cache.groups[0].allocator.num_free == 0 and s.schedule_ahead() is None
+    s.cache.check_invariant()
+
+
+def test_schedule_ahead_stops_before_the_length_limit_and_survives_an_end_token() -> None:
+    s = make(num_pages=16, page=4, seqs=2)
+    a, b = Request(0, [1, 2], 3), Request(1, [3], 9, eos_ids=frozenset({50}))
+    s.add(a)
+    s.add(b)
+    s.schedule()
+    s.update([a, b], [7, 8])
+    s.schedule()
+    # a has 1 of 3 tokens; the token under way is its second, so a third step is still its own
+    assert s.schedule_ahead() == [a, b]
+    s.update([a, b], [9, 50])                               # b draws its end token: it leaves, the extra room with it
+    assert b.status is Status.FINISHED and b.cache is None and s.running == [a]
+    # a's step ahead was its last (third token): nothing more may be reserved
+    assert s.schedule_ahead() is None
+    s.update([a], [11])
+    assert a.status is Status.FINISHED and not s.has_work()
+    assert all(g.allocator.num_used == 0 for g in s.cache.groups)

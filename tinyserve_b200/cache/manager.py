@@ -177,6 +177,15 @@ class CacheManager:
             short = max(short, need - g.allocator.num_free)
         return max(short, 0)
 
+    def pages_short_for_all(self, reqs: "list[RequestCache]", n: int) -> int:
+        """How many pages are lacking, in the worst group, to append ``n`` tokens to every one
+        of ``reqs``. 0 means they all fit."""
+        short = 0
+        for i, g in enumerate(self.groups):
+            need = sum(r.tables[i].pages_needed(n) for r in reqs)
+            short = max(short, need - g.allocator.num_free)
+        return max(short, 0)
+
     def pages_for(self, num_tokens: int) -> int:
         """Pages a request of ``num_tokens`` tokens holds at most in any group."""
         return (num_tokens + self.page_size - 1) // self.page_size

@@ -66,6 +66,26 @@ class Scheduler:
         self._admit_waiting()
         return list(self.running)
 
+    def schedule_ahead(self) -> list[Request] | None:
+        """Reserve the NEXT decode step while the step just scheduled is still running and its
+        tokens are unknown. Possible only when that needs no decision that depends on them:
+        nobody waits, every running request has just run its last pending token and will not
+        reach ``max_new_tokens`` with the token under way, and one more token fits for all of
+        them without preempting anybody. Returns the requests (one token each) or None; in
+        between, such a request has -1 pending tokens. A request that turns out to have ended
+        (an end token) simply leaves as usual; the extra token it was given room for is never
+        used."""
+        if self.waiting or not self.running:
+            return None
+        for r in self.running:
+            if r.num_scheduled != 1 or r.num_pending() != 0 or len(r.output) + 1 >= r.max_new_tokens:
+                return None
+        if self.cache.pages_short_for_all([r.cache for r in self.running], 1):
+            return None
+        for r in self.running:
+            self.cache.append(r.cache, 1)
+        return list(self.running)
+
     def _reserve_running(self) -> None:
         queue = deque(self.running)
         self.running = []

@@ -337,15 +337,25 @@ class ModelRunner:
         return self.graphs[min(r for r in self.graphs if r >= len(entries))]
 
     # --------------------------------------------------------------------- step
+    def replays(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None = None) -> bool:
+        """Whether :meth:`step` would replay a recorded decode step for these entries."""
+        return self._graph_for(entries, want) is not None
+
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None = None
-             ) -> torch.Tensor | None:
+    def step(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None = None,
+             tokens_from: torch.Tensor | None = None) -> torch.Tensor | None:
         """Run one step. Returns float32 logits ``[wanted, vocab]`` in the order of the entries
         and of their wanted places (a view into step scratch: use it before the next step),
-        or ``None`` when nothing is wanted."""
+        or ``None`` when nothing is wanted. ``tokens_from`` (int32 on the device, one per entry;
+        only for steps that :meth:`replays` accepts): the entries' tokens are taken from there
+        instead of from the host, so a step can be launched before the host knows them."""
         graph = self._graph_for(entries, want)
+        if tokens_from is not None and graph is None:
+            raise ValueError("tokens on the device can only feed a recorded decode step")
         if graph is not None:
             graph.fill(self, entries)
+            if tokens_from is not None:
+                graph.dev[graph.s_tokens][: len(entries)].copy_(tokens_from[: len(entries)], non_blocking=True)
             graph.graph.replay()
             ops.launch_count += graph.num_kernels
             self.num_steps += 1

@@ -35,32 +35,69 @@ class TokenLogprobs:
     top: list[tuple[int, float]]
 
 
+class SampleTicket:
+    """Tokens on their way to the host: ``device_tokens`` (int32, on the device, valid until the
+    sampler's next launch has run) can feed the next step at once; ``wait()`` returns the host
+    list once the copy has arrived."""
+
+    __slots__ = ("device_tokens", "_host", "_event", "_rows", "_tokens")
+
+    def __init__(self, device_tokens: torch.Tensor, host: torch.Tensor, event: "torch.cuda.Event | None", rows: int) -> None:
+        self.device_tokens, self._host, self._event, self._rows = device_tokens, host, event, rows
+        self._tokens: list[int] | None = None
+
+    def wait(self) -> list[int]:
+        if self._tokens is None:
+            if self._event is not None:
+                self._event.synchronize()
+            self._tokens = self._host[: self._rows].tolist()
+        return self._tokens
+
+
+class _Staging:
+    """Pinned host buffers of one launch (parameters out, tokens back) and the event that says
+    the tokens have arrived."""
+
+    def __init__(self, max_rows: int, pin: bool) -> None:
+        self.f_host = torch.empty(2 * max_rows, dtype=torch.float32, pin_memory=pin)
+        self.i_host = torch.empty(2 * max_rows, dtype=torch.int64, pin_memory=pin)
+        self.out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=pin)
+        self.event = torch.cuda.Event() if pin else None
+        self.ticket: SampleTicket | None = None
+
+
 class Sampler:
     def __init__(self, device: torch.device | str, max_rows: int = 1024) -> None:
         self.device = torch.device(device)
         pin = self.device.type == "cuda"
         self._cap = max_rows
-        self._f_host = torch.empty(2 * max_rows, dtype=torch.float32, pin_memory=pin)
-        self._i_host = torch.empty(2 * max_rows, dtype=torch.int64, pin_memory=pin)
+        # two launches may be under way at a time (the engine runs one step ahead): their host
+        # buffers alternate
+        self._staging = [_Staging(max_rows, pin), _Staging(max_rows, pin)]
+        self._turn = 0
         self._f_dev = torch.empty(2 * max_rows, dtype=torch.float32, device=self.device)
         self._i_dev = torch.empty(2 * max_rows, dtype=torch.int64, device=self.device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
-        self._out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=pin)
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               draws: Sequence[int]) -> list[int]:
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               draws: Sequence[int]) -> SampleTicket:
         """``logits`` ``[R, V]`` float32 on the device; row r belongs to a request with
-        ``params[r]``, noise seed ``seeds[r]`` that has drawn ``draws[r]`` tokens so far."""
+        ``params[r]``, noise seed ``seeds[r]`` that has drawn ``draws[r]`` tokens so far. Launches
+        the kernel and the copy of the tokens to the host and returns without waiting."""
         r = logits.shape[0]
         if not (len(params) == len(seeds) == len(draws) == r):
             raise ValueError(f"{r} rows, {len(params)} params, {len(seeds)} seeds, {len(draws)} draws")
         if r > self._cap:
             raise ValueError(f"{r} rows exceed the sampler's capacity {self._cap}")
+        st = self._staging[self._turn]
+        self._turn ^= 1
+        if st.ticket is not None:
+            st.ticket.wait()               # the launch that used these buffers last has been read
         out = self._out[:r]
         if all(p.greedy for p in params):
             ops.sample(logits, out)
         else:
-            f, i = self._f_host, self._i_host
+            f, i = st.f_host, st.i_host
             f[:r] = torch.tensor([p.temperature for p in params], dtype=torch.float32)
             f[r: 2 * r] = torch.tensor([p.top_p for p in params], dtype=torch.float32)
             i[:r] = torch.tensor(list(seeds), dtype=torch.int64)
@@ -69,11 +106,16 @@ class Sampler:
             self._i_dev[: 2 * r].copy_(i[: 2 * r], non_blocking=True)
             top_p = self._f_dev[r: 2 * r] if any(p.top_p < 1 for p in params) else None
             ops.sample(logits, out, self._f_dev[:r], top_p, self._i_dev[:r], self._i_dev[r: 2 * r])
-        host = self._out_host[:r]
-        host.copy_(out, non_blocking=True)
-        if self.device.type == "cuda":
-            torch.cuda.current_stream().synchronize()
-        return host.tolist()
+        st.out_host[:r].copy_(out, non_blocking=True)
+        if st.event is not None:
+            st.event.record()
+        st.ticket = SampleTicket(out, st.out_host, st.event, r)
+        return st.ticket
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               draws: Sequence[int]) -> list[int]:
+        """:meth:`launch` and wait: the chosen tokens as a host list."""
+        return self.launch(logits, params, seeds, draws).wait()
 
 
 def token_logprobs(logits: torch.Tensor, tokens: Sequence[int], ks: Sequence[int]) -> list[TokenLogprobs]:
