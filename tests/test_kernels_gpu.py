@@ -498,3 +498,17 @@ def test_sample_frequencies_follow_softmax() -> None:
     above = p[order].cumsum(0) - p[order]
     allowed = set(order[above < 0.6].tolist())
     assert set(out.unique().tolist()) == allowed
+
+
+def test_prefetch_l2_reads_only() -> None:
+    """Prefetch requests change nothing that can be seen: they run (ragged sizes, a side stream
+    joined again) and the memory reads as before; more than 8 ranges are refused."""
+    ts = [rnd(1000, 1024, dtype=torch.bfloat16, seed=1), rnd(3, 5, seed=2), rnd(16 * 1024 + 8, seed=3)]
+    before = [t.clone() for t in ts]
+    ops.prefetch_l2(ts)
+    join = ops.prefetch_l2_beside(ts + [None])
+    join()
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(ts, before))
+    with pytest.raises(ops.KernelError, match="at most 8"):
+        ops.prefetch_l2([ts[1]] * 9)

@@ -1,0 +1,55 @@
+// Ask the memory system to bring ranges of global memory into L2 ahead of their use
+// (cp.async.bulk.prefetch.L2): a decode step reads every weight exactly once, one kernel after
+// the other, and the attention kernel in the middle of a layer leaves part of the memory
+// bandwidth idle; the weights that the products after it will stream are fetched meanwhile.
+// The kernel only issues the requests (one thread per piece) and ends; nothing waits for the
+// data, and nothing goes wrong if a line is evicted again before its use. No counterpart in
+// upstream, whose products are library calls.
+#include "common.cuh"
+
+namespace ts {
+
+constexpr int PF_MAX_RANGES = 8;
+constexpr unsigned int PF_PIECE = 16 * 1024;      // bytes per request
+
+struct PrefetchRanges {
+  const char* base[PF_MAX_RANGES];
+  unsigned long long bytes[PF_MAX_RANGES];        // multiples of 16
+  unsigned int first_piece[PF_MAX_RANGES + 1];    // pieces before each range
+  int count;
+};
+
+__global__ void prefetch_l2_kernel(PrefetchRanges r) {
+  const unsigned int piece = blockIdx.x * blockDim.x + threadIdx.x;
+  if (piece >= r.first_piece[r.count]) return;
+  int i = 0;
+  while (piece >= r.first_piece[i + 1]) ++i;
+  const unsigned long long off = (unsigned long long)(piece - r.first_piece[i]) * PF_PIECE;
+  const unsigned long long left = r.bytes[i] - off;
+  const unsigned int n = left < PF_PIECE ? (unsigned int)left : PF_PIECE;
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(r.base[i] + off), "r"(n) : "memory");
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+// Prefetch `count` (at most 8) ranges into L2. Every base must be 16-byte aligned; sizes are
+// rounded down to a multiple of 16.
+extern "C" int ts_prefetch_l2(const void* const* bases, const unsigned long long* sizes, int count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (count > PF_MAX_RANGES) return TS_ERR_BAD_ARGUMENT;
+  PrefetchRanges r;
+  r.count = count;
+  unsigned int pieces = 0;
+  for (int i = 0; i < count; ++i) {
+    if (((uintptr_t)bases[i]) & 15) return TS_ERR_UNSUPPORTED;
+    r.base[i] = (const char*)bases[i];
+    r.bytes[i] = sizes[i] & ~15ull;
+    r.first_piece[i] = pieces;
+    pieces += (unsigned int)((r.bytes[i] + PF_PIECE - 1) / PF_PIECE);
+  }
+  for (int i = count; i <= PF_MAX_RANGES; ++i) r.first_piece[i] = pieces;
+  if (pieces == 0) return 0;
+  return launch(prefetch_l2_kernel, (pieces + 127) / 128, 128, 0, stream, r);
+}

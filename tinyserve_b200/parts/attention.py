@@ -71,6 +71,7 @@ class GQAAttention(Mixer):
     def forward(self, x: "torch.Tensor | LazyNormed", ctx: StepContext, cache: KVCacheEntry, writes_cache: bool,
                 position: Any, stream: ResidualStream | None = None) -> torch.Tensor | None:
         t = x.shape[0]
+        x_device = cache.k.device
         arena = ctx.arena
         group = ctx.kv[cache.group]
         width = self.q_size + 2 * self.kv_size if writes_cache else self.q_size
@@ -81,6 +82,13 @@ class GQAAttention(Mixer):
         rotary_dim = 0 if position is None else position.rotary_dim
         interleaved = False if position is None else position.interleaved
         attn = arena.take((t, self.q_size), ctx.dtype)
+        join = None
+        if ops.PREFETCH_WEIGHTS and ctx.num_prefill == 0 and ctx.num_decode <= ops.PREFETCH_MAX_ROWS and x_device.type == "cuda":
+            # decode: attention streams the cache and leaves bandwidth idle; the weights of the
+            # products after it (output projection, feed-forward) come into L2 meanwhile
+            ahead = [w for w in [self.w_o, *ctx.upcoming_weights] if w is not None]
+            if ahead and sum(w.numel() * w.element_size() for w in ahead) <= ops.PREFETCH_MAX_BYTES:
+                join = ops.prefetch_l2_beside(ahead[:8])
         if writes_cache and ops.can_fuse_decode(ctx, ctx.dtype, self.num_heads, self.num_kv_heads, self.head_dim,
                                                 cache.page_size, cache.k.shape[0], rotary_dim, interleaved,
                                                 cache.k.device):
@@ -95,6 +103,8 @@ class GQAAttention(Mixer):
                                    self.num_heads, self.num_kv_heads, self.head_dim, writes_cache)
             ops.paged_attention(q, cache.k, cache.v, cache.page_size, group.block_tables, ctx,
                                 self.scale, self.window or 0, attn)
+        if join is not None:
+            join()
         return project_to_stream(attn, self.w_o, stream, ctx)
 
 

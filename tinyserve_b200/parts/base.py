@@ -127,6 +127,9 @@ class StepContext:
     arena: "Any"
     dtype: torch.dtype
     position_tables: dict[Any, Any] = field(default_factory=dict)
+    # Weights that the kernels after the current mixer will stream (set by the block): a mixer
+    # with a long kernel that leaves memory bandwidth idle may have them fetched into L2 beside it.
+    upcoming_weights: list[torch.Tensor] = field(default_factory=list)
 
 
 class ResidualStream:
@@ -271,6 +274,11 @@ class Mixer(Part):
 class FeedForward(Part):
     takes_lazy_input: bool = False     # as for Mixer
     adds_to_stream: bool = False
+
+    def streamed_weights(self) -> list[torch.Tensor]:
+        """The weight tensors that ``forward`` reads once from end to end, in the order of use
+        (what is worth fetching into L2 ahead of it); empty if it is not that simple."""
+        return []
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError

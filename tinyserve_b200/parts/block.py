@@ -17,6 +17,7 @@ class PreNormBlock(Block):
         # layer's, whose pending output the first norm below still has to read.
         ctx.arena.next_frame()
         mixer, ff = self.mixer, self.feed_forward
+        ctx.upcoming_weights = ff.streamed_weights()
         hn = self.mixer_norm.lazy(stream, ctx) if mixer.takes_lazy_input else self.mixer_norm.forward(stream, ctx)
         if mixer.adds_to_stream:
             mixed = mixer.forward(hn, ctx, cache, writes_cache, position, stream=stream)

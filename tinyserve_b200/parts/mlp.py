@@ -40,6 +40,9 @@ class SwiGLU(FeedForward):
     takes_lazy_input = True
     adds_to_stream = True
 
+    def streamed_weights(self) -> list[torch.Tensor]:
+        return [self.w_gate_up, self.w_down]
+
     def forward(self, x: "torch.Tensor | LazyNormed", ctx: StepContext,
                 stream: ResidualStream | None = None) -> torch.Tensor | None:
         t = x.shape[0]
