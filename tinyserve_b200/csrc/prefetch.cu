@@ -10,7 +10,14 @@
 namespace ts {
 
 constexpr int PF_MAX_RANGES = 8;
-constexpr unsigned int PF_PIECE = 16 * 1024;      // bytes per request
+// Bytes per request; 128 threads per CTA. The kernel lasts until its requests are served, and an
+// SM passes them on at about 0.15 TB/s, so the number of CTAs sets the rate: 16 KB x 128 threads
+// fetches 23 MB with 12 CTAs at 1.9 TB/s in 11 us, about the length of the attention kernel it
+// runs beside. Measured on B200 (Qwen3-0.6B sizes, batch 8): spread thinly over all SMs the same
+// requests are served at 5.7 TB/s but take the bandwidth from the attention kernel (step 1.144 ms
+// instead of 1.126 ms); slower than this, the step waits for the prefetch (1.27 ms). Fetching the
+// next layer's cache pages the same way made every batch size slower and is not done.
+constexpr unsigned int PF_PIECE = 16 * 1024;
 
 struct PrefetchRanges {
   const char* base[PF_MAX_RANGES];
