@@ -88,10 +88,12 @@ def test_silu_mul(dtype, inter) -> None:
 @pytest.mark.parametrize("hq,hkv,d,rot,inter,norm,page", [
     (4, 2, 16, 16, False, True, 16), (4, 1, 32, 32, False, True, 8), (3, 3, 48, 48, False, True, 32),
     (16, 8, 128, 128, False, True, 16), (6, 2, 64, 32, True, False, 4), (2, 2, 256, 0, False, True, 16),
+    (5, 1, 64, 64, False, True, 8), (3, 3, 256, 256, False, False, 16),
 ])
 @pytest.mark.parametrize("write_kv", [True, False])
-def test_qk_norm_rope_write(dtype, hq, hkv, d, rot, inter, norm, page, write_kv) -> None:
-    t, pages = 29, 11
+@pytest.mark.parametrize("t", [29, 301])       # few tokens (decode) and many (prefill) take different kernels
+def test_qk_norm_rope_write(dtype, hq, hkv, d, rot, inter, norm, page, write_kv, t) -> None:
+    pages = -(-t // page) + 3
     width = (hq + 2 * hkv) * d if write_kv else hq * d
     qkv = rnd(t, width, dtype=dtype, seed=4, scale=2.0)
     qw = (1 + rnd(d, seed=5, scale=0.2)).to(dtype) if norm else None

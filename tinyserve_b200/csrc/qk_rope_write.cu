@@ -197,6 +197,106 @@ __global__ void qk_norm_rope_write_fast_kernel(
   }
 }
 
+// The same for many tokens (prefill), bf16, head_dim 64, 128 or 256: D / 8 lanes share a head,
+// each with 4 consecutive elements of the first half and their 4 partners of the second (two
+// 8-byte accesses), so a warp works on 32 / (D / 8) heads at once and half as many instructions
+// move the same bytes as in the kernel above.
+template <int D>
+__global__ void qk_norm_rope_write_wide_kernel(
+    const bf16* __restrict__ qkv, bf16* __restrict__ q_out, const bf16* __restrict__ q_weight,
+    const bf16* __restrict__ k_weight, float eps, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, const int* __restrict__ slots, bf16* __restrict__ k_cache,
+    bf16* __restrict__ v_cache, int page_size, int num_tokens, int num_heads, int num_kv_heads, int write_kv) {
+  constexpr int LPH = D / 8, HPW = 32 / LPH, HALF = D / 2;
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPH, l = lane % LPH;
+  const int heads_per_token = write_kv ? num_heads + 2 * num_kv_heads : num_heads;
+  const long long item = ((long long)blockIdx.x * QK_WARPS + warp) * HPW + sub;
+  const bool live = item < (long long)num_tokens * heads_per_token;
+  const int t = live ? (int)(item / heads_per_token) : 0;
+  const int h = live ? (int)(item - (long long)t * heads_per_token) : 0;
+  const bf16* src = qkv + ((size_t)t * heads_per_token + h) * D + 4 * l;
+  bf16* dst;
+  const bf16* weight = nullptr;
+  bool is_v = false;
+  if (h < num_heads) {
+    dst = q_out + ((size_t)t * num_heads + h) * D;
+    weight = q_weight;
+  } else {
+    const int slot = slots[t];
+    const int page = slot / page_size, off = slot - page * page_size;
+    const bool is_k = h < num_heads + num_kv_heads;
+    const int kvh = is_k ? h - num_heads : h - num_heads - num_kv_heads;
+    dst = (is_k ? k_cache : v_cache) + (((size_t)page * num_kv_heads + kvh) * page_size + off) * D;
+    is_v = !is_k;
+    weight = k_weight;
+  }
+  dst += 4 * l;
+  uint2 ua = make_uint2(0u, 0u), ub = make_uint2(0u, 0u);
+  if (live) {
+    ua = *reinterpret_cast<const uint2*>(src);
+    ub = *reinterpret_cast<const uint2*>(src + HALF);
+  }
+  if (is_v) {
+    if (live) {
+      *reinterpret_cast<uint2*>(dst) = ua;
+      *reinterpret_cast<uint2*>(dst + HALF) = ub;
+    }
+  }
+  float a[4] = {__uint_as_float(ua.x << 16), __uint_as_float(ua.x & 0xffff0000u), __uint_as_float(ua.y << 16),
+                __uint_as_float(ua.y & 0xffff0000u)};
+  float b[4] = {__uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u), __uint_as_float(ub.y << 16),
+                __uint_as_float(ub.y & 0xffff0000u)};
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) ss += a[e] * a[e] + b[e] * b[e];
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // within the head's lanes
+  if (!live || is_v) return;
+  if (weight != nullptr) {
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const uint2 wa = *reinterpret_cast<const uint2*>(weight + 4 * l);
+    const uint2 wb = *reinterpret_cast<const uint2*>(weight + HALF + 4 * l);
+    const float fa[4] = {__uint_as_float(wa.x << 16), __uint_as_float(wa.x & 0xffff0000u), __uint_as_float(wa.y << 16),
+                         __uint_as_float(wa.y & 0xffff0000u)};
+    const float fb[4] = {__uint_as_float(wb.x << 16), __uint_as_float(wb.x & 0xffff0000u), __uint_as_float(wb.y << 16),
+                         __uint_as_float(wb.y & 0xffff0000u)};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      a[e] = round_to<bf16>(round_to<bf16>(a[e] * rstd) * fa[e]);
+      b[e] = round_to<bf16>(round_to<bf16>(b[e] * rstd) * fb[e]);
+    }
+  }
+  const float4 cv = *reinterpret_cast<const float4*>(cos_t + (size_t)t * HALF + 4 * l);
+  const float4 sv = *reinterpret_cast<const float4*>(sin_t + (size_t)t * HALF + 4 * l);
+  const float c[4] = {cv.x, cv.y, cv.z, cv.w}, sn[4] = {sv.x, sv.y, sv.z, sv.w};
+  float ra[4], rb[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    ra[e] = a[e] * c[e] - b[e] * sn[e];
+    rb[e] = b[e] * c[e] + a[e] * sn[e];
+  }
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(ra[0], ra[1]), p1 = __floats2bfloat162_rn(ra[2], ra[3]);
+  __nv_bfloat162 q0 = __floats2bfloat162_rn(rb[0], rb[1]), q1 = __floats2bfloat162_rn(rb[2], rb[3]);
+  *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1));
+  *reinterpret_cast<uint2*>(dst + HALF) = make_uint2(*reinterpret_cast<uint32_t*>(&q0), *reinterpret_cast<uint32_t*>(&q1));
+}
+
+template <int D>
+static int launch_wide(const void* qkv, void* q_out, const void* q_weight, const void* k_weight, float eps,
+                       const float* cos_t, const float* sin_t, const int* slots, void* k_cache, void* v_cache,
+                       int page_size, int num_tokens, int num_heads, int num_kv_heads, int write_kv, cudaStream_t stream) {
+  constexpr int HPW = 32 / (D / 8);
+  const int heads_per_token = write_kv ? num_heads + 2 * num_kv_heads : num_heads;
+  const long long items = (long long)num_tokens * heads_per_token;
+  const long long per_block = (long long)QK_WARPS * HPW;
+  return launch(qk_norm_rope_write_wide_kernel<D>, (int)((items + per_block - 1) / per_block), QK_WARPS * 32, 0, stream,
+                (const bf16*)qkv, (bf16*)q_out, (const bf16*)q_weight, (const bf16*)k_weight, eps, cos_t, sin_t, slots,
+                (bf16*)k_cache, (bf16*)v_cache, page_size, num_tokens, num_heads, num_kv_heads, write_kv);
+}
+
 }  // namespace ts
 
 using namespace ts;
@@ -215,6 +315,15 @@ extern "C" int ts_qk_norm_rope_write(const void* qkv, void* q_out, const void* q
   const size_t smem = (size_t)QK_WARPS * head_dim * sizeof(float);
   if (rotary_dim == head_dim && !interleaved && head_dim % 8 == 0 && head_dim <= 256 &&
       (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0) {
+    if (dtype == TS_DTYPE_BF16 && num_tokens >= 32 && (q_weight == nullptr) == (k_weight == nullptr)) {
+#define TS_WIDE(D_)                                                                                              \
+  return launch_wide<D_>(qkv, q_out, q_weight, k_weight, eps, cos_t, sin_t, slots, k_cache, v_cache, page_size, \
+                         num_tokens, num_heads, num_kv_heads, write_kv, stream)
+      if (head_dim == 64) { TS_WIDE(64); }
+      if (head_dim == 128) { TS_WIDE(128); }
+      if (head_dim == 256) { TS_WIDE(256); }
+#undef TS_WIDE
+    }
     if (dtype == TS_DTYPE_F32)
       return launch(qk_norm_rope_write_fast_kernel<float, 2>, blocks, QK_WARPS * 32, 0, stream,
                     (const float*)qkv, (float*)q_out, (const float*)q_weight, (const float*)k_weight, eps, cos_t,

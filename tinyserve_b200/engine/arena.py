@@ -12,12 +12,21 @@ from __future__ import annotations
 import torch
 
 _ALIGN = 256
+_ELEMENT_SIZE: dict[torch.dtype, int] = {}
+
+
+def _element_size(dtype: torch.dtype) -> int:
+    n = _ELEMENT_SIZE.get(dtype)
+    if n is None:
+        n = _ELEMENT_SIZE[dtype] = torch.empty(0, dtype=dtype).element_size()
+    return n
 
 
 class _Region:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self.buf = torch.empty(0, dtype=torch.uint8, device=device)
+        self._typed: dict[torch.dtype, torch.Tensor] = {}     # ``buf`` seen as each dtype asked for so far
         self.used = 0          # offset in ``buf`` of the next take
         self.demand = 0        # bytes taken since the last reset, wherever they came from
         self.high_water = 0    # the largest demand of any step so far
@@ -26,7 +35,8 @@ class _Region:
         if self.high_water > self.buf.numel():
             # The last step outgrew the buffer and was served piecemeal; make one buffer that
             # holds a whole step, so that from now on nothing moves.
-            self.buf = torch.empty(self.high_water, dtype=torch.uint8, device=self.device)
+            self.buf = torch.empty(self.high_water // _ALIGN * _ALIGN + _ALIGN, dtype=torch.uint8, device=self.device)
+            self._typed = {}
         self.used = 0
         self.demand = 0
 
@@ -34,7 +44,8 @@ class _Region:
         numel = 1
         for s in shape:
             numel *= int(s)
-        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        size = _element_size(dtype)
+        nbytes = numel * size
         self.demand = (self.demand + _ALIGN - 1) // _ALIGN * _ALIGN + nbytes
         self.high_water = max(self.high_water, self.demand)
         start = (self.used + _ALIGN - 1) // _ALIGN * _ALIGN
@@ -42,12 +53,16 @@ class _Region:
         if end > self.buf.numel():
             # Grow: views handed out earlier keep the old buffer alive until they die.
             grow = max(nbytes, 2 * self.buf.numel(), 1 << 16)
-            self.buf = torch.empty(grow, dtype=torch.uint8, device=self.device)
+            self.buf = torch.empty((grow + _ALIGN - 1) // _ALIGN * _ALIGN, dtype=torch.uint8, device=self.device)
+            self._typed = {}
             start, end = 0, nbytes
         self.used = end
         if numel == 0:
             return torch.empty(shape, dtype=dtype, device=self.device)
-        return self.buf[start:end].view(dtype).view(shape)
+        typed = self._typed.get(dtype)
+        if typed is None:
+            typed = self._typed[dtype] = self.buf.view(dtype)     # buffer sizes are multiples of 256 bytes
+        return typed[start // size: end // size].view(shape)
 
 
 class Arena:

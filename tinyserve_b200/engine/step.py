@@ -122,7 +122,8 @@ class DecodeGraph:
 
         def run() -> torch.Tensor:
             self.arena.begin_step()
-            return model.forward(self.context(runner), caches, self.dev[self.s_rows], self.rows)
+            with ops.stream_scope():
+                return model.forward(self.context(runner), caches, self.dev[self.s_rows], self.rows)
 
         # Twice without recording: the first sizes the scratch memory, the second shows that
         # it no longer moves; then the same launches are recorded.
@@ -364,6 +365,7 @@ class ModelRunner:
         ctx, rows, r = self.build_context(entries, want)
         if self.tune_launch_overlap and self.device.type == "cuda":
             ops.use_pdl_mask(ops.PREFILL_PDL_MASK if ctx.num_prefill else ops.DEFAULT_PDL_MASK)
-        logits = self.model.forward(ctx, self.cache.entries, rows, r)
+        with ops.stream_scope():
+            logits = self.model.forward(ctx, self.cache.entries, rows, r)
         self.num_steps += 1
         return logits

@@ -107,8 +107,27 @@ def _check(status: int, name: str, kernels: int = 1) -> None:
     raise KernelError(f"{name}: CUDA error {status}")
 
 
+_stream_stack: list[int] = []
+
+
 def _stream() -> int:
+    if _stream_stack:
+        return _stream_stack[-1]
     return torch.cuda.current_stream().cuda_stream
+
+
+class stream_scope:
+    """While it is open, this library's kernels go to the stream that was current when it was
+    opened, without asking for the current stream at every launch (that query costs several
+    microseconds, as much as the launch). Open it around a step's launches; inside it, change
+    the stream only through another ``stream_scope`` opened under the new stream."""
+
+    def __enter__(self) -> "stream_scope":
+        _stream_stack.append(torch.cuda.current_stream().cuda_stream if torch.cuda.is_available() else 0)
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        _stream_stack.pop()
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -623,7 +642,7 @@ def prefetch_l2_beside(tensors: Sequence[torch.Tensor]) -> "Callable[[], None]":
     if side is None:
         side = _side_streams[cur.device.index] = torch.cuda.Stream(device=cur.device)
     side.wait_stream(cur)
-    with torch.cuda.stream(side):
+    with torch.cuda.stream(side), stream_scope():
         prefetch_l2(tensors)
     return lambda: cur.wait_stream(side)
 
