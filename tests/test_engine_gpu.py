@@ -109,6 +109,47 @@ def test_graph_logits_equal_eager_logits(tiny) -> None:
     torch.testing.assert_close(outs[0], outs[1], atol=2e-5, rtol=2e-5)
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_recorded_prompt_portion_equals_eager(tiny, name) -> None:
+    """A prompt fed in portions of a fixed size: the recorded step of such a portion (on top of
+    whatever the request already holds, pages scattered) gives the logits of the kernel-by-kernel
+    step; portions of other sizes and steps of several requests are not taken by the recording."""
+    from tinyserve_b200.cache import CacheManager
+    from tinyserve_b200.engine.step import ModelRunner, StepEntry
+    from tinyserve_b200.model import DecoderModel
+
+    folder, page, prompts, _ = tiny[name]
+    cfg = TINIES[name][0]
+    model = DecoderModel.from_folder(folder, torch.float32, "cuda")
+    prompt = random_prompt(59, cfg["vocab_size"], 3)
+    portion = 12
+    outs = []
+    for graphs in (False, True):
+        cache = CacheManager(model.cache_needs(), page_size=page, num_pages=40, max_requests=4,
+                             dtype=torch.float32, device="cuda")
+        runner = ModelRunner(model, cache)
+        if graphs:
+            runner.record_prefill_graph(portion, 128)
+        other = cache.new_request()                     # scatters the pages of the request under test
+        r = cache.new_request()
+        rows, at = [], 0
+        while at < len(prompt):
+            n = min(portion, len(prompt) - at)
+            cache.append(other, 3)
+            cache.append(r, n)
+            rows.append(runner.step([StepEntry(r, prompt[at: at + n])]).clone())
+            at += n
+        assert runner.num_graph_steps == (len(prompt) // portion if graphs else 0)
+        cache.append(r, portion)
+        assert runner.step([StepEntry(r, prompt[:portion])], [[]]) is None      # a portion that wants nothing
+        cache.append(r, portion)
+        cache.append(other, portion)
+        two = runner.step([StepEntry(r, prompt[:portion]), StepEntry(other, prompt[:portion])])
+        assert two.shape[0] == 2
+        outs.append(torch.cat(rows))
+    torch.testing.assert_close(outs[0], outs[1], atol=2e-5, rtol=2e-5)
+
+
 def test_seeded_sampling_is_reproducible_and_batch_independent(tiny) -> None:
     from tinyserve_b200 import LLM, SamplingParams
 

@@ -351,8 +351,8 @@ def test_gemm_skinny(out_dtype, m, n, k) -> None:
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m", [1, 8, 13, 16, 40])
-@pytest.mark.parametrize("inter,k", [(3072, 1024), (176, 80), (48, 64), (112, 96)])
+@pytest.mark.parametrize("m", [1, 8, 13, 16, 40, 128, 300, 2048])
+@pytest.mark.parametrize("inter,k", [(3072, 1024), (176, 80), (48, 64), (112, 96), (1100, 200)])
 def test_gemm_swiglu(dtype, m, inter, k) -> None:
     x = rnd(m, k, dtype=dtype, seed=1)
     w = rnd(2 * inter, k, dtype=dtype, seed=2, scale=0.1)

@@ -14,6 +14,11 @@
 //                                           marks its accumulator "full")
 //   warps 2-5        : epilogue            (tcgen05.ld of the warp's 32 TMEM lanes, cast, store,
 //                                           then the accumulator buffer is handed back)
+// SWIGLU variant: w holds 2 N rows (gate rows, then up rows); a tile's B operand is 128 gate
+// rows followed by the 128 up rows of the same output columns (two TMA boxes), so the
+// accumulator holds gate in columns 0..127 and up in 128..255 and the epilogue writes
+// silu(gate) * up, [M, N], with the rounding points of the separate kernels (each product to
+// bf16, the SiLU to bf16, the result to bf16; upstream src/tinyserve/layers.py:94-115).
 // Every wait on an mbarrier is bounded: when the bound is hit the kernel records it in
 // *error_flag, stops waiting and still frees its tensor memory, so a fault in the pipeline
 // shows as an error code on the host and never as a hang.
@@ -32,7 +37,7 @@ constexpr int TG_THREADS = 192;     // TMA warp, MMA warp, four epilogue warps
 // rows fastest, so CTAs that run together share weight tiles in L2). The accumulator is double-
 // buffered in tensor memory (2 x BN columns): while the four epilogue warps drain tile i, the
 // MMA warp already accumulates tile i + 1.
-template <int BN, int STAGES, typename TOut>
+template <int BN, int STAGES, typename TOut, bool SWIGLU = false>
 __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   TOut* __restrict__ out, int M, int N, int K,
@@ -52,7 +57,9 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN - 1) / BN;
+  static_assert(!SWIGLU || BN == 256, "the fused activation pairs 128 gate with 128 up columns");
+  constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;          // output columns per tile
+  const int tiles_m = (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN_OUT - 1) / BN_OUT;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + TG_BK - 1) / TG_BK;
 
@@ -74,7 +81,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
     if (lane == 0) {
       int it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+        const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN_OUT;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
@@ -82,7 +89,13 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
           unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
           tma_load_2d(a, &map_x, &full_bar[s], kb * TG_BK, m0);
-          tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
+          if constexpr (SWIGLU) {
+            // the map's box is 128 rows: gate rows n0.., then up rows N + n0.. of the merged matrix
+            tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
+            tma_load_2d(a + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], kb * TG_BK, N + n0);
+          } else {
+            tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
+          }
         }
       }
     }
@@ -119,13 +132,43 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
     int t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
       const int b = t & 1;
-      const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN_OUT;
       if (!mbar_wait(&acc_full[b], (t >> 1) & 1) || failed) {
         if (lane == 0) atomicExch(error_flag, 1);
         break;
       }
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
+      if constexpr (SWIGLU) {
+#pragma unroll 1
+        for (int c = 0; c < BN_OUT / 32; ++c) {
+          uint32_t g[32], u[32];
+          const uint32_t base = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN + c * 32);
+          tmem_ld_32_nowait(base, g);
+          tmem_ld_32_nowait(base + BN_OUT, u);
+          tmem_ld_wait();
+          if (row < M) {
+            bf16* dst = (bf16*)out + (size_t)row * N + n0 + c * 32;
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float gv = round_to<bf16>(__uint_as_float(g[j])), uv = round_to<bf16>(__uint_as_float(u[j]));
+              f[j] = round_to<bf16>(__fdividef(gv, 1.f + __expf(-gv))) * uv;
+            }
+            if (n0 + c * 32 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                Vec<bf16> v;
+                v.pack(f + j);
+                v.store(dst + j);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (n0 + c * 32 + j < N) dst[j] = from_float<bf16>(f[j]);
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -154,6 +197,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
               if (n0 + c * 32 + j < N) dst[j] = from_float<TOut>(__uint_as_float(r[j]));
           }
         }
+      }
       }
       // this warp has read its part of the accumulator: hand the buffer back to the MMA warp
       tc_fence_before();
@@ -196,14 +240,15 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int bo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, typename TOut>
+template <int BN, int STAGES, typename TOut, bool SWIGLU = false>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, int M, int N, int K, int* error_flag,
                      cudaStream_t stream) {
   const size_t smem = (size_t)STAGES * (TG_BM + BN) * TG_BK * 2 + 1024;
-  auto kern = gemm_tcgen05_kernel<BN, STAGES, TOut>;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, TOut, SWIGLU>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  const int num_tiles = ((N + BN - 1) / BN) * ((M + TG_BM - 1) / TG_BM);
+  constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
+  const int num_tiles = ((N + BN_OUT - 1) / BN_OUT) * ((M + TG_BM - 1) / TG_BM);
   const int ctas = num_tiles < 148 ? num_tiles : 148;     // one persistent CTA per SM
   return launch(kern, ctas, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag);
 }
@@ -230,4 +275,16 @@ extern "C" int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, i
   if (tile_n == 128) { TS_TC(128, 6); }
   TS_TC(256, 4);
 #undef TS_TC
+}
+
+// act[M, inter] = silu(x gate^T) * (x up^T) in bf16 with w = [gate rows; up rows], [2 inter, K]:
+// the product and the activation in one kernel (SWIGLU above). K % 8 == 0.
+extern "C" int ts_gemm_tcgen05_swiglu(const void* x, const void* w, void* out, int M, int inter, int K, int* error_flag,
+                                      cudaStream_t stream) {
+  if (M <= 0 || inter <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, TG_BM) || !make_map(&mw, w, 2 * inter, K, 128)) return TS_ERR_UNSUPPORTED;
+  return launch_tc<256, 4, bf16, true>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
 }

@@ -81,10 +81,13 @@ class Engine:
                  max_batch_tokens: int = 2048, clock: Callable[[], float] = time.perf_counter,
                  seed: int = 0, trace_steps: bool = False, chunked_prefill: bool = False,
                  runner: ModelRunner | None = None, decode_graphs: bool = False,
-                 graph_max_context: int | None = None, run_ahead: bool = True) -> None:
+                 graph_max_context: int | None = None, run_ahead: bool = True, prefill_graph: bool = True) -> None:
         """``decode_graphs``: record the decode step once per batch-size bucket (CUDA graphs)
         and replay it whenever every scheduled request brings one token (upstream passes a
         ``DecodeGraphs`` object for this, src/tinyserve/engine.py:96,188-196).
+
+        ``prefill_graph`` (with ``decode_graphs`` and ``chunked_prefill``): the step of one request
+        that brings a full portion of ``max_batch_tokens`` prompt tokens is recorded too.
 
         ``run_ahead``: while a recorded decode step runs, the next one is launched before its
         tokens are read, fed on the device with the tokens it is about to draw, so the host's
@@ -99,6 +102,8 @@ class Engine:
         if decode_graphs and not self.runner.graphs:
             limit = min(model.spec.max_position_embeddings, cache.num_pages * cache.page_size)
             self.runner.record_decode_graphs(max_num_seqs, graph_max_context or limit)
+            if prefill_graph and chunked_prefill and max_batch_tokens <= (graph_max_context or limit):
+                self.runner.record_prefill_graph(max_batch_tokens, graph_max_context or limit)
         self.scheduler = Scheduler(cache, max_num_seqs, max_batch_tokens, chunked_prefill=chunked_prefill)
         self.sampler = Sampler(model.device, max_rows=max(max_num_seqs, 1))
         self.clock = clock

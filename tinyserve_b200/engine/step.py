@@ -174,6 +174,105 @@ class DecodeGraph:
         self.copied.record()
 
 
+class PrefillGraph:
+    """One recorded step of ONE request that brings exactly ``tokens`` new tokens (a portion of
+    a long prompt, as chunked prefill cuts them) on top of any context up to ``max_context``.
+    A step of a few thousand tokens launches some 250 kernels whose host-side cost is as long
+    as their run time at small model sizes; replayed from a recording it costs one launch. The
+    logits of the portion's last token are always computed (a mid-prompt portion ignores them)."""
+
+    def __init__(self, runner: "ModelRunner", tokens: int, max_context: int) -> None:
+        self.tokens = t = tokens
+        cache, dev = runner.cache, runner.device
+        groups = cache.groups
+        self.width = -(-max_context // cache.page_size)
+        off = 0
+
+        def section(n: int) -> slice:
+            nonlocal off
+            s = slice(off, off + n)
+            off = _round_up(off + n, 4)
+            return s
+
+        self.s_tokens, self.s_pos, self.s_cu, self.s_ctx = section(t), section(t), section(2), section(1)
+        self.s_dec, self.s_pre, self.s_rows, self.s_state = section(1), section(1), section(1), section(1)
+        self.s_slots = [section(t) for _ in groups]
+        self.s_tables = [section(self.width) for _ in groups]
+        self.host = torch.empty(off, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.empty(off, dtype=torch.int32, device=dev)
+        self.copied = torch.cuda.Event()
+        self.arena = Arena(dev)
+        buf = self.host_np
+        buf[:] = 0
+        buf[self.s_cu] = [0, t]
+        buf[self.s_ctx] = t
+        buf[self.s_pos] = np.arange(t)
+        buf[self.s_rows] = t - 1
+        for g, ss, st in zip(groups, self.s_slots, self.s_tables):
+            # until the first fill: every token on the pad page
+            buf[ss] = g.pad_page * g.page_size + np.arange(t) % g.page_size
+            buf[st] = g.pad_page
+        self.dev.copy_(self.host)
+        self._arange = np.arange(t, dtype=np.int64)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+
+    def context(self, runner: "ModelRunner") -> StepContext:
+        t, dev, w = self.tokens, self.dev, self.width
+        cache = runner.cache
+        kv = {g.index: KVGroupContext(g.page_size, dev[st].view(1, w), dev[ss])
+              for g, ss, st in zip(cache.groups, self.s_slots, self.s_tables)}
+        cap = w * cache.page_size
+        return StepContext(
+            num_tokens=t, num_seqs=1, query_lens=[t], context_lens=[cap],
+            tokens=dev[self.s_tokens], positions=dev[self.s_pos], cu_query_lens=dev[self.s_cu],
+            context_lens_dev=dev[self.s_ctx], decode_seqs=dev[self.s_dec], prefill_seqs=dev[self.s_pre],
+            num_decode=0, num_prefill=1, max_query_len=t, max_context_len=cap, kv=kv,
+            state_slots=dev[self.s_state] if cache.has_state else None, state_slots_host=[0],
+            arena=self.arena, dtype=runner.model.dtype)
+
+    def record(self, runner: "ModelRunner") -> None:
+        model, caches = runner.model, runner.cache.entries
+
+        def run() -> torch.Tensor:
+            self.arena.begin_step()
+            with ops.stream_scope():
+                return model.forward(self.context(runner), caches, self.dev[self.s_rows], 1)
+
+        run()
+        run()
+        reserved = self.arena.reserved_bytes
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        with torch.cuda.graph(graph):
+            logits = run()
+        self.num_kernels = ops.launch_count - before
+        ops.launch_count = before          # recorded, not run
+        if self.arena.reserved_bytes != reserved:
+            raise RuntimeError("scratch memory moved while a prefill graph was being recorded")
+        self.graph, self.logits = graph, logits
+
+    def fill(self, runner: "ModelRunner", entry: StepEntry) -> None:
+        self.copied.synchronize()          # the last copy must have left the host buffer
+        buf, t = self.host_np, self.tokens
+        total = entry.cache.num_tokens
+        first = total - t
+        buf[self.s_tokens] = entry.tokens
+        buf[self.s_pos] = self._arange + first
+        buf[self.s_ctx] = total
+        buf[self.s_state] = entry.cache.state_slot
+        for g, ss, st in zip(runner.cache.groups, self.s_slots, self.s_tables):
+            ps = g.page_size
+            arr = entry.cache.tables[g.index].pages_array()
+            buf[st][: arr.shape[0]] = arr
+            pos = self._arange + first
+            buf[ss] = arr[pos // ps].astype(np.int64) * ps + pos % ps
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager) -> None:
         self.model = model
@@ -184,6 +283,7 @@ class ModelRunner:
         # mask itself (measurements) turns this off
         self.tune_launch_overlap = True
         self.graphs: dict[int, DecodeGraph] = {}
+        self.prefill_graphs: dict[int, PrefillGraph] = {}
         self.graph_max_context = 0
         self.num_graph_steps = 0
         self._host: torch.Tensor | None = None     # pinned int32 staging buffer
@@ -327,6 +427,33 @@ class ModelRunner:
             g.record(self)
             self.graphs[rows] = g
 
+    @torch.inference_mode()
+    def record_prefill_graph(self, tokens: int, max_context: int) -> None:
+        """Record the step of one request that brings exactly ``tokens`` tokens. Afterwards such
+        a step (whose request holds at most ``max_context`` tokens, and that wants no logits or
+        those of its last token) is replayed from the recording."""
+        if self.device.type != "cuda":
+            raise RuntimeError("prefill graphs need a CUDA device")
+        if not all(layer.block.mixer.graph_safe for layer in self.model.parts.layers):
+            raise RuntimeError("a mixer of this model reads the step on the host; its steps cannot be recorded")
+        if self.tune_launch_overlap:
+            ops.use_pdl_mask(ops.PREFILL_PDL_MASK)
+        g = PrefillGraph(self, tokens, max_context)
+        g.record(self)
+        self.prefill_graphs[tokens] = g
+        self.prefill_graph_max_context = max_context
+
+    def _prefill_graph_for(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None) -> PrefillGraph | None:
+        if not self.prefill_graphs or len(entries) != 1:
+            return None
+        e = entries[0]
+        g = self.prefill_graphs.get(len(e.tokens))
+        if g is None or e.cache.num_tokens > self.prefill_graph_max_context:
+            return None
+        if want is not None and list(want[0]) not in ([], [len(e.tokens) - 1]):
+            return None
+        return g
+
     def _graph_for(self, entries: Sequence[StepEntry], want: Sequence[Sequence[int]] | None) -> DecodeGraph | None:
         if not self.graphs or len(entries) > max(self.graphs):
             return None
@@ -362,6 +489,14 @@ class ModelRunner:
             self.num_steps += 1
             self.num_graph_steps += 1
             return graph.logits[: len(entries)]
+        pgraph = self._prefill_graph_for(entries, want)
+        if pgraph is not None:
+            pgraph.fill(self, entries[0])
+            pgraph.graph.replay()
+            ops.launch_count += pgraph.num_kernels
+            self.num_steps += 1
+            self.num_graph_steps += 1
+            return None if want is not None and not list(want[0]) else pgraph.logits
         ctx, rows, r = self.build_context(entries, want)
         if self.tune_launch_overlap and self.device.type == "cuda":
             ops.use_pdl_mask(ops.PREFILL_PDL_MASK if ctx.num_prefill else ops.DEFAULT_PDL_MASK)

@@ -54,6 +54,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "ts_gemm_tcgen05_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp, _vp],
     "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _fns: dict[str, Any] = {}
@@ -539,7 +540,8 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
     """``out[M, I] = silu(x Wgate^T) * (x Wup^T)`` with ``w_gate_up`` = gate rows then up rows,
     ``[2 I, K]``. For a few bf16 rows the product and the activation are one kernel (the gate
     and up rows of an output column are computed by the same CTA); otherwise a product into
-    scratch from ``arena`` followed by the SiLU-multiply kernel."""
+    scratch from ``arena`` followed by the SiLU-multiply kernel; many bf16 rows of a wide matrix
+    take the tcgen05 product with the activation in its epilogue."""
     m, k = x.shape
     inter = out.shape[1]
     if tuple(w_gate_up.shape) != (2 * inter, k) or out.shape[0] != m or out.dtype != x.dtype:
@@ -548,6 +550,11 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
             and 2 * inter * k <= SKINNY_MAX_WEIGHTS):
         _check(_fn("ts_gemm_skinny_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
                                             _stream()), "gemm_swiglu")
+        return
+    if x.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and 2 * inter >= TCGEN05_MIN_COLS and k % 8 == 0:
+        # many rows: the tcgen05 product with the activation in its epilogue
+        _check(_fn("ts_gemm_tcgen05_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
+                                             _error_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_swiglu")
         return
     gate_up = arena.take((m, 2 * inter), x.dtype)
     gemm(x, w_gate_up, gate_up)
