@@ -22,6 +22,13 @@
 //   warp 4 NQ + 1       : allocates tensor memory; one lane issues every tcgen05.mma and the
 //                         tcgen05.commit that tells the other roles what has finished; zeroes V
 //                         rows outside the live key range (0 x garbage would not be 0)
+// Where the time goes (B200, 16 / 8 heads of 128): a tile step (128 rows x 128 keys) costs 1,024
+// cycles of tensor core (16 instructions of 128 x 128 x 16 at the measured 64 cycles each) and
+// 1,024 cycles of the exponential unit, but also 64 KB of K and V from L2, and the kernel runs at
+// about 3,500 cycles a step = 18 bytes per cycle and SM = 5 TB/s over the chip, which is what L2
+// delivers: at 8,192 tokens 630 TFLOP/s. Splitting the softmax over more warps (by columns, or by
+// alternating tiles with two accumulators) changed nothing for that reason; the way on is more
+// query rows per key tile in a CTA (NQ = 2 below, so far held back by its tiles of 64 keys).
 // Every wait is bounded and gives up at once when another role has: the CTA then records the
 // failure in *error_flag, waits for its copies in flight, frees its tensor memory and returns.
 #define TS_PDL_CLASS PDL_ATTENTION
@@ -50,13 +57,6 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-
-#ifdef TS_FA_TIMING
-__device__ unsigned long long fa_prof[16];
-#define FA_T(i) do { const long long now_ = clock64(); t_acc[i] += now_ - t_prev; t_prev = now_; } while (0)
-#else
-#define FA_T(i) do { } while (0)
-#endif
 
 // A wait of a whole warp with one outcome for all its lanes.
 __device__ __forceinline__ bool fa_warp_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
@@ -118,11 +118,6 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
   const int kvh = head0 / (a.num_heads / a.num_kv_heads);
 
   pdl_trigger();
-#ifdef TS_FA_TIMING
-  long long t_acc[13] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long t_prev = clock64();
-  const long long t_enter = t_prev;
-#endif
   unsigned char* smem = (unsigned char*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -143,7 +138,6 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   pdl_wait();      // q and the cache rows of this step are written by the kernels before
-  FA_T(8);
 
   if (warp < SOFTMAX_WARPS) {
     // =========================================================== softmax warps of query head q
@@ -180,12 +174,9 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
     const int p_abs = p_lo + r;
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
-    FA_T(9);
     for (int j = 0; j < n_tiles; ++j) {
-      FA_T(0);
       if (!fa_warp_wait(&s_full[q], j & 1, failed)) { ok = false; break; }
       tc_fence_after();
-      FA_T(1);
       uint32_t sraw[BN];
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld_32_nowait(tmem_s + c * 32, sraw + c * 32);
@@ -193,7 +184,6 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[q]);                  // S may be overwritten by the next tile's product
-      FA_T(2);
       const int k0 = (t_begin + j) * BN;
       const bool edge = (k0 + BN - 1 > p_lo) || (a.window > 0 && k0 < p_lo + FA_BM - a.window);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: the maxima do not wait on one another
@@ -212,7 +202,6 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * a.scale_log2);
-      FA_T(3);
       if (j == 0) {
         m_used = m_new;
       } else {
@@ -234,7 +223,6 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
           if (grow) { l_sum *= alpha; m_used = m_new; }
         }
       }
-      FA_T(4);
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
       float add4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -245,13 +233,11 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       }
       const float add = (add4[0] + add4[1]) + (add4[2] + add4[3]);
       l_sum += add;
-      FA_T(5);
       const int pb = j % FA_PBUF;
       if (j >= FA_PBUF) {
         // the product that read this P buffer two tiles ago must be done
         if (!fa_warp_wait(&pv_done[q][pb], ((j / FA_PBUF) - 1) & 1, failed)) { ok = false; break; }
       }
-      FA_T(6);
       unsigned char* p_tile = smem + L::OFF_P + (q * FA_PBUF + pb) * L::P_BYTES;
 #pragma unroll
       for (int c = 0; c < BN / 8; ++c) {
@@ -265,13 +251,11 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[q][pb]);
-      FA_T(7);
     }
     if (ok) {
       const int last = n_tiles - 1;
       ok = fa_warp_wait(&pv_done[q][last % FA_PBUF], (last / FA_PBUF) & 1, failed);
     }
-    FA_T(10);
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l_sum;
@@ -407,18 +391,10 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       __syncwarp();
     }
   }
-  FA_T(11);
   if (*failed && (threadIdx.x & 31) == 0) atomicExch(error_flag, 1);
   tc_fence_before();
   __syncthreads();
   if (warp == SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
-  FA_T(12);
-#ifdef TS_FA_TIMING
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < 13; ++i) atomicAdd(&fa_prof[i], (unsigned long long)t_acc[i]);
-    atomicAdd(&fa_prof[14], (unsigned long long)(clock64() - t_enter)); atomicAdd(&fa_prof[15], 1ull);
-  }
-#endif
 }
 
 // ---------------------------------------------------------------- host side
@@ -474,17 +450,6 @@ static int launch_fa(const AttnArgs& a, long long cache_rows, int max_query_len,
 
 using namespace ts;
 
-#ifdef TS_FA_TIMING
-extern "C" int ts_fa_timing_read(unsigned long long* host16, int reset) {
-  cudaError_t e = cudaMemcpyFromSymbol(host16, fa_prof, sizeof(unsigned long long) * 16);
-  if (e == cudaSuccess && reset) {
-    unsigned long long z[16] = {0};
-    e = cudaMemcpyToSymbol(fa_prof, z, sizeof(z));
-  }
-  return (int)e;
-}
-#endif
-
 // bf16 prefill attention on tcgen05 for the requests listed in prefill_seqs. head_dim 64 or 128;
 // page_size 8 or a multiple of 16; num_pages_total = pages of the cache tensors (the pad page
 // included). heads_per_cta: 1 or 2 query heads of a kv group share a CTA's key and value tiles
@@ -518,9 +483,6 @@ extern "C" int ts_prefill_attention_tcgen05(
 #define TS_FA(D64_, BR_)                                                                                   \
   return heads_per_cta == 2 ? launch_fa<D64_, BR_, 2, 64>(a, rows, max_query_len, error_flag, stream)      \
                             : launch_fa<D64_, BR_, 1, 128>(a, rows, max_query_len, error_flag, stream)
-#ifdef TS_FA_BIG_BOX
-  if (head_dim == 128 && page_size % 128 == 0 && heads_per_cta == 1) return launch_fa<2, 128, 1, 128>(a, rows, max_query_len, error_flag, stream);
-#endif
   if (head_dim == 64) {
     if (page_size == 8) { TS_FA(1, 8); }
     TS_FA(1, 16);
