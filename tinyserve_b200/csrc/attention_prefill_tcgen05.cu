@@ -3,34 +3,35 @@
 // (upstream src/tinyserve/attention.py:89-111, src/tinyserve/triton_prefill.py:50-125):
 // S = Q K^T * scale, causal (and window) mask, softmax in 32-bit, O = P V.
 //
-// A CTA owns 128 consecutive tokens of one request for NQ query heads of one kv group (NQ = 1 or
-// 2; the heads of a group share the key and value tiles). Both products run as tcgen05.mma with
-// the accumulators in tensor memory:
-//   S_q = Q_q K^T : A = Q_q  [128 x D]   K-major, shared memory, 128-byte swizzle
-//                   B = K    [BN x D]    K-major, the cache rows as TMA delivers them
-//   O_q += P_q V  : A = P_q  [128 x BN]  K-major, written to shared memory by the softmax warps
-//                   B = V    [BN x D]    read as it lies in the cache: MN-major (D contiguous)
+// A CTA owns 128 consecutive tokens of one request for one query head. Both products run as
+// tcgen05.mma with the accumulators in tensor memory:
+//   S = Q K^T : A = Q  [128 x D]    K-major, shared memory, 128-byte swizzle
+//               B = K  [128 x D]    K-major, the cache rows as TMA delivers them
+//   O += P V  : A = P  [128 x 128]  bf16 in tensor memory, written there by the softmax warps over
+//                                   the scores they were computed from
+//               B = V  [128 x D]    read as it lies in the cache: MN-major (D contiguous)
+// Tensor memory: two score / probability buffers of 128 columns, used by alternate tiles, and O.
 // Roles:
-//   warps 0 .. 4 NQ - 1 : softmax; four warps per query head, one thread per row: reads its row of
-//                         S from tensor memory (tcgen05.ld), masks, keeps the running maximum and
-//                         sum, writes P as bf16 into the swizzled operand layout, and scales O in
-//                         tensor memory only when the maximum has grown by more than 2^8 (the
-//                         sum and O then simply carry a common factor that the final division
-//                         removes); at the end divides O by the sum and stores it
-//   warp 4 NQ           : TMA producer: K and V tiles of BN positions, double-buffered, a box per
-//                         page part and 64 columns, one lane per box
-//   warp 4 NQ + 1       : allocates tensor memory; one lane issues every tcgen05.mma and the
-//                         tcgen05.commit that tells the other roles what has finished; zeroes V
-//                         rows outside the live key range (0 x garbage would not be 0)
+//   warps 0-3 : softmax, one thread per row: reads its row of S (tcgen05.ld), masks, keeps the
+//               running maximum and sum, writes P as bf16 over the first 64 columns of the same
+//               buffer (tcgen05.st), and scales O in tensor memory only when the maximum has
+//               grown by more than 2^8 (the sum and O then simply carry a common factor that the
+//               final division removes); at the end divides O by the sum and stores it
+//   warp 4    : TMA producer: K and V tiles of 128 positions, three stages, a box per page part
+//               and 64 columns, one lane per box
+//   warp 5    : allocates tensor memory; one lane issues every tcgen05.mma and the
+//               tcgen05.commit that tells the other roles what has finished; zeroes V rows
+//               outside the live key range (0 x garbage would not be 0). S of tile j + 1 is
+//               issued before P V of tile j, so it is computed while the softmax warps work on
+//               tile j; it goes to the buffer that P of tile j - 1 was read from by a product
+//               issued earlier, and the tensor core runs them in order.
 // Where the time goes (B200, 16 / 8 heads of 128): a tile step (128 rows x 128 keys) costs 1,024
 // cycles of tensor core (16 instructions of 128 x 128 x 16 at the measured 64 cycles each) and
-// 1,024 cycles of the exponential unit, but also 64 KB of K and V from L2, and the kernel runs at
-// about 3,500 cycles a step = 18 bytes per cycle and SM = 5 TB/s over the chip, which is what L2
-// delivers: at 8,192 tokens 630 TFLOP/s. Splitting the softmax over more warps (by columns, or by
-// alternating tiles with two accumulators) changed nothing for that reason; the way on is more
-// query rows per key tile in a CTA (NQ = 2 below, so far held back by its tiles of 64 keys).
-// Every wait is bounded and gives up at once when another role has: the CTA then records the
-// failure in *error_flag, waits for its copies in flight, frees its tensor memory and returns.
+// 1,024 cycles of the exponential unit; every operand read from shared memory and every TMA
+// write goes through the same 128 bytes per cycle, which is why P stays in tensor memory.
+// Every wait is on an mbarrier, is bounded and gives up at once when another role has: the CTA
+// then records the failure in *error_flag, waits for its copies in flight, frees its tensor
+// memory and returns.
 #define TS_PDL_CLASS PDL_ATTENTION
 #include <cuda.h>
 
@@ -43,9 +44,10 @@
 
 namespace ts {
 
-constexpr int FA_BM = 128;
-constexpr int FA_KV_STAGES = 2;
-constexpr int FA_PBUF = 2;
+constexpr int FA_BM = 128, FA_BN = 128;
+constexpr int FA_KV_STAGES = 3;
+constexpr int FA_SOFTMAX_WARPS = 4;
+constexpr int FA_THREADS = (FA_SOFTMAX_WARPS + 2) * 32;
 constexpr float FA_RESCALE_STEP = 8.f;      // log2 of the growth of a row maximum that is tolerated without scaling O
 
 __device__ __forceinline__ float fa_exp2(float x) {
@@ -63,30 +65,27 @@ __device__ __forceinline__ bool fa_warp_wait(uint64_t* bar, uint32_t parity, vol
   return __all_sync(0xffffffffu, mbar_wait_or_fail(bar, parity, failed) ? 1 : 0) != 0;
 }
 
-template <int D64, int BR, int NQ, int BN>
+template <int D64>
 struct FaLayout {
   static constexpr int D = 64 * D64;
-  static constexpr uint32_t Q_BYTES = FA_BM * D * 2;          // per query head
-  static constexpr uint32_t KV_BYTES = BN * D * 2;            // one K or V tile
-  static constexpr uint32_t P_BYTES = FA_BM * BN * 2;
+  static constexpr uint32_t Q_BYTES = FA_BM * D * 2;
+  static constexpr uint32_t KV_BYTES = FA_BN * D * 2;         // one K or V tile
   static constexpr uint32_t OFF_Q = 0;
-  static constexpr uint32_t OFF_K = OFF_Q + NQ * Q_BYTES;
+  static constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
   static constexpr uint32_t OFF_V = OFF_K + FA_KV_STAGES * KV_BYTES;
-  static constexpr uint32_t OFF_P = OFF_V + FA_KV_STAGES * KV_BYTES;
-  static constexpr uint32_t TOTAL = OFF_P + NQ * FA_PBUF * P_BYTES;
-  static constexpr uint32_t TMEM_PER_Q = BN + D;              // S then O
-  static constexpr uint32_t TMEM_NEED = NQ * TMEM_PER_Q;
-  static constexpr uint32_t TMEM_COLS = TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512);
-  static constexpr int THREADS = (4 * NQ + 2) * 32;
+  static constexpr uint32_t TOTAL = OFF_V + FA_KV_STAGES * KV_BYTES;
+  static constexpr uint32_t TMEM_SP = 0, TMEM_O = 2 * FA_BN;  // S/P buffer 0, S/P buffer 1, O
+  static constexpr uint32_t TMEM_COLS = 512;
 };
 
-template <int D64, int BR, int NQ, int BN>
-__global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k,
-                                                                            const __grid_constant__ CUtensorMap map_v,
-                                                                            AttnArgs a, int* error_flag) {
-  using L = FaLayout<D64, BR, NQ, BN>;
-  constexpr int D = L::D;
-  constexpr int SOFTMAX_WARPS = 4 * NQ;
+// D64 = head_dim / 64; BR = rows of a tensor box (16, or 8 for pages of 8).
+// blockIdx = (query head, tile of 128 tokens counted from the end, request in the list).
+template <int D64, int BR>
+__global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                     const __grid_constant__ CUtensorMap map_v,
+                                                                     AttnArgs a, int* error_flag) {
+  using L = FaLayout<D64>;
+  constexpr int D = L::D, BN = FA_BN;
   // instruction descriptors: D = f32, A = B = bf16, M = 128; S: N = BN, both operands K-major;
   // PV: N = D, B MN-major (bit 16)
   constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
@@ -94,7 +93,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
   extern __shared__ unsigned char fa_raw[];
   __shared__ __align__(8) uint64_t k_full[FA_KV_STAGES], k_empty[FA_KV_STAGES], v_full[FA_KV_STAGES], v_empty[FA_KV_STAGES];
-  __shared__ __align__(8) uint64_t s_full[NQ], s_free[NQ], p_full[NQ][FA_PBUF], pv_done[NQ][FA_PBUF], q_ready;
+  __shared__ __align__(8) uint64_t s_full[2], p_full[2], pv_done[2], q_ready;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed_flag;
   volatile int* failed = &failed_flag;
@@ -114,8 +113,8 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
   const int lo = a.window > 0 ? max(0, p_lo - a.window + 1) : 0;   // first key any row sees
   const int t_begin = lo / BN;
   const int n_tiles = (p_hi + 1 + BN - 1) / BN - t_begin;     // >= 1
-  const int head0 = (int)blockIdx.x * NQ;
-  const int kvh = head0 / (a.num_heads / a.num_kv_heads);
+  const int head = (int)blockIdx.x;
+  const int kvh = head / (a.num_heads / a.num_kv_heads);
 
   pdl_trigger();
   unsigned char* smem = (unsigned char*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
@@ -124,33 +123,28 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
     for (int s = 0; s < FA_KV_STAGES; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int q = 0; q < NQ; ++q) {
-      mbar_init(&s_full[q], 1); mbar_init(&s_free[q], 4);
-      for (int b = 0; b < FA_PBUF; ++b) { mbar_init(&p_full[q][b], 4); mbar_init(&pv_done[q][b], 1); }
-    }
-    mbar_init(&q_ready, SOFTMAX_WARPS);
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], FA_SOFTMAX_WARPS); mbar_init(&pv_done[b], 1); }
+    mbar_init(&q_ready, FA_SOFTMAX_WARPS);
     failed_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == SOFTMAX_WARPS + 1) tmem_alloc(&tmem_base_slot, L::TMEM_COLS);
+  if (warp == FA_SOFTMAX_WARPS + 1) tmem_alloc(&tmem_base_slot, L::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   pdl_wait();      // q and the cache rows of this step are written by the kernels before
 
-  if (warp < SOFTMAX_WARPS) {
-    // =========================================================== softmax warps of query head q
-    const int q = warp >> 2, quad = warp & 3;
+  if (warp < FA_SOFTMAX_WARPS) {
+    // =========================================================== softmax warps
+    const int quad = warp;
     const int r = quad * 32 + lane;                            // this thread's row
-    const int head = head0 + q;
-    unsigned char* q_tile = smem + L::OFF_Q + q * L::Q_BYTES;
+    unsigned char* q_tile = smem + L::OFF_Q;
     {
-      // Q rows into the swizzled operand layout: 16 (or 8) lanes fetch a row, 16 bytes each
+      // Q rows into the swizzled operand layout: 16 (or 8) threads fetch a row, 16 bytes each
       constexpr int CPR = D / 8;                               // 16-byte chunks per row
       constexpr int RPP = 128 / CPR, PASSES = FA_BM / RPP;     // rows per pass of the 128 threads
-      const int tq = threadIdx.x & 127;
-      const int c = tq % CPR, row0 = tq / CPR;
+      const int c = threadIdx.x % CPR, row0 = threadIdx.x / CPR;
       uint4 v[PASSES];
 #pragma unroll
       for (int i = 0; i < PASSES; ++i) {                       // every load in flight before the first store
@@ -169,21 +163,19 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       if (lane == 0) mbar_arrive(&q_ready);
     }
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    const uint32_t tmem_s = tmem_base + lane_addr + (uint32_t)(q * L::TMEM_PER_Q);
-    const uint32_t tmem_o = tmem_s + BN;
+    const uint32_t tmem_o = tmem_base + lane_addr + L::TMEM_O;
     const int p_abs = p_lo + r;
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      if (!fa_warp_wait(&s_full[q], j & 1, failed)) { ok = false; break; }
+      const int b = j & 1;
+      const uint32_t tmem_sp = tmem_base + lane_addr + L::TMEM_SP + (uint32_t)(b * BN);
+      if (!fa_warp_wait(&s_full[b], (j >> 1) & 1, failed)) { ok = false; break; }
       tc_fence_after();
       uint32_t sraw[BN];
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) tmem_ld_32_nowait(tmem_s + c * 32, sraw + c * 32);
+      for (int c = 0; c < BN / 32; ++c) tmem_ld_32_nowait(tmem_sp + c * 32, sraw + c * 32);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[q]);                  // S may be overwritten by the next tile's product
       const int k0 = (t_begin + j) * BN;
       const bool edge = (k0 + BN - 1 > p_lo) || (a.window > 0 && k0 < p_lo + FA_BM - a.window);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: the maxima do not wait on one another
@@ -207,8 +199,8 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       } else {
         const bool grow = m_new > m_used + FA_RESCALE_STEP;    // also when nothing was seen before (-inf)
         if (__any_sync(0xffffffffu, grow)) {
-          // O of this head is final up to tile j - 1 before it is scaled
-          if (!fa_warp_wait(&pv_done[q][(j - 1) % FA_PBUF], ((j - 1) / FA_PBUF) & 1, failed)) { ok = false; break; }
+          // O is final up to tile j - 1 before it is scaled
+          if (!fa_warp_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, failed)) { ok = false; break; }
           tc_fence_after();
           const float alpha = grow ? (m_used == -INFINITY ? 0.f : fa_exp2(m_used - m_new)) : 1.f;
 #pragma unroll 1
@@ -219,42 +211,33 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
             tmem_st_32(tmem_o + c * 32, o);
           }
-          tc_fence_before();
           if (grow) { l_sum *= alpha; m_used = m_new; }
         }
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
       float add4[4] = {0.f, 0.f, 0.f, 0.f};
+      // P as bf16, two keys per 32-bit column, over the first half of this buffer's columns
 #pragma unroll
-      for (int i = 0; i < BN; ++i) {
-        const float p = fa_exp2(fmaf(__uint_as_float(sraw[i]), a.scale_log2, -m_sub));
-        add4[i & 3] += p;
-        sraw[i] = __float_as_uint(p);
-      }
-      const float add = (add4[0] + add4[1]) + (add4[2] + add4[3]);
-      l_sum += add;
-      const int pb = j % FA_PBUF;
-      if (j >= FA_PBUF) {
-        // the product that read this P buffer two tiles ago must be done
-        if (!fa_warp_wait(&pv_done[q][pb], ((j / FA_PBUF) - 1) & 1, failed)) { ok = false; break; }
-      }
-      unsigned char* p_tile = smem + L::OFF_P + (q * FA_PBUF + pb) * L::P_BYTES;
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
-        uint4 v;
-        v.x = fa_pack(__uint_as_float(sraw[c * 8 + 0]), __uint_as_float(sraw[c * 8 + 1]));
-        v.y = fa_pack(__uint_as_float(sraw[c * 8 + 2]), __uint_as_float(sraw[c * 8 + 3]));
-        v.z = fa_pack(__uint_as_float(sraw[c * 8 + 4]), __uint_as_float(sraw[c * 8 + 5]));
-        v.w = fa_pack(__uint_as_float(sraw[c * 8 + 6]), __uint_as_float(sraw[c * 8 + 7]));
-        *reinterpret_cast<uint4*>(p_tile + (c >> 3) * (FA_BM * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fa_exp2(fmaf(__uint_as_float(sraw[c * 64 + 2 * i]), a.scale_log2, -m_sub));
+          const float p1 = fa_exp2(fmaf(__uint_as_float(sraw[c * 64 + 2 * i + 1]), a.scale_log2, -m_sub));
+          add4[i & 3] += p0 + p1;
+          packed[i] = fa_pack(p0, p1);
+        }
+        tmem_st_32_nowait(tmem_sp + c * 32, packed);
       }
-      fence_proxy_async_smem();
+      l_sum += (add4[0] + add4[1]) + (add4[2] + add4[3]);
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[q][pb]);
+      if (lane == 0) mbar_arrive(&p_full[b]);
     }
     if (ok) {
       const int last = n_tiles - 1;
-      ok = fa_warp_wait(&pv_done[q][last % FA_PBUF], (last / FA_PBUF) & 1, failed);
+      ok = fa_warp_wait(&pv_done[last & 1], (last >> 1) & 1, failed);
     }
     if (ok) {
       tc_fence_after();
@@ -277,7 +260,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
         }
       }
     }
-  } else if (warp == SOFTMAX_WARPS) {
+  } else if (warp == FA_SOFTMAX_WARPS) {
     // =========================================================== TMA producer
     const int* table = a.block_tables + (size_t)seq * a.table_width;
     constexpr int PARTS = BN / BR;
@@ -328,26 +311,22 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
     bool ok = fa_warp_wait(&q_ready, 0, failed);
     const uint32_t q_addr = smem_u32(smem + L::OFF_Q);
     const uint32_t k_addr = smem_u32(smem + L::OFF_K), v_addr = smem_u32(smem + L::OFF_V);
-    const uint32_t p_addr = smem_u32(smem + L::OFF_P);
-    // S_q = Q_q K^T of tile j (all query heads), then the K stage is handed back
+    // S = Q K^T of tile j into buffer j % 2, then the K stage is handed back. The buffer held P
+    // of tile j - 2, whose product was issued before and so is executed before.
     auto issue_s = [&](int j) -> bool {
-      const int st = j % FA_KV_STAGES;
+      const int st = j % FA_KV_STAGES, b = j & 1;
       if (!fa_warp_wait(&k_full[st], (j / FA_KV_STAGES) & 1, failed)) return false;
-      for (int q = 0; q < NQ; ++q) {
-        if (j > 0 && !fa_warp_wait(&s_free[q], (j - 1) & 1, failed)) return false;
-        tc_fence_after();
-        if (lane == 0) {
+      tc_fence_after();
+      if (lane == 0) {
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint64_t ad = sw128_desc(q_addr + q * L::Q_BYTES + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32);
-            const uint64_t bd = sw128_desc(k_addr + st * L::KV_BYTES + (ks >> 2) * (BN * 128) + (ks & 3) * 32);
-            umma_bf16(tmem_base + (uint32_t)(q * L::TMEM_PER_Q), ad, bd, IDESC_S, ks != 0);
-          }
-          umma_commit(&s_full[q]);
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t ad = sw128_desc(q_addr + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32);
+          const uint64_t bd = sw128_desc(k_addr + st * L::KV_BYTES + (ks >> 2) * (BN * 128) + (ks & 3) * 32);
+          umma_bf16(tmem_base + L::TMEM_SP + (uint32_t)(b * BN), ad, bd, IDESC_S, ks != 0);
         }
-        __syncwarp();
+        umma_commit(&s_full[b]);
+        umma_commit(&k_empty[st]);
       }
-      if (lane == 0) umma_commit(&k_empty[st]);
       __syncwarp();
       return true;
     };
@@ -357,7 +336,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
         ok = issue_s(j + 1);
         if (!ok) break;
       }
-      const int st = j % FA_KV_STAGES;
+      const int st = j % FA_KV_STAGES, b = j & 1;
       if (!fa_warp_wait(&v_full[st], (j / FA_KV_STAGES) & 1, failed)) { ok = false; break; }
       const int k0 = (t_begin + j) * BN;
       if (k0 < lo || k0 + BN > ctx) {
@@ -372,29 +351,24 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
         fence_proxy_async_smem();
         __syncwarp();
       }
-      for (int q = 0; q < NQ && ok; ++q) {
-        const int pb = j % FA_PBUF;
-        if (!fa_warp_wait(&p_full[q][pb], (j / FA_PBUF) & 1, failed)) { ok = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
+      if (!fa_warp_wait(&p_full[b], (j >> 1) & 1, failed)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
 #pragma unroll
-          for (int ks = 0; ks < BN / 16; ++ks) {
-            const uint64_t ad = sw128_desc(p_addr + (q * FA_PBUF + pb) * L::P_BYTES + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32);
-            const uint64_t bd = sw128_desc_mn(v_addr + st * L::KV_BYTES + ks * (16 * 128), BN * 128);
-            umma_bf16(tmem_base + (uint32_t)(q * L::TMEM_PER_Q + BN), ad, bd, IDESC_PV, (j | ks) != 0);
-          }
-          umma_commit(&pv_done[q][pb]);
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          const uint64_t bd = sw128_desc_mn(v_addr + st * L::KV_BYTES + ks * (16 * 128), BN * 128);
+          umma_bf16_ta(tmem_base + L::TMEM_O, tmem_base + L::TMEM_SP + (uint32_t)(b * BN + ks * 8), bd, IDESC_PV, (j | ks) != 0);
         }
-        __syncwarp();
+        umma_commit(&pv_done[b]);
+        umma_commit(&v_empty[st]);
       }
-      if (lane == 0) umma_commit(&v_empty[st]);
       __syncwarp();
     }
   }
   if (*failed && (threadIdx.x & 31) == 0) atomicExch(error_flag, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
+  if (warp == FA_SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
 }
 
 // ---------------------------------------------------------------- host side
@@ -432,18 +406,18 @@ static const CUtensorMap* fa_cache_map(const void* base, long long rows, int hea
   return &maps.emplace(key, m).first->second;
 }
 
-template <int D64, int BR, int NQ, int BN>
+template <int D64, int BR>
 static int launch_fa(const AttnArgs& a, long long cache_rows, int max_query_len, int* error_flag, cudaStream_t stream) {
-  using L = FaLayout<D64, BR, NQ, BN>;
+  using L = FaLayout<D64>;
   const CUtensorMap* mk = fa_cache_map(a.k_cache, cache_rows, L::D, BR);
   const CUtensorMap* mv = fa_cache_map(a.v_cache, cache_rows, L::D, BR);
   if (mk == nullptr || mv == nullptr) return TS_ERR_UNSUPPORTED;
   const size_t smem = (size_t)L::TOTAL + 1024;
-  auto kern = prefill_attn_tc_kernel<D64, BR, NQ, BN>;
+  auto kern = prefill_attn_tc_kernel<D64, BR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid(a.num_heads / NQ, (max_query_len + FA_BM - 1) / FA_BM, a.num_seqs);
-  return launch(kern, grid, L::THREADS, smem, stream, *mk, *mv, a, error_flag);
+  dim3 grid(a.num_heads, (max_query_len + FA_BM - 1) / FA_BM, a.num_seqs);
+  return launch(kern, grid, FA_THREADS, smem, stream, *mk, *mv, a, error_flag);
 }
 
 }  // namespace ts
@@ -452,14 +426,12 @@ using namespace ts;
 
 // bf16 prefill attention on tcgen05 for the requests listed in prefill_seqs. head_dim 64 or 128;
 // page_size 8 or a multiple of 16; num_pages_total = pages of the cache tensors (the pad page
-// included). heads_per_cta: 1 or 2 query heads of a kv group share a CTA's key and value tiles
-// (2 needs an even group); 0 picks 2 where it can. Returns TS_ERR_UNSUPPORTED for sizes it does
-// not take.
+// included). Returns TS_ERR_UNSUPPORTED for sizes it does not take.
 extern "C" int ts_prefill_attention_tcgen05(
     const void* q, void* out, const void* k_cache, const void* v_cache, long long num_pages_total,
     const int* block_tables, int table_width, const int* cu_q, const int* ctx_lens, const int* prefill_seqs,
     int num_prefill, int max_query_len, int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
-    int window, int heads_per_cta, int* error_flag, cudaStream_t stream) {
+    int window, int* error_flag, cudaStream_t stream) {
   if (num_prefill <= 0 || max_query_len <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
   if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
@@ -467,10 +439,6 @@ extern "C" int ts_prefill_attention_tcgen05(
   if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache) | ((uintptr_t)q) | ((uintptr_t)out)) & 15) return TS_ERR_UNSUPPORTED;
   const long long rows = num_pages_total * num_kv_heads * page_size;
   if (rows >= (1ll << 31)) return TS_ERR_UNSUPPORTED;
-  const int group = num_heads / num_kv_heads;
-  if (heads_per_cta == 0) heads_per_cta = (group % 2 == 0) ? 2 : 1;
-  if (heads_per_cta != 1 && heads_per_cta != 2) return TS_ERR_BAD_ARGUMENT;
-  if (heads_per_cta == 2 && group % 2 != 0) return TS_ERR_UNSUPPORTED;
   AttnArgs a;
   a.q = q; a.out = out; a.k_cache = k_cache; a.v_cache = v_cache;
   a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
@@ -480,14 +448,9 @@ extern "C" int ts_prefill_attention_tcgen05(
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.num_splits = 1; a.part_acc = nullptr; a.part_ml = nullptr;
-#define TS_FA(D64_, BR_)                                                                                   \
-  return heads_per_cta == 2 ? launch_fa<D64_, BR_, 2, 64>(a, rows, max_query_len, error_flag, stream)      \
-                            : launch_fa<D64_, BR_, 1, 128>(a, rows, max_query_len, error_flag, stream)
-  if (head_dim == 64) {
-    if (page_size == 8) { TS_FA(1, 8); }
-    TS_FA(1, 16);
-  }
-  if (page_size == 8) { TS_FA(2, 8); }
-  TS_FA(2, 16);
-#undef TS_FA
+  if (head_dim == 64)
+    return page_size == 8 ? launch_fa<1, 8>(a, rows, max_query_len, error_flag, stream)
+                          : launch_fa<1, 16>(a, rows, max_query_len, error_flag, stream);
+  return page_size == 8 ? launch_fa<2, 8>(a, rows, max_query_len, error_flag, stream)
+                        : launch_fa<2, 16>(a, rows, max_query_len, error_flag, stream);
 }

@@ -46,7 +46,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_prefill_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
                                  _i, _vp, _vp],
     "ts_prefill_attention_tcgen05": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                     _f, _i, _i, _vp, _vp],
+                                     _f, _i, _vp, _vp],
     "ts_gemm_skinny_normed": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_to_stream": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_prefetch_l2": [_vp, _vp, _i, _vp],
@@ -236,11 +236,8 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: torch.T
 
 # -------------------------------------------------------------------- attention
 # The bf16 prefill kernel for head sizes 64 / 128: "tcgen05" (tensor memory accumulators) or "mma"
-# (mma.sync with TMA tiles); and how many query heads of a kv group share a CTA of the former
-# (0: two where the group is even; measured on B200 at 16 / 8 heads of 128: one head with tiles of
-# 128 keys beats two heads with tiles of 64 by 10 to 20 %).
+# (mma.sync with TMA tiles).
 PREFILL_ATTENTION = "tcgen05"
-PREFILL_HEADS_PER_CTA = 1
 TARGET_DECODE_CTAS = 148 * 4
 MIN_KEYS_PER_SPLIT = 64
 MAX_SPLITS = 32
@@ -302,7 +299,6 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                 _dev(ctx.context_lens_dev, "context_lens", torch.int32),
                 _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
                 hq, hkv, d, page_size, float(scale), int(window),
-                PREFILL_HEADS_PER_CTA if (hq // hkv) % 2 == 0 else 1,
                 _error_word(q.device).data_ptr(), _stream()), "prefill_attention_tcgen05")
         elif tma_ok:
             _check(_fn("ts_prefill_attention_tma")(
