@@ -68,6 +68,37 @@ def test_steps_launched_ahead_change_nothing(tiny, name) -> None:
     assert outs[0] == outs[1]
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_everything_at_once_still_equals_plain(tiny, name) -> None:
+    """Recorded decode steps, the recorded prompt portion, steps launched ahead, chunked prompts and
+    a cache so small that requests are preempted and recomputed, together: greedy tokens still
+    equal the plain implementation's, and every page comes back."""
+    from tinyserve_b200 import LLM
+
+    folder, page, _, _ = tiny[name]
+    cfg = TINIES[name][0]
+    pc, pw = plain.read_config(folder), plain.read_weights(folder, torch.float32)
+    prompts = [random_prompt(n, cfg["vocab_size"], 80 + i) for i, n in enumerate([3, 29, 16, 41, 8, 33])]
+    new = 12
+    want = [plain.greedy(pc, pw, p, new) for p in prompts]
+    longest = max(len(p) for p in prompts) + new
+    pages = -(-longest // page) + 3                         # room for the longest request and little more
+    llm = LLM.from_folder(folder, dtype="float32", page_size=page, num_pages=pages, max_num_seqs=4,
+                          max_batch_tokens=16, chunked_prefill=True, decode_graphs=True)
+    e = llm.engine
+    assert e.runner.prefill_graphs, "the prompt portion of the step budget should have been recorded"
+    ids = [e.add_request(p, new) for p in prompts[:4]]
+    steps = 0
+    while e.has_work():
+        e.step()
+        steps += 1
+        if steps == 5:
+            ids += [e.add_request(p, new) for p in prompts[4:]]     # late arrivals
+    assert [e.requests[i].output for i in ids] == want
+    assert e.scheduler.num_preemptions > 0 and e.num_steps_ahead > 0 and e.runner.num_graph_steps > 0
+    assert all(g.allocator.num_used == 0 for g in llm.cache.groups)
+
+
 def test_greedy_bfloat16_close_to_plain_and_tight_cache(tiny) -> None:
     from tinyserve_b200 import LLM
 
