@@ -16,7 +16,8 @@ constexpr int PF_MAX_RANGES = 8;
 // runs beside. Measured on B200 (Qwen3-0.6B sizes, batch 8): spread thinly over all SMs the same
 // requests are served at 5.7 TB/s but take the bandwidth from the attention kernel (step 1.144 ms
 // instead of 1.126 ms); slower than this, the step waits for the prefetch (1.27 ms). Fetching the
-// next layer's cache pages the same way made every batch size slower and is not done.
+// next layer's cache pages the same way (beside the attention kernel, or beside the products
+// after it) made every batch size slower, 1.33 ms at batch 8, and is not done.
 constexpr unsigned int PF_PIECE = 16 * 1024;
 
 struct PrefetchRanges {
