@@ -156,7 +156,7 @@ def _attention_case(dtype, hq, hkv, d, page, lens, window, seed=0, scale=None, s
     pre = [i for i, n in enumerate(qlens) if n > 1]
     pad = lambda xs: torch.tensor(xs + [0] * (b - len(xs)), dtype=torch.int32, device="cuda")
     ctx = SimpleNamespace(
-        num_seqs=b, cu_query_lens=torch.tensor(cu, dtype=torch.int32, device="cuda"),
+        num_seqs=b, query_lens=qlens, cu_query_lens=torch.tensor(cu, dtype=torch.int32, device="cuda"),
         context_lens_dev=torch.tensor([c for c, _ in lens], dtype=torch.int32, device="cuda"),
         decode_seqs=pad(dec), prefill_seqs=pad(pre), num_decode=len(dec), num_prefill=len(pre),
         max_query_len=max(qlens), max_context_len=max(c for c, _ in lens), arena=Arena("cuda"))
@@ -181,14 +181,15 @@ def test_attention_mixed_batch(dtype, hq, hkv, d, page) -> None:
     torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
 
 
-@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("kernel,heads_per_cta", [("tcgen05", 1), ("tcgen05", 2), ("mma", 0)])
 @pytest.mark.parametrize("hq,hkv,d,page", [(16, 8, 128, 16), (4, 2, 64, 8), (8, 2, 128, 32), (6, 1, 64, 48),
                                            (5, 5, 128, 8)])
 @pytest.mark.parametrize("window", [0, 150])
-def test_prefill_attention_kernels(kernel, hq, hkv, d, page, window, monkeypatch) -> None:
+def test_prefill_attention_kernels(kernel, heads_per_cta, hq, hkv, d, page, window, monkeypatch) -> None:
     """Each bf16 prefill kernel by name: whole prompts, chunks on top of a long context, lengths
     around the 64 / 128 tile edges, and short chunks."""
     monkeypatch.setattr(ops, "PREFILL_ATTENTION", kernel)
+    monkeypatch.setattr(ops, "PREFILL_HEADS_PER_CTA", heads_per_cta)
     lens = [(2, 2), (127, 127), (128, 128), (129, 129), (700, 700), (1000, 300), (515, 3), (260, 131), (64, 64),
             (1300, 1), (385, 256)]
     out, want = _attention_case(torch.bfloat16, hq, hkv, d, page, lens, window, seed=2)
@@ -197,8 +198,10 @@ def test_prefill_attention_kernels(kernel, hq, hkv, d, page, window, monkeypatch
     torch.testing.assert_close(out.float(), want.float(), **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("heads_per_cta", [1, 2])
 @pytest.mark.parametrize("pos", [0, 63, 64, 127, 128, 511, 999])
-def test_prefill_attention_tcgen05_far_key(pos) -> None:
+def test_prefill_attention_tcgen05_far_key(heads_per_cta, pos, monkeypatch) -> None:
+    monkeypatch.setattr(ops, "PREFILL_HEADS_PER_CTA", heads_per_cta)
     lens = [(1000, 200), (64, 1)]
     out, want = _attention_case(torch.bfloat16, 4, 2, 128, 16, lens, 0, spike=(0, pos), scale=1.0)
     ops.check_device_errors()

@@ -3,32 +3,41 @@
 // (upstream src/tinyserve/attention.py:89-111, src/tinyserve/triton_prefill.py:50-125):
 // S = Q K^T * scale, causal (and window) mask, softmax in 32-bit, O = P V.
 //
-// A CTA owns 128 consecutive tokens of one request for one query head. Both products run as
-// tcgen05.mma with the accumulators in tensor memory:
+// A CTA owns 128 consecutive tokens of one request for NQ query heads of one kv group (NQ = 2
+// where the group is even, else 1): the heads share the key and value tiles in shared memory, so
+// a tile is fetched once for 256 query rows. Both products run as tcgen05.mma with the
+// accumulators in tensor memory:
 //   S = Q K^T : A = Q  [128 x D]    K-major, shared memory, 128-byte swizzle
 //               B = K  [128 x D]    K-major, the cache rows as TMA delivers them
 //   O += P V  : A = P  [128 x 128]  bf16 in tensor memory, written there by the softmax warps over
 //                                   the scores they were computed from
 //               B = V  [128 x D]    read as it lies in the cache: MN-major (D contiguous)
-// Tensor memory: two score / probability buffers of 128 columns, used by alternate tiles, and O.
+// Tensor memory, NQ = 1: two score / probability buffers of 128 columns, used by alternate tiles,
+// and O; S of tile j + 1 is issued before P V of tile j, so it is computed while the softmax warps
+// work on tile j. NQ = 2: one score / probability buffer and O per head (512 columns in all); the
+// tensor core alternates between the heads (P V of head 0, S of head 0's next tile, P V of head 1,
+// S of head 1's next tile), so it works for one head while the other head's softmax runs.
 // Roles:
-//   warps 0-3 : softmax, one thread per row: reads its row of S (tcgen05.ld), masks, keeps the
+//   warps 0 .. 4 NQ - 1 : softmax, four warps per head, one thread per row: reads its row of S (tcgen05.ld), masks, keeps the
 //               running maximum and sum, writes P as bf16 over the first 64 columns of the same
 //               buffer (tcgen05.st), and scales O in tensor memory only when the maximum has
 //               grown by more than 2^8 (the sum and O then simply carry a common factor that the
 //               final division removes); at the end divides O by the sum and stores it
-//   warp 4    : TMA producer: K and V tiles of 128 positions, three stages, a box per page part
-//               and 64 columns, one lane per box
-//   warp 5    : allocates tensor memory; one lane issues every tcgen05.mma and the
+//   next warp : TMA producer: K and V tiles of 128 positions (three stages, two for NQ = 2), a
+//               box per page part and 64 columns, one lane per box
+//   last warp : allocates tensor memory; one lane issues every tcgen05.mma and the
 //               tcgen05.commit that tells the other roles what has finished; zeroes V rows
-//               outside the live key range (0 x garbage would not be 0). S of tile j + 1 is
-//               issued before P V of tile j, so it is computed while the softmax warps work on
-//               tile j; it goes to the buffer that P of tile j - 1 was read from by a product
-//               issued earlier, and the tensor core runs them in order.
+//               outside the live key range (0 x garbage would not be 0). A product that
+//               overwrites a buffer is always issued after the product that read P from it, and
+//               the tensor core runs them in order.
 // Where the time goes (B200, 16 / 8 heads of 128): a tile step (128 rows x 128 keys) costs 1,024
 // cycles of tensor core (16 instructions of 128 x 128 x 16 at the measured 64 cycles each) and
-// 1,024 cycles of the exponential unit; every operand read from shared memory and every TMA
-// write goes through the same 128 bytes per cycle, which is why P stays in tensor memory.
+// 1,024 cycles of the exponential unit, but one softmax warp per sub-core needs about 3,000 cycles
+// for it (load, maximum, exponentials, pack, store, each waiting for the one before), and with one
+// head that is the pace: 8,192 tokens run at 640 TFLOP/s. With two heads the tensor core works
+// for one while the other's softmax runs: 940 TFLOP/s. Every operand read from shared memory and
+// every TMA write goes through the same 128 bytes per cycle, which is why P stays in tensor
+// memory.
 // Every wait is on an mbarrier, is bounded and gives up at once when another role has: the CTA
 // then records the failure in *error_flag, waits for its copies in flight, frees its tensor
 // memory and returns.
@@ -45,9 +54,6 @@
 namespace ts {
 
 constexpr int FA_BM = 128, FA_BN = 128;
-constexpr int FA_KV_STAGES = 3;
-constexpr int FA_SOFTMAX_WARPS = 4;
-constexpr int FA_THREADS = (FA_SOFTMAX_WARPS + 2) * 32;
 constexpr float FA_RESCALE_STEP = 8.f;      // log2 of the growth of a row maximum that is tolerated without scaling O
 
 __device__ __forceinline__ float fa_exp2(float x) {
@@ -65,27 +71,32 @@ __device__ __forceinline__ bool fa_warp_wait(uint64_t* bar, uint32_t parity, vol
   return __all_sync(0xffffffffu, mbar_wait_or_fail(bar, parity, failed) ? 1 : 0) != 0;
 }
 
-template <int D64>
+template <int D64, int NQ>
 struct FaLayout {
   static constexpr int D = 64 * D64;
-  static constexpr uint32_t Q_BYTES = FA_BM * D * 2;
+  static constexpr int STAGES = NQ == 1 ? 3 : 2;              // K / V tiles in flight
+  static constexpr int SPB = NQ == 1 ? 2 : 1;                 // score / probability buffers per head
+  static constexpr int SOFTMAX_WARPS = 4 * NQ;
+  static constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+  static constexpr uint32_t Q_BYTES = FA_BM * D * 2;          // per head
   static constexpr uint32_t KV_BYTES = FA_BN * D * 2;         // one K or V tile
   static constexpr uint32_t OFF_Q = 0;
-  static constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
-  static constexpr uint32_t OFF_V = OFF_K + FA_KV_STAGES * KV_BYTES;
-  static constexpr uint32_t TOTAL = OFF_V + FA_KV_STAGES * KV_BYTES;
-  static constexpr uint32_t TMEM_SP = 0, TMEM_O = 2 * FA_BN;  // S/P buffer 0, S/P buffer 1, O
+  static constexpr uint32_t OFF_K = OFF_Q + NQ * Q_BYTES;
+  static constexpr uint32_t OFF_V = OFF_K + STAGES * KV_BYTES;
+  static constexpr uint32_t TOTAL = OFF_V + STAGES * KV_BYTES;
+  // tensor memory columns: the score / probability buffers of every head, then the outputs
+  static constexpr uint32_t TMEM_SP = 0, TMEM_O = NQ * SPB * FA_BN;
   static constexpr uint32_t TMEM_COLS = 512;
 };
 
-// D64 = head_dim / 64; BR = rows of a tensor box (16, or 8 for pages of 8).
-// blockIdx = (query head, tile of 128 tokens counted from the end, request in the list).
-template <int D64, int BR>
-__global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k,
-                                                                     const __grid_constant__ CUtensorMap map_v,
-                                                                     AttnArgs a, int* error_flag) {
-  using L = FaLayout<D64>;
-  constexpr int D = L::D, BN = FA_BN;
+// D64 = head_dim / 64; BR = rows of a tensor box (16, or 8 for pages of 8); NQ = heads per CTA.
+// blockIdx = (group of NQ query heads, tile of 128 tokens counted from the end, request in the list).
+template <int D64, int BR, int NQ>
+__global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                            const __grid_constant__ CUtensorMap map_v,
+                                                                            AttnArgs a, int* error_flag) {
+  using L = FaLayout<D64, NQ>;
+  constexpr int D = L::D, BN = FA_BN, FA_KV_STAGES = L::STAGES, SPB = L::SPB, FA_SOFTMAX_WARPS = L::SOFTMAX_WARPS;
   // instruction descriptors: D = f32, A = B = bf16, M = 128; S: N = BN, both operands K-major;
   // PV: N = D, B MN-major (bit 16)
   constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
@@ -93,7 +104,7 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
       (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
   extern __shared__ unsigned char fa_raw[];
   __shared__ __align__(8) uint64_t k_full[FA_KV_STAGES], k_empty[FA_KV_STAGES], v_full[FA_KV_STAGES], v_empty[FA_KV_STAGES];
-  __shared__ __align__(8) uint64_t s_full[2], p_full[2], pv_done[2], q_ready;
+  __shared__ __align__(8) uint64_t s_full[NQ][SPB], p_full[NQ][SPB], pv_done[NQ][SPB], q_ready;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed_flag;
   volatile int* failed = &failed_flag;
@@ -113,8 +124,8 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
   const int lo = a.window > 0 ? max(0, p_lo - a.window + 1) : 0;   // first key any row sees
   const int t_begin = lo / BN;
   const int n_tiles = (p_hi + 1 + BN - 1) / BN - t_begin;     // >= 1
-  const int head = (int)blockIdx.x;
-  const int kvh = head / (a.num_heads / a.num_kv_heads);
+  const int head0 = (int)blockIdx.x * NQ;
+  const int kvh = head0 / (a.num_heads / a.num_kv_heads);
 
   pdl_trigger();
   unsigned char* smem = (unsigned char*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
@@ -123,7 +134,8 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
     for (int s = 0; s < FA_KV_STAGES; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], FA_SOFTMAX_WARPS); mbar_init(&pv_done[b], 1); }
+    for (int q = 0; q < NQ; ++q)
+      for (int b = 0; b < SPB; ++b) { mbar_init(&s_full[q][b], 1); mbar_init(&p_full[q][b], 4); mbar_init(&pv_done[q][b], 1); }
     mbar_init(&q_ready, FA_SOFTMAX_WARPS);
     failed_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -137,14 +149,16 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
 
   if (warp < FA_SOFTMAX_WARPS) {
     // =========================================================== softmax warps
-    const int quad = warp;
+    const int q = warp >> 2, quad = warp & 3;                  // head of this warp, lane quarter
+    const int head = head0 + q;
     const int r = quad * 32 + lane;                            // this thread's row
-    unsigned char* q_tile = smem + L::OFF_Q;
+    unsigned char* q_tile = smem + L::OFF_Q + q * L::Q_BYTES;
     {
       // Q rows into the swizzled operand layout: 16 (or 8) threads fetch a row, 16 bytes each
       constexpr int CPR = D / 8;                               // 16-byte chunks per row
       constexpr int RPP = 128 / CPR, PASSES = FA_BM / RPP;     // rows per pass of the 128 threads
-      const int c = threadIdx.x % CPR, row0 = threadIdx.x / CPR;
+      const int tq = threadIdx.x & 127;
+      const int c = tq % CPR, row0 = tq / CPR;
       uint4 v[PASSES];
 #pragma unroll
       for (int i = 0; i < PASSES; ++i) {                       // every load in flight before the first store
@@ -163,14 +177,14 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
       if (lane == 0) mbar_arrive(&q_ready);
     }
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    const uint32_t tmem_o = tmem_base + lane_addr + L::TMEM_O;
+    const uint32_t tmem_o = tmem_base + lane_addr + L::TMEM_O + (uint32_t)(q * D);
     const int p_abs = p_lo + r;
     float m_used = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      const int b = j & 1;
-      const uint32_t tmem_sp = tmem_base + lane_addr + L::TMEM_SP + (uint32_t)(b * BN);
-      if (!fa_warp_wait(&s_full[b], (j >> 1) & 1, failed)) { ok = false; break; }
+      const int b = j % SPB, nth = j / SPB;                    // buffer, and how often it has been used
+      const uint32_t tmem_sp = tmem_base + lane_addr + L::TMEM_SP + (uint32_t)((q * SPB + b) * BN);
+      if (!fa_warp_wait(&s_full[q][b], nth & 1, failed)) { ok = false; break; }
       tc_fence_after();
       uint32_t sraw[BN];
 #pragma unroll
@@ -200,7 +214,7 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
         const bool grow = m_new > m_used + FA_RESCALE_STEP;    // also when nothing was seen before (-inf)
         if (__any_sync(0xffffffffu, grow)) {
           // O is final up to tile j - 1 before it is scaled
-          if (!fa_warp_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, failed)) { ok = false; break; }
+          if (!fa_warp_wait(&pv_done[q][(j - 1) % SPB], ((j - 1) / SPB) & 1, failed)) { ok = false; break; }
           tc_fence_after();
           const float alpha = grow ? (m_used == -INFINITY ? 0.f : fa_exp2(m_used - m_new)) : 1.f;
 #pragma unroll 1
@@ -233,11 +247,11 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[b]);
+      if (lane == 0) mbar_arrive(&p_full[q][b]);
     }
     if (ok) {
       const int last = n_tiles - 1;
-      ok = fa_warp_wait(&pv_done[last & 1], (last >> 1) & 1, failed);
+      ok = fa_warp_wait(&pv_done[q][last % SPB], (last / SPB) & 1, failed);
     }
     if (ok) {
       tc_fence_after();
@@ -311,36 +325,50 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
     bool ok = fa_warp_wait(&q_ready, 0, failed);
     const uint32_t q_addr = smem_u32(smem + L::OFF_Q);
     const uint32_t k_addr = smem_u32(smem + L::OFF_K), v_addr = smem_u32(smem + L::OFF_V);
-    // S = Q K^T of tile j into buffer j % 2, then the K stage is handed back. The buffer held P
-    // of tile j - 2, whose product was issued before and so is executed before.
-    auto issue_s = [&](int j) -> bool {
-      const int st = j % FA_KV_STAGES, b = j & 1;
-      if (!fa_warp_wait(&k_full[st], (j / FA_KV_STAGES) & 1, failed)) return false;
-      tc_fence_after();
+    // S_q = Q_q K^T of tile j into the head's buffer j % SPB
+    auto issue_s = [&](int j, int q) {
+      const int st = j % FA_KV_STAGES, bq = q * SPB + j % SPB;
       if (lane == 0) {
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint64_t ad = sw128_desc(q_addr + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32);
+          const uint64_t ad = sw128_desc(q_addr + q * L::Q_BYTES + (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32);
           const uint64_t bd = sw128_desc(k_addr + st * L::KV_BYTES + (ks >> 2) * (BN * 128) + (ks & 3) * 32);
-          umma_bf16(tmem_base + L::TMEM_SP + (uint32_t)(b * BN), ad, bd, IDESC_S, ks != 0);
+          umma_bf16(tmem_base + L::TMEM_SP + (uint32_t)(bq * BN), ad, bd, IDESC_S, ks != 0);
         }
-        umma_commit(&s_full[b]);
-        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[q][j % SPB]);
+        if (q == NQ - 1) umma_commit(&k_empty[st]);       // the K stage is free once the last head's S has read it
+      }
+      __syncwarp();
+    };
+    // O_q += P_q V of tile j, P read from the head's buffer in tensor memory
+    auto issue_pv = [&](int j, int q) -> bool {
+      const int st = j % FA_KV_STAGES, b = j % SPB;
+      if (!fa_warp_wait(&p_full[q][b], (j / SPB) & 1, failed)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          const uint64_t bd = sw128_desc_mn(v_addr + st * L::KV_BYTES + ks * (16 * 128), BN * 128);
+          umma_bf16_ta(tmem_base + L::TMEM_O + (uint32_t)(q * D),
+                       tmem_base + L::TMEM_SP + (uint32_t)((q * SPB + b) * BN + ks * 8), bd, IDESC_PV, (j | ks) != 0);
+        }
+        umma_commit(&pv_done[q][b]);
+        if (q == NQ - 1) umma_commit(&v_empty[st]);
       }
       __syncwarp();
       return true;
     };
-    if (ok) ok = issue_s(0);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (j + 1 < n_tiles) {
-        ok = issue_s(j + 1);
-        if (!ok) break;
-      }
-      const int st = j % FA_KV_STAGES, b = j & 1;
-      if (!fa_warp_wait(&v_full[st], (j / FA_KV_STAGES) & 1, failed)) { ok = false; break; }
+    auto k_ready = [&](int j) -> bool {
+      const bool got = fa_warp_wait(&k_full[j % FA_KV_STAGES], (j / FA_KV_STAGES) & 1, failed);
+      tc_fence_after();
+      return got;
+    };
+    // V of tile j is there; its rows of positions outside [lo, ctx) may hold anything: zero them (their P is 0)
+    auto v_ready = [&](int j) -> bool {
+      const int st = j % FA_KV_STAGES;
+      if (!fa_warp_wait(&v_full[st], (j / FA_KV_STAGES) & 1, failed)) return false;
       const int k0 = (t_begin + j) * BN;
       if (k0 < lo || k0 + BN > ctx) {
-        // value rows of positions outside [lo, ctx) may hold anything: zero them (their P is 0)
         unsigned char* v_tile = smem + L::OFF_V + st * L::KV_BYTES;
         for (int idx = lane; idx < BN * D64 * 8; idx += 32) {
           const int row = idx / (D64 * 8), c = idx - row * (D64 * 8);
@@ -351,18 +379,32 @@ __global__ void __launch_bounds__(FA_THREADS) prefill_attn_tc_kernel(const __gri
         fence_proxy_async_smem();
         __syncwarp();
       }
-      if (!fa_warp_wait(&p_full[b], (j >> 1) & 1, failed)) { ok = false; break; }
-      tc_fence_after();
-      if (lane == 0) {
-#pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          const uint64_t bd = sw128_desc_mn(v_addr + st * L::KV_BYTES + ks * (16 * 128), BN * 128);
-          umma_bf16_ta(tmem_base + L::TMEM_O, tmem_base + L::TMEM_SP + (uint32_t)(b * BN + ks * 8), bd, IDESC_PV, (j | ks) != 0);
+      return true;
+    };
+    if (ok) ok = k_ready(0);
+    if (ok) {
+      for (int q = 0; q < NQ; ++q) issue_s(0, q);
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const bool more = j + 1 < n_tiles;
+      if constexpr (NQ == 1) {
+        // two buffers: the next tile's scores are computed while the softmax warps work on this one
+        if (more) {
+          ok = k_ready(j + 1);
+          if (!ok) break;
+          issue_s(j + 1, 0);
         }
-        umma_commit(&pv_done[b]);
-        umma_commit(&v_empty[st]);
+        ok = v_ready(j) && issue_pv(j, 0);
+      } else {
+        // one buffer per head: a head's next scores follow the product that read its P; meanwhile
+        // the other head's softmax runs
+        ok = v_ready(j);
+        if (ok && more) ok = k_ready(j + 1);
+        for (int q = 0; q < NQ && ok; ++q) {
+          ok = issue_pv(j, q);
+          if (ok && more) issue_s(j + 1, q);
+        }
       }
-      __syncwarp();
     }
   }
   if (*failed && (threadIdx.x & 31) == 0) atomicExch(error_flag, 1);
@@ -406,18 +448,18 @@ static const CUtensorMap* fa_cache_map(const void* base, long long rows, int hea
   return &maps.emplace(key, m).first->second;
 }
 
-template <int D64, int BR>
+template <int D64, int BR, int NQ>
 static int launch_fa(const AttnArgs& a, long long cache_rows, int max_query_len, int* error_flag, cudaStream_t stream) {
-  using L = FaLayout<D64>;
+  using L = FaLayout<D64, NQ>;
   const CUtensorMap* mk = fa_cache_map(a.k_cache, cache_rows, L::D, BR);
   const CUtensorMap* mv = fa_cache_map(a.v_cache, cache_rows, L::D, BR);
   if (mk == nullptr || mv == nullptr) return TS_ERR_UNSUPPORTED;
   const size_t smem = (size_t)L::TOTAL + 1024;
-  auto kern = prefill_attn_tc_kernel<D64, BR>;
+  auto kern = prefill_attn_tc_kernel<D64, BR, NQ>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid(a.num_heads, (max_query_len + FA_BM - 1) / FA_BM, a.num_seqs);
-  return launch(kern, grid, FA_THREADS, smem, stream, *mk, *mv, a, error_flag);
+  dim3 grid(a.num_heads / NQ, (max_query_len + FA_BM - 1) / FA_BM, a.num_seqs);
+  return launch(kern, grid, L::THREADS, smem, stream, *mk, *mv, a, error_flag);
 }
 
 }  // namespace ts
@@ -426,12 +468,14 @@ using namespace ts;
 
 // bf16 prefill attention on tcgen05 for the requests listed in prefill_seqs. head_dim 64 or 128;
 // page_size 8 or a multiple of 16; num_pages_total = pages of the cache tensors (the pad page
-// included). Returns TS_ERR_UNSUPPORTED for sizes it does not take.
+// included). heads_per_cta: 1, or 2 query heads of a kv group sharing a CTA's key and value tiles
+// (needs an even group); 0 picks 2 where it can. Returns TS_ERR_UNSUPPORTED for sizes it does
+// not take.
 extern "C" int ts_prefill_attention_tcgen05(
     const void* q, void* out, const void* k_cache, const void* v_cache, long long num_pages_total,
     const int* block_tables, int table_width, const int* cu_q, const int* ctx_lens, const int* prefill_seqs,
     int num_prefill, int max_query_len, int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
-    int window, int* error_flag, cudaStream_t stream) {
+    int window, int heads_per_cta, int* error_flag, cudaStream_t stream) {
   if (num_prefill <= 0 || max_query_len <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
   if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
@@ -439,6 +483,10 @@ extern "C" int ts_prefill_attention_tcgen05(
   if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache) | ((uintptr_t)q) | ((uintptr_t)out)) & 15) return TS_ERR_UNSUPPORTED;
   const long long rows = num_pages_total * num_kv_heads * page_size;
   if (rows >= (1ll << 31)) return TS_ERR_UNSUPPORTED;
+  const int group = num_heads / num_kv_heads;
+  if (heads_per_cta == 0) heads_per_cta = (group % 2 == 0) ? 2 : 1;
+  if (heads_per_cta != 1 && heads_per_cta != 2) return TS_ERR_BAD_ARGUMENT;
+  if (heads_per_cta == 2 && group % 2 != 0) return TS_ERR_UNSUPPORTED;
   AttnArgs a;
   a.q = q; a.out = out; a.k_cache = k_cache; a.v_cache = v_cache;
   a.block_tables = block_tables; a.table_width = table_width; a.cu_q = cu_q; a.ctx_lens = ctx_lens;
@@ -448,9 +496,14 @@ extern "C" int ts_prefill_attention_tcgen05(
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.num_splits = 1; a.part_acc = nullptr; a.part_ml = nullptr;
-  if (head_dim == 64)
-    return page_size == 8 ? launch_fa<1, 8>(a, rows, max_query_len, error_flag, stream)
-                          : launch_fa<1, 16>(a, rows, max_query_len, error_flag, stream);
-  return page_size == 8 ? launch_fa<2, 8>(a, rows, max_query_len, error_flag, stream)
-                        : launch_fa<2, 16>(a, rows, max_query_len, error_flag, stream);
+#define TS_FA(D64_, BR_)                                                                                \
+  return heads_per_cta == 2 ? launch_fa<D64_, BR_, 2>(a, rows, max_query_len, error_flag, stream)       \
+                            : launch_fa<D64_, BR_, 1>(a, rows, max_query_len, error_flag, stream)
+  if (head_dim == 64) {
+    if (page_size == 8) { TS_FA(1, 8); }
+    TS_FA(1, 16);
+  }
+  if (page_size == 8) { TS_FA(2, 8); }
+  TS_FA(2, 16);
+#undef TS_FA
 }

@@ -46,7 +46,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_prefill_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
                                  _i, _vp, _vp],
     "ts_prefill_attention_tcgen05": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                     _f, _i, _vp, _vp],
+                                     _f, _i, _i, _vp, _vp],
     "ts_gemm_skinny_normed": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_to_stream": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_prefetch_l2": [_vp, _vp, _i, _vp],
@@ -236,11 +236,26 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: torch.T
 
 # -------------------------------------------------------------------- attention
 # The bf16 prefill kernel for head sizes 64 / 128: "tcgen05" (tensor memory accumulators) or "mma"
-# (mma.sync with TMA tiles).
+# (mma.sync with TMA tiles); and how many query heads of a kv group share a CTA of the former and
+# its key / value tiles (0: chosen by the size of the grid, see ``_prefill_heads_per_cta``).
 PREFILL_ATTENTION = "tcgen05"
+PREFILL_HEADS_PER_CTA = 0
 TARGET_DECODE_CTAS = 148 * 4
 MIN_KEYS_PER_SPLIT = 64
 MAX_SPLITS = 32
+
+
+def _prefill_heads_per_cta(ctx: Any, num_heads: int, num_kv_heads: int) -> int:
+    """Two query heads of a kv group in a CTA share its key and value tiles, which is worth more
+    than anything once the pairs alone give every SM a CTA (measured on B200, 16 / 8 heads of 128:
+    2,048 tokens 39 us with one head, 46 us with two; 3,072 tokens 79 / 64 us; 8,192 tokens
+    428 / 292 us)."""
+    if (num_heads // num_kv_heads) % 2:
+        return 1
+    if PREFILL_HEADS_PER_CTA:
+        return PREFILL_HEADS_PER_CTA
+    tiles = sum(-(-n // 128) for n in ctx.query_lens if n > 1)
+    return 2 if tiles * (num_heads // 2) > 148 else 1
 
 
 def decode_splits(num_decode: int, num_kv_heads: int, group: int, max_context_len: int) -> int:
@@ -299,6 +314,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                 _dev(ctx.context_lens_dev, "context_lens", torch.int32),
                 _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
                 hq, hkv, d, page_size, float(scale), int(window),
+                _prefill_heads_per_cta(ctx, hq, hkv),
                 _error_word(q.device).data_ptr(), _stream()), "prefill_attention_tcgen05")
         elif tma_ok:
             _check(_fn("ts_prefill_attention_tma")(
