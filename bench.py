@@ -124,8 +124,9 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--fused-decode-rows", type=int, default=None,
                     help="largest decode batch that takes the fused norm+rotation+attention kernel (0: never)")
-    ap.add_argument("--fused-norms", action="store_true",
-                    help="decode steps fold every RMSNorm into the products around it (default: kernels of their own)")
+    ap.add_argument("--separate-norms", action="store_true",
+                    help="decode steps run every RMSNorm as a kernel of its own (default: folded into the products "
+                         "around it for up to 8 rows)")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="run a small case kernel by kernel between cudaProfilerStart/Stop and exit "
                          "(for ncu --profile-from-start off); combine with --layers, --batch")
@@ -148,8 +149,8 @@ def main() -> int:
     from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
-    if args.fused_norms:
-        ops.FUSE_STREAM_NORM = True
+    if args.separate_norms:
+        ops.FUSE_STREAM_NORM = False
     if args.fused_decode_rows is not None:
         ops.FUSED_DECODE_MAX_ROWS = args.fused_decode_rows
     fixed_pdl = args.no_pdl or args.pdl is not None

@@ -39,19 +39,21 @@ def real(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype,variant", [(torch.float32, "default"), (torch.bfloat16, "default"),
-                                           (torch.bfloat16, "fuse_every_decode"), (torch.bfloat16, "fused_norms")])
+                                           (torch.bfloat16, "fuse_every_decode"), (torch.bfloat16, "separate_norms")])
 def test_real_layer_sizes_under_every_cut(real, dtype, variant, monkeypatch) -> None:
     """``fuse_every_decode``: steps of decode tokens alone take the fused norm + rotation +
     cache write + attention kernel whatever their grid (the engine picks it only for grids that
-    gain from it, which these short requests never make). ``fused_norms``: the RMSNorms of decode
-    steps run inside the products around them instead of as kernels of their own."""
+    gain from it, which these short requests never make). ``separate_norms``: the RMSNorms of
+    decode steps run as kernels of their own instead of inside the products around them (the
+    default for a few bf16 rows)."""
     fuse_every_decode = variant == "fuse_every_decode"
     from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
     fused_norm_calls = []
-    if variant == "fused_norms":
-        monkeypatch.setattr(ops, "FUSE_STREAM_NORM", True)
+    if variant == "separate_norms":
+        monkeypatch.setattr(ops, "FUSE_STREAM_NORM", False)
+    else:
         normed = ops.gemm_normed
         monkeypatch.setattr(ops, "gemm_normed", lambda *a, **k: (fused_norm_calls.append(1), normed(*a, **k))[1])
     if fuse_every_decode:
@@ -70,4 +72,4 @@ def test_real_layer_sizes_under_every_cut(real, dtype, variant, monkeypatch) -> 
     if fuse_every_decode:
         assert calls, "no step took the fused kernel"
     if dtype == torch.bfloat16:
-        assert bool(fused_norm_calls) == (variant == "fused_norms")
+        assert bool(fused_norm_calls) == (variant != "separate_norms")
