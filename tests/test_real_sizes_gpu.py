@@ -39,14 +39,12 @@ def real(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype,variant", [(torch.float32, "default"), (torch.bfloat16, "default"),
-                                           (torch.bfloat16, "fuse_every_decode"), (torch.bfloat16, "separate_norms")])
+                                           (torch.bfloat16, "separate_rope"), (torch.bfloat16, "separate_norms")])
 def test_real_layer_sizes_under_every_cut(real, dtype, variant, monkeypatch) -> None:
-    """``fuse_every_decode``: steps of decode tokens alone take the fused norm + rotation +
-    cache write + attention kernel whatever their grid (the engine picks it only for grids that
-    gain from it, which these short requests never make). ``separate_norms``: the RMSNorms of
-    decode steps run as kernels of their own instead of inside the products around them (the
-    default for a few bf16 rows)."""
-    fuse_every_decode = variant == "fuse_every_decode"
+    """By default steps of decode tokens alone take the fused q/k-norm + rotation + cache write +
+    attention kernel and, for a few bf16 rows, fold the RMSNorms into the products around them.
+    ``separate_rope``: the q/k-norm, rotation and cache write run as a kernel of their own before
+    the attention kernel. ``separate_norms``: the RMSNorms run as kernels of their own."""
     from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
@@ -56,11 +54,11 @@ def test_real_layer_sizes_under_every_cut(real, dtype, variant, monkeypatch) -> 
     else:
         normed = ops.gemm_normed
         monkeypatch.setattr(ops, "gemm_normed", lambda *a, **k: (fused_norm_calls.append(1), normed(*a, **k))[1])
-    if fuse_every_decode:
-        monkeypatch.setattr(ops, "FUSED_DECODE_MIN_CTAS", 0)
-        calls = []
-        fused = ops.decode_attention_fused
-        monkeypatch.setattr(ops, "decode_attention_fused", lambda *a, **k: (calls.append(1), fused(*a, **k))[1])
+    calls = []
+    fused = ops.decode_attention_fused
+    monkeypatch.setattr(ops, "decode_attention_fused", lambda *a, **k: (calls.append(1), fused(*a, **k))[1])
+    if variant == "separate_rope":
+        monkeypatch.setattr(ops, "FUSED_DECODE_MAX_ROWS", 0)
     folder, reqs, want = real
     model = DecoderModel.from_folder(folder, dtype, "cuda")
     plans = [cases.mixed(reqs, 5)]
@@ -69,7 +67,7 @@ def test_real_layer_sizes_under_every_cut(real, dtype, variant, monkeypatch) -> 
     for steps in plans:
         got = run_steps(model, 16, steps, cases.max_live_tokens(steps))
         check(got, want, {r: reqs[r] for r in got}, dtype)
-    if fuse_every_decode:
-        assert calls, "no step took the fused kernel"
+    if dtype == torch.bfloat16:
+        assert bool(calls) == (variant != "separate_rope")
     if dtype == torch.bfloat16:
         assert bool(fused_norm_calls) == (variant != "separate_norms")

@@ -420,9 +420,9 @@ class ModelRunner:
         if not all(layer.block.mixer.graph_safe for layer in self.model.parts.layers):
             raise RuntimeError("a mixer of this model reads the step on the host; its decode step cannot be recorded")
         self.graph_max_context = max_context
-        if self.tune_launch_overlap:
-            ops.use_pdl_mask(ops.DEFAULT_PDL_MASK)
         for rows in sorted(set(buckets or default_buckets(max_batch))):
+            if self.tune_launch_overlap:
+                ops.use_pdl_mask(ops.decode_pdl_mask(rows))
             g = DecodeGraph(self, rows, max_context)
             g.record(self)
             self.graphs[rows] = g
@@ -499,7 +499,7 @@ class ModelRunner:
             return None if want is not None and not list(want[0]) else pgraph.logits
         ctx, rows, r = self.build_context(entries, want)
         if self.tune_launch_overlap and self.device.type == "cuda":
-            ops.use_pdl_mask(ops.PREFILL_PDL_MASK if ctx.num_prefill else ops.DEFAULT_PDL_MASK)
+            ops.use_pdl_mask(ops.PREFILL_PDL_MASK if ctx.num_prefill else ops.decode_pdl_mask(ctx.num_tokens))
         with ops.stream_scope():
             logits = self.model.forward(ctx, self.cache.entries, rows, r)
         self.num_steps += 1

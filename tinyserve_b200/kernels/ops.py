@@ -59,11 +59,20 @@ _SIGNATURES: dict[str, list[Any]] = {
 }
 _fns: dict[str, Any] = {}
 
-# Kernel classes launched with programmatic dependent launch by default: the skinny product
-# (its weight prefetch runs while the predecessor drains) and the attention kernels. Measured on
-# B200 in the recorded decode step of Qwen3-0.6B at batch 8: 1.195 ms with this mask, 1.263 ms
-# with none, 1.330 ms with all classes (the small elementwise kernels lose from starting early).
+# Kernel classes launched with programmatic dependent launch in decode steps. Up to 16 rows: all
+# classes (the L2 prefetch kernel then starts beside the product before it, and nothing small is
+# left that loses from starting early); beyond: the skinny product and the attention kernels.
+# Measured on B200 in the recorded decode step of Qwen3-0.6B, all classes against those two:
+# batch 8 1.046 / 1.112 ms, 16 1.736 / 1.776 ms, 32 1.839 / 1.796 ms, 64 2.719 / 2.690 ms.
 DEFAULT_PDL_MASK = 2 | 4
+SMALL_DECODE_PDL_MASK = -1
+SMALL_DECODE_ROWS = 16
+
+
+def decode_pdl_mask(rows: int) -> int:
+    return SMALL_DECODE_PDL_MASK if rows <= SMALL_DECODE_ROWS else DEFAULT_PDL_MASK
+
+
 # Steps that carry prompt portions run large kernels, where starting early costs nothing and
 # hides the launch: all classes (2,048-token prefill of Qwen3-0.6B: 7.7 ms against 8.1 ms).
 PREFILL_PDL_MASK = -1
@@ -382,12 +391,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 # The fused decode kernel takes steps of up to this many decode tokens (0 turns it off), and
-# only grids of at least this many CTAs that fit the machine at once. Measured on B200 (Qwen3-0.6B
-# sizes, 1,024-token contexts): batches 4 to 48 gain 1 to 5 % of the step; smaller grids (batch 1,
-# 2) are bound by the latency of a single CTA, which the extra work at its start lengthens, and
-# larger ones (batch 56, 64) repeat that work in a second round of CTAs; both lose 1 to 4 %.
+# only grids that fit the machine at once (and have at least FUSED_DECODE_MIN_CTAS CTAs). Measured
+# on B200 (Qwen3-0.6B sizes, 1,024-token contexts): batches 1 to 48 gain 1 to 5 % of the step;
+# larger ones (batch 56, 64) repeat the extra work in a second round of CTAs and lose 1 to 4 %.
 FUSED_DECODE_MAX_ROWS = 1 << 30
-FUSED_DECODE_MIN_CTAS = 256
+FUSED_DECODE_MIN_CTAS = 0
 
 
 def can_fuse_decode(ctx: Any, dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
