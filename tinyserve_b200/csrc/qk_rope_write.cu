@@ -197,17 +197,35 @@ __global__ void qk_norm_rope_write_fast_kernel(
   }
 }
 
-// The same for many tokens (prefill), bf16, head_dim 64, 128 or 256: D / 8 lanes share a head,
-// each with 4 consecutive elements of the first half and their 4 partners of the second (two
-// 8-byte accesses), so a warp works on 32 / (D / 8) heads at once and half as many instructions
-// move the same bytes as in the kernel above.
+// The same for many tokens (prefill), bf16, head_dim 64, 128 or 256: D / 16 lanes share a head,
+// each with 8 consecutive elements of the first half and their 8 partners of the second (two
+// 16-byte accesses), so a warp works on 32 / (D / 16) heads at once and a quarter as many
+// instructions move the same bytes as in the kernel above.
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 template <int D>
 __global__ void qk_norm_rope_write_wide_kernel(
     const bf16* __restrict__ qkv, bf16* __restrict__ q_out, const bf16* __restrict__ q_weight,
     const bf16* __restrict__ k_weight, float eps, const float* __restrict__ cos_t,
     const float* __restrict__ sin_t, const int* __restrict__ slots, bf16* __restrict__ k_cache,
     bf16* __restrict__ v_cache, int page_size, int num_tokens, int num_heads, int num_kv_heads, int write_kv) {
-  constexpr int LPH = D / 8, HPW = 32 / LPH, HALF = D / 2;
+  constexpr int LPH = D / 16, HPW = 32 / LPH, HALF = D / 2;
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -217,7 +235,7 @@ __global__ void qk_norm_rope_write_wide_kernel(
   const bool live = item < (long long)num_tokens * heads_per_token;
   const int t = live ? (int)(item / heads_per_token) : 0;
   const int h = live ? (int)(item - (long long)t * heads_per_token) : 0;
-  const bf16* src = qkv + ((size_t)t * heads_per_token + h) * D + 4 * l;
+  const bf16* src = qkv + ((size_t)t * heads_per_token + h) * D + 8 * l;
   bf16* dst;
   const bf16* weight = nullptr;
   bool is_v = false;
@@ -233,62 +251,57 @@ __global__ void qk_norm_rope_write_wide_kernel(
     is_v = !is_k;
     weight = k_weight;
   }
-  dst += 4 * l;
-  uint2 ua = make_uint2(0u, 0u), ub = make_uint2(0u, 0u);
+  dst += 8 * l;
+  uint4 ua = make_uint4(0u, 0u, 0u, 0u), ub = ua;
   if (live) {
-    ua = *reinterpret_cast<const uint2*>(src);
-    ub = *reinterpret_cast<const uint2*>(src + HALF);
+    ua = *reinterpret_cast<const uint4*>(src);
+    ub = *reinterpret_cast<const uint4*>(src + HALF);
   }
-  if (is_v) {
-    if (live) {
-      *reinterpret_cast<uint2*>(dst) = ua;
-      *reinterpret_cast<uint2*>(dst + HALF) = ub;
-    }
+  if (is_v && live) {
+    *reinterpret_cast<uint4*>(dst) = ua;
+    *reinterpret_cast<uint4*>(dst + HALF) = ub;
   }
-  float a[4] = {__uint_as_float(ua.x << 16), __uint_as_float(ua.x & 0xffff0000u), __uint_as_float(ua.y << 16),
-                __uint_as_float(ua.y & 0xffff0000u)};
-  float b[4] = {__uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u), __uint_as_float(ub.y << 16),
-                __uint_as_float(ub.y & 0xffff0000u)};
+  float a[8], b[8];
+  unpack8(ua, a);
+  unpack8(ub, b);
   float ss = 0.f;
 #pragma unroll
-  for (int e = 0; e < 4; ++e) ss += a[e] * a[e] + b[e] * b[e];
+  for (int e = 0; e < 8; ++e) ss += a[e] * a[e] + b[e] * b[e];
 #pragma unroll
   for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // within the head's lanes
   if (!live || is_v) return;
   if (weight != nullptr) {
     const float rstd = rsqrtf(ss / (float)D + eps);
-    const uint2 wa = *reinterpret_cast<const uint2*>(weight + 4 * l);
-    const uint2 wb = *reinterpret_cast<const uint2*>(weight + HALF + 4 * l);
-    const float fa[4] = {__uint_as_float(wa.x << 16), __uint_as_float(wa.x & 0xffff0000u), __uint_as_float(wa.y << 16),
-                         __uint_as_float(wa.y & 0xffff0000u)};
-    const float fb[4] = {__uint_as_float(wb.x << 16), __uint_as_float(wb.x & 0xffff0000u), __uint_as_float(wb.y << 16),
-                         __uint_as_float(wb.y & 0xffff0000u)};
+    float fa[8], fb[8];
+    unpack8(*reinterpret_cast<const uint4*>(weight + 8 * l), fa);
+    unpack8(*reinterpret_cast<const uint4*>(weight + HALF + 8 * l), fb);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int e = 0; e < 8; ++e) {
       a[e] = round_to<bf16>(round_to<bf16>(a[e] * rstd) * fa[e]);
       b[e] = round_to<bf16>(round_to<bf16>(b[e] * rstd) * fb[e]);
     }
   }
-  const float4 cv = *reinterpret_cast<const float4*>(cos_t + (size_t)t * HALF + 4 * l);
-  const float4 sv = *reinterpret_cast<const float4*>(sin_t + (size_t)t * HALF + 4 * l);
-  const float c[4] = {cv.x, cv.y, cv.z, cv.w}, sn[4] = {sv.x, sv.y, sv.z, sv.w};
-  float ra[4], rb[4];
+  const float* cp = cos_t + (size_t)t * HALF + 8 * l;
+  const float* sp = sin_t + (size_t)t * HALF + 8 * l;
+  const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  float ra[8], rb[8];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
+  for (int e = 0; e < 8; ++e) {
     ra[e] = a[e] * c[e] - b[e] * sn[e];
     rb[e] = b[e] * c[e] + a[e] * sn[e];
   }
-  __nv_bfloat162 p0 = __floats2bfloat162_rn(ra[0], ra[1]), p1 = __floats2bfloat162_rn(ra[2], ra[3]);
-  __nv_bfloat162 q0 = __floats2bfloat162_rn(rb[0], rb[1]), q1 = __floats2bfloat162_rn(rb[2], rb[3]);
-  *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1));
-  *reinterpret_cast<uint2*>(dst + HALF) = make_uint2(*reinterpret_cast<uint32_t*>(&q0), *reinterpret_cast<uint32_t*>(&q1));
+  *reinterpret_cast<uint4*>(dst) = pack8(ra);
+  *reinterpret_cast<uint4*>(dst + HALF) = pack8(rb);
 }
 
 template <int D>
 static int launch_wide(const void* qkv, void* q_out, const void* q_weight, const void* k_weight, float eps,
                        const float* cos_t, const float* sin_t, const int* slots, void* k_cache, void* v_cache,
                        int page_size, int num_tokens, int num_heads, int num_kv_heads, int write_kv, cudaStream_t stream) {
-  constexpr int HPW = 32 / (D / 8);
+  constexpr int HPW = 32 / (D / 16);
   const int heads_per_token = write_kv ? num_heads + 2 * num_kv_heads : num_heads;
   const long long items = (long long)num_tokens * heads_per_token;
   const long long per_block = (long long)QK_WARPS * HPW;
