@@ -191,7 +191,7 @@ def test_prefill_attention_kernels(kernel, heads_per_cta, hq, hkv, d, page, wind
     monkeypatch.setattr(ops, "PREFILL_ATTENTION", kernel)
     monkeypatch.setattr(ops, "PREFILL_HEADS_PER_CTA", heads_per_cta)
     lens = [(2, 2), (127, 127), (128, 128), (129, 129), (700, 700), (1000, 300), (515, 3), (260, 131), (64, 64),
-            (1300, 1), (385, 256)]
+            (1300, 1), (385, 256), (2500, 1400), (3000, 129)]
     out, want = _attention_case(torch.bfloat16, hq, hkv, d, page, lens, window, seed=2)
     ops.check_device_errors()
     assert not out.isnan().any()
