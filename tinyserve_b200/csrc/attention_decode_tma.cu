@@ -211,7 +211,11 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
-  pdl_wait();
+  // Nothing that the kernels just before this one write is read until the first tiles are on
+  // their way: lengths and block tables are the step's host-made inputs, and the cache rows of
+  // earlier positions were written in earlier steps. Only the tile with the newest position
+  // (written by the kernel before, or, in the fused form, taken from shared memory) and the
+  // queries wait for the predecessor.
 
   const int seq = a.seq_ids[si];
   const int ctx = a.ctx_lens[seq];
@@ -261,7 +265,14 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
   const int first = tile_begin + warp;
   for (int s = 0; s < DM_STAGES; ++s) {
     const int tile = first + s * DM_WARPS;
-    if (tile < tile_end) load_tile(tile, s);
+    if (tile < tile_end && (FUSED || tile < ntiles_all - 1)) load_tile(tile, s);
+  }
+  pdl_wait();
+  if constexpr (!FUSED) {
+    for (int s = 0; s < DM_STAGES; ++s) {
+      const int tile = first + s * DM_WARPS;
+      if (tile < tile_end && tile == ntiles_all - 1) load_tile(tile, s);
+    }
   }
 
   // (the first tiles are on their way; the work on the queries overlaps their flight)
