@@ -74,28 +74,45 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  pdl_wait();      // barriers and tensor memory are set up; x may now be read, out written
 
   if (warp == 0) {
     // ---------------- TMA producer (one lane)
     if (lane == 0) {
+      // The weights do not depend on the kernel before this one: the B tiles of the first stages
+      // are requested before the wait for it, the A tiles (its output) after.
+      auto load_b = [&](int s, int kb, int n0) {
+        unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
+        if constexpr (SWIGLU) {
+          // the map's box is 128 rows: gate rows n0.., then up rows N + n0.. of the merged matrix
+          tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
+          tma_load_2d(a + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], kb * TG_BK, N + n0);
+        } else {
+          tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
+        }
+      };
+      int early = 0;
+      if ((int)blockIdx.x < num_tiles) {
+        const int n0 = ((int)blockIdx.x / tiles_m) * BN_OUT;
+        early = num_kb < STAGES ? num_kb : STAGES;
+        for (int kb = 0; kb < early; ++kb) {          // fresh barriers: nothing to wait for
+          mbar_expect_tx(&full_bar[kb], STAGE_BYTES);
+          load_b(kb, kb, n0);
+        }
+      }
+      pdl_wait();
       int it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !failed; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN_OUT;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], phase ^ 1)) { failed = 1; break; }
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
           unsigned char* a = tiles + (size_t)s * STAGE_BYTES;
-          tma_load_2d(a, &map_x, &full_bar[s], kb * TG_BK, m0);
-          if constexpr (SWIGLU) {
-            // the map's box is 128 rows: gate rows n0.., then up rows N + n0.. of the merged matrix
-            tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
-            tma_load_2d(a + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], kb * TG_BK, N + n0);
-          } else {
-            tma_load_2d(a + A_BYTES, &map_w, &full_bar[s], kb * TG_BK, n0);
+          if (it >= early) {
+            if (!mbar_wait(&empty_bar[s], phase ^ 1)) { failed = 1; break; }
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            load_b(s, kb, n0);
           }
+          tma_load_2d(a, &map_x, &full_bar[s], kb * TG_BK, m0);
         }
       }
     }
@@ -128,6 +145,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
     }
   } else {
     // ---------------- epilogue: warps 2..5; warp w may touch TMEM lanes 32 (w % 4) .. + 31
+    pdl_wait();      // out may be written only once the kernel before this one is done
     const int quad = warp & 3;
     int t = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
