@@ -223,6 +223,19 @@ def test_attention_decode_only_many_splits(dtype) -> None:
     torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("window", [0, 50])
+@pytest.mark.parametrize("batch", [56, 60, 74])
+def test_attention_decode_grid_just_over_three_ctas_per_sm(batch, window) -> None:
+    """Unsplit grids of 448 to 592 CTAs (batch x 8 kv heads) run as CTAs of three warps, four to an
+    SM; every context length from one key to several tiles per warp, one far key dominating."""
+    lens = [(1 + (i * 37) % 300, 1) for i in range(batch - 1)] + [(900, 1)]
+    out, want = _attention_case(torch.bfloat16, 16, 8, 128, 16, lens, window, seed=5,
+                                spike=(batch - 1, 3 if window == 0 else 870))
+    ops.check_device_errors()
+    assert not out.isnan().any()
+    torch.testing.assert_close(out.float(), want.float(), **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("new", [1, 5])
 @pytest.mark.parametrize("pos", [0, 15, 16, 511, 700])

@@ -183,15 +183,16 @@ __device__ __forceinline__ void fused_head_row(const bf16* src, const bf16* weig
 // D64 = head_dim / 64 (1 or 2). BR = rows of a tensor box: 16 (page size a multiple of 16) or 8.
 // blockIdx = (request in the list, kv head * passes + pass, key range); a pass covers up to 16
 // query heads of the group.
-template <int D64, int BR, bool FUSED>
-__global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+// WARPS: warps per CTA (4; 3 where one more CTA per SM lets a grid run as a single wave).
+template <int D64, int BR, bool FUSED, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                      const __grid_constant__ CUtensorMap map_v,
                                                                      AttnArgs a, FusedQkv f, int passes,
                                                                      int* error_flag) {
   constexpr int D = D64 * 64, D16 = D / 16;
   constexpr int TILE_BYTES = DM_TK * D * 2;                 // one K (or V) tile: 16 rows, unpadded
   extern __shared__ __align__(16) unsigned char dm_raw[];
-  __shared__ __align__(8) uint64_t bars[DM_WARPS][DM_STAGES];
+  __shared__ __align__(8) uint64_t bars[WARPS][DM_STAGES];
   __shared__ int is_last;
   __shared__ __align__(16) bf16 q_stage[FUSED ? 16 * 128 : 8];     // this CTA's query heads, ready for the mma
   __shared__ __align__(16) bf16 new_kv[FUSED ? 2 * 128 : 8];       // the new token's key and value rows
@@ -261,16 +262,16 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   bool failed = false;
 
-  // this warp's tiles: tile_begin + warp, + DM_WARPS, ...
+  // this warp's tiles: tile_begin + warp, + WARPS, ...
   const int first = tile_begin + warp;
   for (int s = 0; s < DM_STAGES; ++s) {
-    const int tile = first + s * DM_WARPS;
+    const int tile = first + s * WARPS;
     if (tile < tile_end && (FUSED || tile < ntiles_all - 1)) load_tile(tile, s);
   }
   pdl_wait();
   if constexpr (!FUSED) {
     for (int s = 0; s < DM_STAGES; ++s) {
-      const int tile = first + s * DM_WARPS;
+      const int tile = first + s * WARPS;
       if (tile < tile_end && tile == ntiles_all - 1) load_tile(tile, s);
     }
   }
@@ -282,7 +283,7 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
     const bf16* row = f.qkv + (size_t)qrow * width;
     const float* c = f.cos_t ? f.cos_t + (size_t)qrow * (D / 2) : nullptr;
     const float* sn = f.sin_t ? f.sin_t + (size_t)qrow * (D / 2) : nullptr;
-    for (int r = warp; r < 16; r += DM_WARPS) {
+    for (int r = warp; r < 16; r += WARPS) {
       if (r < ng) {
         fused_head_row<D>(row + (size_t)(kvh * G + g0 + r) * D, f.q_weight, f.eps, c, sn, q_stage + r * D, nullptr, lane);
       } else {
@@ -296,10 +297,10 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
       const int page = slot / a.page_size, off = slot - page * a.page_size;
       const size_t at = kv_offset(page, kvh, off, a);
       const bool writer = (g0 == 0);
-      if (warp == (ng % DM_WARPS)) {
+      if (warp == (ng % WARPS)) {
         fused_head_row<D>(row + (size_t)(a.num_heads + kvh) * D, f.k_weight, f.eps, c, sn, new_kv,
                           writer ? f.k_cache + at : nullptr, lane);
-      } else if (warp == ((ng + 1) % DM_WARPS)) {
+      } else if (warp == ((ng + 1) % WARPS)) {
         const bf16* vsrc = row + (size_t)(a.num_heads + a.num_kv_heads + kvh) * D;
         for (int i = lane * 8; i < D; i += 256) {
           const uint4 v = *reinterpret_cast<const uint4*>(vsrc + i);
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
   }
 
   int n = 0;
-  for (int tile = first; tile < tile_end; tile += DM_WARPS, ++n) {
+  for (int tile = first; tile < tile_end; tile += WARPS, ++n) {
     const int stage = n % DM_STAGES;
     const uint32_t parity = (n / DM_STAGES) & 1;
     if (!dm_bar_wait(&bars[warp][stage], parity)) { failed = true; break; }
@@ -435,7 +436,7 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
     // order this warp's accesses to the stage (reads, and the zeroing above) before the copy
     // engine's next write into it
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    const int nxt = tile + DM_STAGES * DM_WARPS;
+    const int nxt = tile + DM_STAGES * WARPS;
     if (nxt < tile_end) load_tile(nxt, stage);
   }
   if (failed && lane == 0) atomicExch(error_flag, 1);
@@ -447,7 +448,7 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
   }
   __syncthreads();                                 // all warps are done with their tiles
-  float* red = reinterpret_cast<float*>(tiles);    // [DM_WARPS][16][D + 2], reusing the tile memory
+  float* red = reinterpret_cast<float*>(tiles);    // [WARPS][16][D + 2], reusing the tile memory
   constexpr int WS = D + 2;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -463,14 +464,14 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_tma_kernel(const __gri
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < ng * D; idx += DM_THREADS) {
+  for (int idx = threadIdx.x; idx < ng * D; idx += (WARPS * 32)) {
     const int r = idx / D, d = idx - r * D;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DM_WARPS; ++w) mm = fmaxf(mm, red[((size_t)w * 16 + r) * WS + D]);
+    for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, red[((size_t)w * 16 + r) * WS + D]);
     float num = 0.f, den = 0.f;
 #pragma unroll
-    for (int w = 0; w < DM_WARPS; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       const float* ws = red + ((size_t)w * 16 + r) * WS;
       const float c = (ws[D] == -INFINITY) ? 0.f : exp2f(ws[D] - mm);
       num += ws[d] * c;
@@ -533,17 +534,16 @@ static const CUtensorMap* cache_map(const void* base, long long rows, int head_d
   return &maps.emplace(key, m).first->second;
 }
 
-template <int D64, int BR, bool FUSED = false>
-static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, cudaStream_t stream,
-                     const FusedQkv& f = FusedQkv()) {
+template <int D64, int BR, bool FUSED, int WARPS>
+static int launch_dt_w(const AttnArgs& a, long long cache_rows, int* error_flag, cudaStream_t stream, const FusedQkv& f) {
   constexpr int D = D64 * 64;
   const CUtensorMap* mk = cache_map(a.k_cache, cache_rows, D, BR);
   const CUtensorMap* mv = cache_map(a.v_cache, cache_rows, D, BR);
   if (mk == nullptr || mv == nullptr) return TS_ERR_UNSUPPORTED;
-  const size_t tiles = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TK * D * 2 + 1024;
-  const size_t red = sizeof(float) * (size_t)DM_WARPS * 16 * (D + 2) + 1024;
+  const size_t tiles = (size_t)WARPS * DM_STAGES * 2 * DM_TK * D * 2 + 1024;
+  const size_t red = sizeof(float) * (size_t)WARPS * 16 * (D + 2) + 1024;
   const size_t smem = tiles > red ? tiles : red;
-  auto kern = decode_attn_tma_kernel<D64, BR, FUSED>;
+  auto kern = decode_attn_tma_kernel<D64, BR, FUSED, WARPS>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -552,7 +552,20 @@ static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, c
   const int passes = (G + 15) / 16;
   if (a.num_splits > 1 && (long long)a.num_seqs * a.num_kv_heads * passes > DM_MAX_COUNTERS) return TS_ERR_UNSUPPORTED;
   dim3 grid(a.num_seqs, a.num_kv_heads * passes, a.num_splits);
-  return launch(kern, grid, DM_THREADS, smem, stream, *mk, *mv, a, f, passes, error_flag);
+  return launch(kern, grid, WARPS * 32, smem, stream, *mk, *mv, a, f, passes, error_flag);
+}
+
+// Four warps per CTA run three to an SM (registers, shared memory); an unsplit grid of more than
+// 3 x 148 and at most 4 x 148 CTAs would need a second, nearly empty round of them, so it gets
+// CTAs of three warps, four to an SM (batch 64 of the 16 / 8 head layout: 512 CTAs).
+template <int D64, int BR, bool FUSED = false>
+static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, cudaStream_t stream,
+                     const FusedQkv& f = FusedQkv()) {
+  const int G = a.num_heads / a.num_kv_heads;
+  const long long ctas = (long long)a.num_seqs * a.num_kv_heads * ((G + 15) / 16) * a.num_splits;
+  if (D64 == 2 && a.num_splits == 1 && ctas > 3 * 148 && ctas <= 4 * 148)
+    return launch_dt_w<D64, BR, FUSED, 3>(a, cache_rows, error_flag, stream, f);
+  return launch_dt_w<D64, BR, FUSED, 4>(a, cache_rows, error_flag, stream, f);
 }
 
 }  // namespace ts
