@@ -124,6 +124,9 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--fused-decode-rows", type=int, default=None,
                     help="largest decode batch that takes the fused norm+rotation+attention kernel (0: never)")
+    ap.add_argument("--max-splits", type=int, default=None, help="most key ranges per request in decode attention")
+    ap.add_argument("--no-cluster-merge", action="store_true",
+                    help="decode attention merges its key ranges through global memory, not inside a cluster")
     ap.add_argument("--separate-norms", action="store_true",
                     help="decode steps run every RMSNorm as a kernel of its own (default: folded into the products "
                          "around it for up to 8 rows)")
@@ -151,6 +154,10 @@ def main() -> int:
 
     if args.separate_norms:
         ops.FUSE_STREAM_NORM = False
+    if args.max_splits is not None:
+        ops.MAX_SPLITS = args.max_splits
+    if args.no_cluster_merge:
+        ops.set_decode_cluster_merge(False)
     if args.fused_decode_rows is not None:
         ops.FUSED_DECODE_MAX_ROWS = args.fused_decode_rows
     fixed_pdl = args.no_pdl or args.pdl is not None

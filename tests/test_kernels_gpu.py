@@ -236,6 +236,27 @@ def test_attention_decode_grid_just_over_three_ctas_per_sm(batch, window) -> Non
     torch.testing.assert_close(out.float(), want.float(), **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("hq,hkv,d,page", [(16, 8, 128, 16), (14, 2, 64, 8), (40, 2, 128, 16), (5, 5, 64, 32)])
+@pytest.mark.parametrize("splits", [2, 3, 5, 8])
+@pytest.mark.parametrize("window", [0, 37])
+def test_decode_attention_cluster_merge_gives_the_same_bits(hq, hkv, d, page, splits, window, monkeypatch) -> None:
+    """2 to 8 key ranges of a request merge inside a thread-block cluster; through global memory
+    (the path of more ranges) the same sums are formed in the same order."""
+    monkeypatch.setattr(ops, "MAX_SPLITS", splits)
+    lens = [(2048, 1), (1, 1), (777, 1), (130, 1)]
+    try:
+        ops.set_decode_cluster_merge(True)
+        out, want = _attention_case(torch.bfloat16, hq, hkv, d, page, lens, window, seed=9, spike=(0, 1500 if window == 0 else 2030))
+        ops.set_decode_cluster_merge(False)
+        plain, _ = _attention_case(torch.bfloat16, hq, hkv, d, page, lens, window, seed=9, spike=(0, 1500 if window == 0 else 2030))
+    finally:
+        ops.set_decode_cluster_merge(True)
+    ops.check_device_errors()
+    assert not out.isnan().any()
+    assert torch.equal(out, plain)
+    torch.testing.assert_close(out.float(), want.float(), **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("new", [1, 5])
 @pytest.mark.parametrize("pos", [0, 15, 16, 511, 700])

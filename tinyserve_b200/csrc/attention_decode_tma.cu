@@ -111,27 +111,43 @@ struct FusedQkv {
 // One head row (head_dim elements at src): optional RMSNorm with weight, optional rotate-half
 // rotation with the token's tables; result rounded to bf16 into dst0 and, if given, dst1.
 // Executed by a whole warp. Rounding points as in qk_rope_write.cu.
+// A lane's share of a per-head norm weight (the elements fused_head_row gives it). The weights
+// are constants of the model, so they are loaded before the kernel waits for its predecessor.
 template <int D>
-__device__ __forceinline__ void fused_head_row(const bf16* src, const bf16* weight, float eps, const float* c,
+struct HeadWeight {
+  static constexpr int MAXJ = (D / 2 + 63) / 64;
+  uint32_t a[MAXJ], b[MAXJ];
+  bool given;
+  __device__ __forceinline__ void load(const bf16* weight, int lane) {
+    given = weight != nullptr;
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+      const int p = 2 * lane + 64 * j;
+      a[j] = b[j] = 0x3f803f80u;                 // bf16 ones
+      if (given && p < D / 2) {
+        a[j] = *reinterpret_cast<const uint32_t*>(weight + p);
+        b[j] = *reinterpret_cast<const uint32_t*>(weight + D / 2 + p);
+      }
+    }
+  }
+};
+
+template <int D>
+__device__ __forceinline__ void fused_head_row(const bf16* src, const HeadWeight<D>& weight, float eps, const float* c,
                                                const float* s, bf16* dst0, bf16* dst1, int lane) {
   constexpr int HALF = D / 2, MAXJ = (HALF + 63) / 64;
-  // every load first (row, weights, tables), so that they travel together
-  uint32_t xa[MAXJ], xb[MAXJ], wa[MAXJ], wb[MAXJ];
+  // every load first (row, tables), so that they travel together
+  uint32_t xa[MAXJ], xb[MAXJ];
   float2 cv[MAXJ], sv[MAXJ];
 #pragma unroll
   for (int j = 0; j < MAXJ; ++j) {
     const int p = 2 * lane + 64 * j;
     xa[j] = xb[j] = 0u;
-    wa[j] = wb[j] = 0x3f803f80u;                 // bf16 ones
     cv[j] = make_float2(1.f, 1.f);
     sv[j] = make_float2(0.f, 0.f);
     if (p < HALF) {
       xa[j] = *reinterpret_cast<const uint32_t*>(src + p);
       xb[j] = *reinterpret_cast<const uint32_t*>(src + HALF + p);
-      if (weight != nullptr) {
-        wa[j] = *reinterpret_cast<const uint32_t*>(weight + p);
-        wb[j] = *reinterpret_cast<const uint32_t*>(weight + HALF + p);
-      }
       if (c != nullptr) {
         cv[j] = *reinterpret_cast<const float2*>(c + p);
         sv[j] = *reinterpret_cast<const float2*>(s + p);
@@ -146,13 +162,13 @@ __device__ __forceinline__ void fused_head_row(const bf16* src, const bf16* weig
     b[j][0] = __uint_as_float(xb[j] << 16); b[j][1] = __uint_as_float(xb[j] & 0xffff0000u);
     ss += a[j][0] * a[j][0] + a[j][1] * a[j][1] + b[j][0] * b[j][0] + b[j][1] * b[j][1];
   }
-  if (weight != nullptr) {
+  if (weight.given) {
     ss = warp_sum(ss);
     const float rstd = rsqrtf(ss / (float)D + eps);
 #pragma unroll
     for (int j = 0; j < MAXJ; ++j) {
-      const float fa[2] = {__uint_as_float(wa[j] << 16), __uint_as_float(wa[j] & 0xffff0000u)};
-      const float fb[2] = {__uint_as_float(wb[j] << 16), __uint_as_float(wb[j] & 0xffff0000u)};
+      const float fa[2] = {__uint_as_float(weight.a[j] << 16), __uint_as_float(weight.a[j] & 0xffff0000u)};
+      const float fb[2] = {__uint_as_float(weight.b[j] << 16), __uint_as_float(weight.b[j] & 0xffff0000u)};
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         a[j][e] = round_to<bf16>(round_to<bf16>(a[j][e] * rstd) * fa[e]);
@@ -184,7 +200,11 @@ __device__ __forceinline__ void fused_head_row(const bf16* src, const bf16* weig
 // blockIdx = (request in the list, kv head * passes + pass, key range); a pass covers up to 16
 // query heads of the group.
 // WARPS: warps per CTA (4; 3 where one more CTA per SM lets a grid run as a single wave).
-template <int D64, int BR, bool FUSED, int WARPS>
+// CLUSTER: the CTAs of the key ranges of one (request, kv head, pass) form a thread-block cluster
+// (1, 1, num_splits) and merge their results through distributed shared memory instead of through
+// global memory and an arrival counter: the tail of the kernel, where no key is in flight any
+// more, is two cluster barriers long instead of two trips to L2 and one atomic.
+template <int D64, int BR, bool FUSED, int WARPS, bool CLUSTER>
 __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                      const __grid_constant__ CUtensorMap map_v,
                                                                      AttnArgs a, FusedQkv f, int passes,
@@ -268,6 +288,17 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     const int tile = first + s * WARPS;
     if (tile < tile_end && (FUSED || tile < ntiles_all - 1)) load_tile(tile, s);
   }
+  // (fused form) constants of the model and host-made inputs of the step, before the wait too
+  const bool owns_last = tile_begin < tile_end && tile_end == ntiles_all;   // this range ends at the newest key
+  HeadWeight<D> q_w, k_w;
+  int new_slot = 0;
+  if constexpr (FUSED) {
+    q_w.load(f.q_weight, lane);
+    if (owns_last) {
+      k_w.load(f.k_weight, lane);
+      new_slot = f.slots[qrow];
+    }
+  }
   pdl_wait();
   if constexpr (!FUSED) {
     for (int s = 0; s < DM_STAGES; ++s) {
@@ -277,7 +308,6 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
   }
 
   // (the first tiles are on their way; the work on the queries overlaps their flight)
-  const bool owns_last = tile_begin < tile_end && tile_end == ntiles_all;   // this range ends at the newest key
   if constexpr (FUSED) {
     const int width = (a.num_heads + 2 * a.num_kv_heads) * D;
     const bf16* row = f.qkv + (size_t)qrow * width;
@@ -285,7 +315,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     const float* sn = f.sin_t ? f.sin_t + (size_t)qrow * (D / 2) : nullptr;
     for (int r = warp; r < 16; r += WARPS) {
       if (r < ng) {
-        fused_head_row<D>(row + (size_t)(kvh * G + g0 + r) * D, f.q_weight, f.eps, c, sn, q_stage + r * D, nullptr, lane);
+        fused_head_row<D>(row + (size_t)(kvh * G + g0 + r) * D, q_w, f.eps, c, sn, q_stage + r * D, nullptr, lane);
       } else {
         for (int i = lane * 8; i < D; i += 256) *reinterpret_cast<uint4*>(q_stage + r * D + i) = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -293,12 +323,11 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     if (owns_last) {
       // the new key (normalised, rotated) and value: into the cache for later steps (once per
       // kv head: the CTA of the first pass writes) and into shared memory for this step
-      const int slot = f.slots[qrow];
-      const int page = slot / a.page_size, off = slot - page * a.page_size;
+      const int page = new_slot / a.page_size, off = new_slot - page * a.page_size;
       const size_t at = kv_offset(page, kvh, off, a);
       const bool writer = (g0 == 0);
       if (warp == (ng % WARPS)) {
-        fused_head_row<D>(row + (size_t)(a.num_heads + kvh) * D, f.k_weight, f.eps, c, sn, new_kv,
+        fused_head_row<D>(row + (size_t)(a.num_heads + kvh) * D, k_w, f.eps, c, sn, new_kv,
                           writer ? f.k_cache + at : nullptr, lane);
       } else if (warp == ((ng + 1) % WARPS)) {
         const bf16* vsrc = row + (size_t)(a.num_heads + a.num_kv_heads + kvh) * D;
@@ -480,6 +509,10 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     const int head = kvh * G + g0 + r;
     if (a.num_splits == 1) {
       ((bf16*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = __float2bfloat16_rn(num / den);
+    } else if constexpr (CLUSTER) {
+      float* part = red + (size_t)WARPS * 16 * WS;          // [16][D + 2]: this range's sums, max and weight
+      part[r * WS + d] = num;
+      if (d == 0) { part[r * WS + D] = mm; part[r * WS + D + 1] = den; }
     } else {
       const size_t pidx = ((size_t)si * a.num_heads + head) * a.num_splits + split;
       a.part_acc[pidx * D + d] = num;
@@ -487,6 +520,47 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     }
   }
   if (a.num_splits == 1) return;
+  if constexpr (CLUSTER) {
+    // ---- every CTA of the cluster merges its share of the outputs from all ranges' shared
+    // memory, ranges in order (the sums of merge_splits, so both paths give the same bits)
+    const int S = a.num_splits;
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const uint32_t part_addr = dm_smem(red + (size_t)WARPS * 16 * WS);
+    const int total = ng * D;
+    const int share = (total + S - 1) / S;
+    const int end = min(total, (split + 1) * share);
+    for (int idx = split * share + threadIdx.x; idx < end; idx += WARPS * 32) {
+      const int r = idx / D, d = idx - r * D;
+      float v[8], ms[8], ls[8];
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        v[sp] = 0.f; ms[sp] = -INFINITY; ls[sp] = 0.f;
+        if (sp < S) {
+          uint32_t remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(part_addr), "r"(sp));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[sp]) : "r"(remote + 4u * (uint32_t)(r * WS + d)));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ms[sp]) : "r"(remote + 4u * (uint32_t)(r * WS + D)));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ls[sp]) : "r"(remote + 4u * (uint32_t)(r * WS + D + 1)));
+        }
+      }
+      float mm = -INFINITY;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) mm = fmaxf(mm, ms[sp]);
+      float num = 0.f, den = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        if (sp < S) {
+          const float c = (ms[sp] == -INFINITY) ? 0.f : exp2f(ms[sp] - mm);
+          num += v[sp] * c;
+          den += ls[sp] * c;
+        }
+      }
+      ((bf16*)a.out)[((size_t)qrow * a.num_heads + kvh * G + g0 + r) * D + d] = __float2bfloat16_rn(num / den);
+    }
+    // nobody leaves while another CTA may still read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    return;
+  }
   // ---- the CTA that arrives last for this (request, heads) merges the ranges
   unsigned int* counter = &g_dt_arrivals[((size_t)si * gridDim.y + blockIdx.y) % DM_MAX_COUNTERS];
   if (!cta_arrives_last(counter, (unsigned int)a.num_splits, &is_last)) return;
@@ -534,16 +608,18 @@ static const CUtensorMap* cache_map(const void* base, long long rows, int head_d
   return &maps.emplace(key, m).first->second;
 }
 
-template <int D64, int BR, bool FUSED, int WARPS>
+static int g_decode_cluster_merge = 1;
+
+template <int D64, int BR, bool FUSED, int WARPS, bool CLUSTER>
 static int launch_dt_w(const AttnArgs& a, long long cache_rows, int* error_flag, cudaStream_t stream, const FusedQkv& f) {
   constexpr int D = D64 * 64;
   const CUtensorMap* mk = cache_map(a.k_cache, cache_rows, D, BR);
   const CUtensorMap* mv = cache_map(a.v_cache, cache_rows, D, BR);
   if (mk == nullptr || mv == nullptr) return TS_ERR_UNSUPPORTED;
   const size_t tiles = (size_t)WARPS * DM_STAGES * 2 * DM_TK * D * 2 + 1024;
-  const size_t red = sizeof(float) * (size_t)WARPS * 16 * (D + 2) + 1024;
+  const size_t red = sizeof(float) * (size_t)(WARPS + 1) * 16 * (D + 2) + 1024;     // the warps' results and the CTA's
   const size_t smem = tiles > red ? tiles : red;
-  auto kern = decode_attn_tma_kernel<D64, BR, FUSED, WARPS>;
+  auto kern = decode_attn_tma_kernel<D64, BR, FUSED, WARPS, CLUSTER>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -552,6 +628,9 @@ static int launch_dt_w(const AttnArgs& a, long long cache_rows, int* error_flag,
   const int passes = (G + 15) / 16;
   if (a.num_splits > 1 && (long long)a.num_seqs * a.num_kv_heads * passes > DM_MAX_COUNTERS) return TS_ERR_UNSUPPORTED;
   dim3 grid(a.num_seqs, a.num_kv_heads * passes, a.num_splits);
+  if (CLUSTER)
+    return launch_cluster(kern, grid, WARPS * 32, smem, stream, dim3(1, 1, a.num_splits), *mk, *mv, a, f, passes,
+                          error_flag);
   return launch(kern, grid, WARPS * 32, smem, stream, *mk, *mv, a, f, passes, error_flag);
 }
 
@@ -564,13 +643,20 @@ static int launch_dt(const AttnArgs& a, long long cache_rows, int* error_flag, c
   const int G = a.num_heads / a.num_kv_heads;
   const long long ctas = (long long)a.num_seqs * a.num_kv_heads * ((G + 15) / 16) * a.num_splits;
   if (D64 == 2 && a.num_splits == 1 && ctas > 3 * 148 && ctas <= 4 * 148)
-    return launch_dt_w<D64, BR, FUSED, 3>(a, cache_rows, error_flag, stream, f);
-  return launch_dt_w<D64, BR, FUSED, 4>(a, cache_rows, error_flag, stream, f);
+    return launch_dt_w<D64, BR, FUSED, 3, false>(a, cache_rows, error_flag, stream, f);
+  // 2 to 8 key ranges (the portable cluster size) merge inside a cluster
+  if (g_decode_cluster_merge && a.num_splits >= 2 && a.num_splits <= 8)
+    return launch_dt_w<D64, BR, FUSED, 4, true>(a, cache_rows, error_flag, stream, f);
+  return launch_dt_w<D64, BR, FUSED, 4, false>(a, cache_rows, error_flag, stream, f);
 }
 
 }  // namespace ts
 
 using namespace ts;
+
+// Whether 2 to 8 key ranges are merged inside a thread-block cluster (on by default) or through
+// global memory like larger numbers of ranges; both give the same bits.
+extern "C" void ts_set_decode_cluster_merge(int on) { g_decode_cluster_merge = on; }
 
 // bf16 decode attention with TMA tile loads. head_dim 64 or 128; page_size 8 or a multiple of 16;
 // num_pages_total = pages of the cache tensors (the pad page included). Other arguments as

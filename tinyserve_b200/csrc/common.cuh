@@ -125,12 +125,64 @@ constexpr int PDL_ELEMENTWISE = 1, PDL_SKINNY = 2, PDL_ATTENTION = 4, PDL_TCGEN0
 #define TS_PDL_CLASS PDL_OTHER
 #endif
 
+#ifdef TS_TIMELINE
+// Built with -DTS_TIMELINE, the first thread of the first CTA of every launch notes the device
+// clock (ns) when it starts and when its wait for the earlier kernels returns: the only way to
+// see, inside a replayed graph with overlapping launches, when each kernel really began and how
+// long the chain before it took. Records are kept per source file and read back sorted by time
+// (ts_timeline_read). Costs an atomic and two stores per launch; never part of a timed build.
+constexpr int TL_CAP = 16384;
+static __device__ unsigned long long tl_records[TL_CAP * 3];
+static __device__ unsigned int tl_count;
+extern "C" void ts_timeline_register(void* records, void* count, int cap);
+__device__ __forceinline__ unsigned long long tl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned int& tl_slot() {
+  __shared__ unsigned int slot;
+  return slot;
+}
+__device__ __forceinline__ bool tl_first() {
+  return (threadIdx.x | threadIdx.y | threadIdx.z | blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+}
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (tl_first()) {
+    const unsigned int s = atomicAdd(&tl_count, 1u) % TL_CAP;
+    tl_slot() = s;
+    tl_records[3 * s] = (unsigned long long)TS_PDL_CLASS | ((unsigned long long)gridDim.x << 8) |
+                        ((unsigned long long)gridDim.y << 28) | ((unsigned long long)blockDim.x << 44);
+    tl_records[3 * s + 2] = 0;
+    tl_records[3 * s + 1] = tl_now();
+  }
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tl_first()) {
+    const unsigned int s = tl_slot();
+    if (tl_records[3 * s + 2] == 0) tl_records[3 * s + 2] = tl_now();
+  }
+}
+static inline void tl_register_once() {
+  static bool done = false;
+  if (done) return;
+  done = true;
+  void *r = nullptr, *c = nullptr;
+  if (cudaGetSymbolAddress(&r, tl_records) == cudaSuccess && cudaGetSymbolAddress(&c, tl_count) == cudaSuccess)
+    ts_timeline_register(r, c, TL_CAP);
+}
+#else
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+static inline void tl_register_once() {}
+#endif
 
 template <typename... KArgs, typename... Args>
 static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                          Args... args) {
+  tl_register_once();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -141,6 +193,28 @@ static inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = (g_programmatic_launch & TS_PDL_CLASS) ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// The same with the CTAs grouped into thread-block clusters of `cluster` CTAs.
+template <typename... KArgs, typename... Args>
+static inline int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 dim3 cluster, Args... args) {
+  tl_register_once();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (g_programmatic_launch & TS_PDL_CLASS) ? 2 : 1;
   return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -202,6 +202,38 @@ using namespace ts;
 extern "C" void ts_set_programmatic_launch(int mask) { g_programmatic_launch = mask; }
 extern "C" int ts_get_programmatic_launch() { return g_programmatic_launch; }
 
+// ---- kernel timeline (only in a library built with -DTS_TIMELINE; else always empty)
+static void* g_tl_records[64];
+static void* g_tl_counts[64];
+static int g_tl_files = 0, g_tl_cap = 0;
+extern "C" void ts_timeline_register(void* records, void* count, int cap) {
+  if (g_tl_files < 64) {
+    g_tl_records[g_tl_files] = records;
+    g_tl_counts[g_tl_files] = count;
+    ++g_tl_files;
+    g_tl_cap = cap;
+  }
+}
+// Copies up to `cap` records {kernel class and launch shape, start ns, wait-returned ns} of all
+// source files to `out` (host memory, 3 words a record, unsorted) and empties the device side.
+// Synchronises the device. Returns the number of records, or -1 on a CUDA error.
+extern "C" int ts_timeline_read(unsigned long long* out, int cap) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  int n = 0;
+  for (int f = 0; f < g_tl_files; ++f) {
+    unsigned int count = 0;
+    if (cudaMemcpy(&count, g_tl_counts[f], sizeof(count), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    int take = (int)(count < (unsigned int)g_tl_cap ? count : (unsigned int)g_tl_cap);
+    if (take > cap - n) take = cap - n;
+    if (take > 0 && cudaMemcpy(out + 3 * (size_t)n, g_tl_records[f], sizeof(unsigned long long) * 3 * take,
+                               cudaMemcpyDeviceToHost) != cudaSuccess)
+      return -1;
+    n += take;
+    if (cudaMemset(g_tl_counts[f], 0, sizeof(unsigned int)) != cudaSuccess) return -1;
+  }
+  return n;
+}
+
 extern "C" int ts_embed(const int* tokens, const void* table, float* out, int num_tokens, int hidden,
                         int vocab, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;

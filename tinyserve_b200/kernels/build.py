@@ -26,6 +26,11 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
+# TINYSERVE_B200_TIMELINE=1 builds a second library (in a folder of its own) whose kernels note
+# when they start and when their wait for the kernels before them returns (ops.timeline()).
+TIMELINE = os.environ.get("TINYSERVE_B200_TIMELINE", "") not in ("", "0")
+if TIMELINE:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DTS_TIMELINE"]
 LIB_NAME = "libtinyserve_b200.so"
 
 _lock = threading.Lock()
@@ -81,10 +86,10 @@ def build_dir() -> Path:
         if not _writable(d):
             raise KernelBuildError(f"TINYSERVE_B200_BUILD_DIR={override} is not writable")
         return d
-    d = CSRC / "_build"
+    d = CSRC / ("_build_timeline" if TIMELINE else "_build")
     if _writable(d):
         return d
-    d = Path(tempfile.gettempdir()) / f"tinyserve_b200_build_{os.getuid()}"
+    d = Path(tempfile.gettempdir()) / f"tinyserve_b200_build_{os.getuid()}{'_timeline' if TIMELINE else ''}"
     if _writable(d):
         return d
     raise KernelBuildError(f"no writable build folder (tried {CSRC / '_build'} and {d})")
