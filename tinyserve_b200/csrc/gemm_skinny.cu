@@ -44,6 +44,7 @@ constexpr int SK_WARPS = 8;
 constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_KSTEP = SK_WARPS * 32;    // distance between a warp's k blocks
 constexpr int SK_MAX_SPLIT = 8;
+constexpr int SK_TALL_WARPS = 16, SK_TALL_PF = 6;
 constexpr int SK_SPLIT_MAX_ROWS = 16;      // K is split across CTAs only for M up to this
 constexpr int SK_SPLIT_MAX_COLS = 2 * 6144;   // and for at most this many (gate + up) columns
 constexpr int SK_MAX_TILES = 1024;
@@ -111,14 +112,18 @@ __device__ __forceinline__ uint4 normed_fragment(const uint4& rv, const uint4& w
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool XRING, bool NORMX = false, bool RESID = false>
-__global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+// WARPS: warps of a CTA, which split K between them (8; 16 in the tall form, see launch_skinny).
+template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool XRING, bool NORMX = false, bool RESID = false,
+          int WARPS = SK_WARPS>
+__global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                  TOut* __restrict__ out, int M, int N, int K,
                                                                  SkinnyNorm nrm) {
   static_assert(!(RESID && FUSE), "the fused activation is not added to the stream");
+  static_assert(!NORMX || WARPS == 8, "the sums of squares are spread over eight warps");
+  constexpr int KSTEP = WARPS * 32;      // distance between a warp's k blocks
   constexpr int TILES = FUSE ? 2 * RT : RT;
   constexpr int COLS = 8 * NT;
-  extern __shared__ float red[];   // [SK_WARPS][TILES][16][COLS]
+  extern __shared__ float red[];   // [WARPS][TILES][16][COLS]
   __shared__ int is_last;
   __shared__ float rstd_s[16];
   pdl_trigger();
@@ -141,7 +146,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
   uint4 ring[SK_PF][TILES][2];
 #pragma unroll
   for (int p = 0; p < SK_PF; ++p) {
-    const int kb = k_lo + warp * 32 + p * SK_KSTEP;
+    const int kb = k_lo + warp * 32 + p * KSTEP;
     if (kb < k_hi) {
 #pragma unroll
       for (int r = 0; r < TILES; ++r) {
@@ -189,7 +194,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
   if constexpr (XRING) {
 #pragma unroll
     for (int p = 0; p < SK_PF; ++p) {
-      const int kb = k_lo + warp * 32 + p * SK_KSTEP;
+      const int kb = k_lo + warp * 32 + p * KSTEP;
 #pragma unroll
       for (int j = 0; j < NT; ++j)
         xring[p][j] = !(kb < k_hi && xok[j]) ? make_uint4(0u, 0u, 0u, 0u) : ld_cached((NORMX ? rrow[j] : xrow[j]) + kb);
@@ -197,10 +202,10 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
     }
   }
 
-  for (int kb0 = k_lo + warp * 32; kb0 < k_hi; kb0 += SK_PF * SK_KSTEP) {
+  for (int kb0 = k_lo + warp * 32; kb0 < k_hi; kb0 += SK_PF * KSTEP) {
 #pragma unroll
     for (int p = 0; p < SK_PF; ++p) {
-      const int kb = kb0 + p * SK_KSTEP;
+      const int kb = kb0 + p * KSTEP;
       if (kb < k_hi) {
         uint4 a[TILES][2];
 #pragma unroll
@@ -213,7 +218,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
           else if constexpr (NORMX) b[j] = xok[j] ? normed_fragment(ld_cached(rrow[j] + kb), ld_cached(nrm.weight + kb + 8 * t)) : make_uint4(0u, 0u, 0u, 0u);
           else b[j] = xok[j] ? ld_cached(xrow[j] + kb) : make_uint4(0u, 0u, 0u, 0u);
         }
-        const int nxt = kb + SK_PF * SK_KSTEP;
+        const int nxt = kb + SK_PF * KSTEP;
         if (nxt < k_hi) {
 #pragma unroll
           for (int r = 0; r < TILES; ++r) {
@@ -279,15 +284,15 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
     sq += __shfl_xor_sync(0xffffffffu, sq, 1);
     if (row == 0 && m < M) nrm.sumsq_out[m * gridDim.x + blockIdx.x] = sq;
   };
-  for (int idx = threadIdx.x; idx < RT * 16 * COLS; idx += SK_THREADS) {
+  for (int idx = threadIdx.x; idx < RT * 16 * COLS; idx += WARPS * 32) {
     const int m = idx / (RT * 16), row = idx - m * (RT * 16);
     float s = 0.f, u = 0.f;
     if (m < M) {
 #pragma unroll
-      for (int wq = 0; wq < SK_WARPS; ++wq) s += red[(size_t)wq * TILES * 16 * COLS + row * COLS + m];
+      for (int wq = 0; wq < WARPS; ++wq) s += red[(size_t)wq * TILES * 16 * COLS + row * COLS + m];
       if constexpr (FUSE) {
 #pragma unroll
-        for (int wq = 0; wq < SK_WARPS; ++wq) u += red[(size_t)wq * TILES * 16 * COLS + (RT * 16 + row) * COLS + m];
+        for (int wq = 0; wq < WARPS; ++wq) u += red[(size_t)wq * TILES * 16 * COLS + (RT * 16 + row) * COLS + m];
       }
       if (ksplit > 1) {
         part[(size_t)m * width + n0 + row] = s;
@@ -313,7 +318,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(const bf16* __r
   if (ksplit == 1) return;
   // ---- the CTA of this row tile that arrives last adds the slices in order
   if (!cta_arrives_last(&g_skinny_arrivals[blockIdx.x], (unsigned int)ksplit, &is_last)) return;
-  for (int idx = threadIdx.x; idx < RT * 16 * COLS; idx += SK_THREADS) {
+  for (int idx = threadIdx.x; idx < RT * 16 * COLS; idx += WARPS * 32) {
     const int m = idx / (RT * 16), row = idx - m * (RT * 16);
     float s = 0.f, u = 0.f;
     if (m < M) {
@@ -359,6 +364,18 @@ static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, 
   }
   constexpr bool CAN_RING = (!FUSE && RT == 1 && NT == 1);
   const bool ring = CAN_RING && K / ksplit <= SK_PF * SK_KSTEP;
+  // The tall form: when the row tiles alone leave SMs idle and a CTA of 16 warps can have its
+  // whole share of the weights in flight (6 k blocks a warp: K up to 3,072), K is split between
+  // the warps of one CTA only. Splitting it across CTAs instead costs a trip through global memory,
+  // an arrival counter and a second pass by the last CTA, about 1.7 us at the end of a kernel in
+  // which nothing else is left to overlap them (measured on B200 inside a decode step).
+  if constexpr (CAN_RING && !NORMX) {
+    if (ksplit > 1 && K <= SK_TALL_PF * SK_TALL_WARPS * 32) {
+      auto tall = gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_TALL_PF, true, NORMX, RESID, SK_TALL_WARPS>;
+      const size_t tall_smem = sizeof(float) * SK_TALL_WARPS * TILES * 16 * 8 * NT;
+      return launch(tall, dim3(tiles, 1), SK_TALL_WARPS * 32, tall_smem, stream, x, w, out, M, N, K, nrm);
+    }
+  }
   void (*kern)(const bf16*, const bf16*, TOut*, int, int, int, SkinnyNorm) =
       gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_PF, false, NORMX, RESID>;
   if constexpr (CAN_RING) {
@@ -379,9 +396,128 @@ static int row_tiles_for(int N, int most) {
   return rt;
 }
 
+// The streaming form, for matrices of very many rows (the output head: 151,936 x 1,024): a CTA
+// takes row tiles blockIdx.x, + gridDim.x, ... one after the other, and asks for the weights of
+// its next tile while the sums of the current one are still being added up and stored, so its
+// requests never pause. (With one tile per CTA, a CTA's loads stop while it reduces and stores,
+// and the next CTA on the SM starts with an empty pipeline: 16 rows on the head of 151,936 x 1,024
+// take 184 us that way and 103 us in this form.)
+// K must be a multiple of SK_ST_PF * 256, so that the ring of weight registers turns over in step
+// with the tiles.
+constexpr int SK_ST_PF = 4;
+template <typename TOut, int NT, int RT>
+__global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const bf16* __restrict__ x,
+                                                                        const bf16* __restrict__ w,
+                                                                        TOut* __restrict__ out, int M, int N, int K) {
+  constexpr int PF = SK_ST_PF, COLS = 8 * NT;
+  extern __shared__ float red[];   // [SK_WARPS][RT][16][COLS]
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int tiles = N / (16 * RT);
+  const size_t tile_stride = (size_t)16 * RT * K;
+  const bf16* lane_w = w + (size_t)g * K + 8 * t + warp * 32;      // row g of tile 0, this lane's k offset
+  uint4 ring[PF][RT][2];
+  {
+    const bf16* base = lane_w + (size_t)blockIdx.x * tile_stride;
+#pragma unroll
+    for (int p = 0; p < PF; ++p)
+#pragma unroll
+      for (int r = 0; r < RT; ++r) {
+        ring[p][r][0] = ld_stream(base + (size_t)(r * 16) * K + p * SK_KSTEP);
+        ring[p][r][1] = ld_stream(base + (size_t)(r * 16 + 8) * K + p * SK_KSTEP);
+      }
+  }
+  pdl_wait();
+  const bf16* xrow[NT];
+  bool xok[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int m = 8 * j + g;
+    xok[j] = m < M;
+    xrow[j] = x + (size_t)(xok[j] ? m : 0) * K + 8 * t + warp * 32;
+  }
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const bool has_next = tile + (int)gridDim.x < tiles;
+    const bf16* cur = lane_w + (size_t)tile * tile_stride;
+    const bf16* nxt_tile = cur + (size_t)gridDim.x * tile_stride;
+    float acc[RT][NT][4];
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[r][j][e] = 0.f;
+    for (int kb0 = 0; kb0 < K; kb0 += PF * SK_KSTEP) {
+#pragma unroll
+      for (int p = 0; p < PF; ++p) {
+        const int kb = kb0 + p * SK_KSTEP;
+        uint4 b[NT];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) b[j] = xok[j] ? ld_cached(xrow[j] + kb) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int r = 0; r < RT; ++r)
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            mma_bf16_16816(acc[r][j], ring[p][r][0].x, ring[p][r][1].x, ring[p][r][0].y, ring[p][r][1].y, b[j].x, b[j].y);
+            mma_bf16_16816(acc[r][j], ring[p][r][0].z, ring[p][r][1].z, ring[p][r][0].w, ring[p][r][1].w, b[j].z, b[j].w);
+          }
+        // the registers are free again: the same k block of the next round, or of the next tile
+        const int ahead = kb + PF * SK_KSTEP;
+        if (ahead < K || has_next) {
+          const bf16* src = ahead < K ? cur + ahead : nxt_tile + (ahead - K);
+#pragma unroll
+          for (int r = 0; r < RT; ++r) {
+            ring[p][r][0] = ld_stream(src + (size_t)(r * 16) * K);
+            ring[p][r][1] = ld_stream(src + (size_t)(r * 16 + 8) * K);
+          }
+        }
+      }
+    }
+    float* mine = red + (size_t)warp * RT * 16 * COLS;
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        float* tl = mine + (size_t)r * 16 * COLS + j * 8;
+        tl[g * COLS + 2 * t] = acc[r][j][0];
+        tl[g * COLS + 2 * t + 1] = acc[r][j][1];
+        tl[(g + 8) * COLS + 2 * t] = acc[r][j][2];
+        tl[(g + 8) * COLS + 2 * t + 1] = acc[r][j][3];
+      }
+    __syncthreads();
+    const int n0 = tile * 16 * RT;
+    for (int idx = threadIdx.x; idx < RT * 16 * COLS; idx += SK_THREADS) {
+      const int m = idx / (RT * 16), row = idx - m * (RT * 16);
+      if (m < M) {
+        float sum = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < SK_WARPS; ++wq) sum += red[(size_t)wq * RT * 16 * COLS + row * COLS + m];   // a fixed order
+        out[(size_t)m * N + n0 + row] = from_float<TOut>(sum);
+      }
+    }
+    __syncthreads();      // the sums are read; the next tile may overwrite them
+  }
+}
+
+template <typename TOut, int NT, int RT>
+static int launch_skinny_stream(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
+  const int tiles = N / (16 * RT);
+  const size_t smem = sizeof(float) * SK_WARPS * RT * 16 * 8 * NT;
+  auto kern = gemm_skinny_stream_kernel<TOut, NT, RT>;
+  return launch(kern, dim3(tiles < 2 * 148 ? tiles : 2 * 148), SK_THREADS, smem, stream, x, w, out, M, N, K);
+}
+
 template <typename TOut, int NT>
 static int dispatch_skinny_nt(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
   const int rt = row_tiles_for(N, 2);
+  if constexpr (NT == 2) {
+    // 9 to 16 rows and at least eight tiles for each CTA. (Up to 8 rows the streaming form is
+    // faster alone, 64 against 71 us for the head of 151,936 x 1,024, but slower inside a decode
+    // step, 110 against 77 us, for a reason that was not found; so those keep one tile per CTA.)
+    if (rt == 2 && K % (SK_ST_PF * SK_KSTEP) == 0 && N / 32 >= 8 * 2 * 148)
+      return launch_skinny_stream<TOut, NT, 2>(x, w, out, M, N, K, stream);
+  }
   if (rt == 2) return launch_skinny<TOut, NT, 2, false, 4>(x, w, out, M, N, K, stream);
   return launch_skinny<TOut, NT, 1, false, 4>(x, w, out, M, N, K, stream);
 }
