@@ -130,7 +130,7 @@ def main() -> int:
     ap.add_argument("--separate-norms", action="store_true",
                     help="decode steps run every RMSNorm as a kernel of its own (default: folded into the products "
                          "around it for up to 8 rows)")
-    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--profile", choices=["decode", "prefill", "timeline"], default=None,
                     help="run a small case kernel by kernel between cudaProfilerStart/Stop and exit "
                          "(for ncu --profile-from-start off); combine with --layers, --batch")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
@@ -247,6 +247,34 @@ def main() -> int:
         h2d = 4 * (batch * (8 + width) + 16)
         return ms, h2d, 4 * batch
 
+    if args.profile == "timeline":
+        # When each kernel of one recorded decode step started and when its wait for the kernels
+        # before it returned, from the device clock. Needs the library built with the notes in
+        # (TINYSERVE_B200_TIMELINE=1 in the environment); no JSON line, no timing claim.
+        if not ops.build.TIMELINE:
+            print("--profile timeline needs TINYSERVE_B200_TIMELINE=1 in the environment")
+            return 2
+        e = prefilled(args.batch, 16)
+        reqs = list(e.requests.values())
+        out = torch.empty(args.batch, dtype=torch.int32, device=dev)
+        for it in range(12):
+            if it == 11:
+                ops.timeline()
+            entries = []
+            for r in reqs:
+                e.cache.append(r.cache, 1)
+                entries.append(StepEntry(r.cache, [r.output[-1]]))
+            ops.sample(e.runner.step(entries), out)
+        records = ops.timeline()
+        t0 = records[0]["start"]
+        print(f"one decode step, batch {args.batch}, layers {cfg.num_layers}: us from the first kernel's start")
+        print(f"{'#':>4} {'class':<12} {'grid':<12} {'block':>5} {'started':>9} {'wait over':>9} {'to next wait':>12}")
+        for i, r in enumerate(records):
+            w = r["waited"] or r["start"]
+            nxt = (records[i + 1]["waited"] or records[i + 1]["start"]) if i + 1 < len(records) else w
+            print(f"{i:>4} {r['class']:<12} {str(r['grid']):<12} {r['block']:>5} {(r['start'] - t0) / 1e3:>9.2f} "
+                  f"{(w - t0) / 1e3:>9.2f} {(nxt - w) / 1e3:>12.2f}")
+        return 0
     if args.profile:
         # A small, eager case for a profiler: nothing is timed and no JSON line is printed.
         args.no_graphs = True
