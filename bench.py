@@ -26,14 +26,14 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# BASELINE configs[2]: the Qwen3-0.6B layer sizes.
+# The headline configuration: the Qwen3-0.6B layer sizes.
 QWEN3_0_6B = {
     "architectures": ["Qwen3ForCausalLM"], "vocab_size": 151936, "hidden_size": 1024,
     "intermediate_size": 3072, "num_hidden_layers": 28, "num_attention_heads": 16,
     "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
     "max_position_embeddings": 4096, "tie_word_embeddings": True, "hidden_act": "silu",
 }
-# BASELINE configs[3] and configs[4]: the Qwen3-8B and Qwen3-32B layer sizes (untied heads).
+# Two larger configurations: the Qwen3-8B and Qwen3-32B layer sizes (untied heads).
 QWEN3_8B = {**QWEN3_0_6B, "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 36,
             "num_attention_heads": 32, "num_key_value_heads": 8, "tie_word_embeddings": False}
 QWEN3_32B = {**QWEN3_0_6B, "hidden_size": 5120, "intermediate_size": 25600, "num_hidden_layers": 64,
@@ -114,7 +114,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--model", choices=sorted(MODELS), default="0.6b",
-                    help="layer sizes: the headline configuration (0.6b) or the larger BASELINE ones")
+                    help="layer sizes: the headline configuration (0.6b) or the two larger ones")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
