@@ -1,8 +1,10 @@
 """The framework takes parts and architectures it has never seen, without a change to its
-files: a toy mixer with state of its own (defined HERE), a layer with a sliding window, a
-partial interleaved rotation, a layer that runs twice and a call that reads another call's
-cache are registered, built from a config.json, loaded, and replayed under every cut of the
-work against a plain implementation of the same toy. (The toy is no model of anyone's.)"""
+files: a toy mixer with state of its own, a toy feed-forward that routes every token to one
+of three experts, a toy position encoding with its own angles (all three defined HERE), a
+layer with a sliding window, a partial interleaved rotation, a layer that runs twice and a
+call that reads another call's cache are registered, built from a config.json, loaded, and
+replayed under every cut of the work against a plain implementation of the same toy. (The toy
+is no model of anyone's.)"""
 
 from __future__ import annotations
 
@@ -19,7 +21,11 @@ import replay_cases as cases
 from tiny_configs import random_prompt
 
 from tinyserve_b200.config import LayerCall, LayerSpec, ModelConfig, ModelSpec, PartSpec, register_architecture
-from tinyserve_b200.parts import Mixer, StateNeed, TensorSpec, register_mixer
+from tinyserve_b200.parts import (
+    FeedForward, Mixer, PositionEncoding, StateNeed, TensorSpec, register_feed_forward, register_mixer,
+    register_position_encoding,
+)
+from tinyserve_b200.parts.rope import RotaryTables
 
 pytestmark = pytest.mark.gpu
 
@@ -60,6 +66,58 @@ class ToyEMAMixer(Mixer):
         return out
 
 
+# ------------------------------------------------- the toy feed-forward with routing
+class ToyRoutedFFN(FeedForward):
+    """Every token goes to the one expert with the largest router logit (32-bit) and gets
+    p_e * W2_e relu(W1_e x), p the softmax of the router logits."""
+
+    def __init__(self, prefix: str, hidden_size: int, expert_size: int, num_experts: int) -> None:
+        self.prefix, self.h, self.f, self.e = prefix, hidden_size, expert_size, num_experts
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        p = prefix + self.prefix
+        return [TensorSpec(p + "router.weight", (self.e, self.h), std=0.05, keep_32bit=True),
+                TensorSpec(p + "w1", (self.e * self.f, self.h)), TensorSpec(p + "w2", (self.e * self.h, self.f))]
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        p = prefix + self.prefix
+        self.router = tensors[p + "router.weight"].float()
+        self.w1 = tensors[p + "w1"].view(self.e, self.f, self.h)
+        self.w2 = tensors[p + "w2"].view(self.e, self.h, self.f)
+
+    def forward(self, x, ctx):
+        logits = x.float() @ self.router.t()
+        prob, expert = torch.softmax(logits, dim=-1).max(dim=-1)
+        out = ctx.arena.take(tuple(x.shape), ctx.dtype)
+        for e in range(self.e):
+            rows = (expert == e).nonzero().flatten()
+            hid = torch.relu(x[rows] @ self.w1[e].t())
+            out[rows] = ((hid @ self.w2[e].t()).float() * prob[rows, None]).to(ctx.dtype)
+        return out
+
+
+# ------------------------------------------------------ the toy position encoding
+class ToyLinearRotary(PositionEncoding):
+    """Rotation angles position * (i + 1) * step: frequencies in a line, not in a geometric row.
+    Hands the mixer the same kind of tables as the built-in encoding, made its own way."""
+
+    def __init__(self, rotary_dim: int, step: float) -> None:
+        self.rotary_dim, self.step = rotary_dim, step
+
+    def key(self) -> Any:
+        return ("toy_linear", self.rotary_dim, self.step)
+
+    def prepare(self, ctx) -> RotaryTables:
+        half = self.rotary_dim // 2
+        freq = torch.arange(1, half + 1, dtype=torch.float64, device=ctx.positions.device) * self.step
+        angle = ctx.positions.double()[:, None] * freq
+        cos = ctx.arena.take_step((ctx.num_tokens, half), torch.float32)
+        sin = ctx.arena.take_step((ctx.num_tokens, half), torch.float32)
+        cos.copy_(angle.cos())
+        sin.copy_(angle.sin())
+        return RotaryTables(cos, sin, self.rotary_dim, False)
+
+
 # ------------------------------------------------------------ the toy architecture
 @dataclass(frozen=True)
 class ToyConfig(ModelConfig):
@@ -90,9 +148,10 @@ class ToyConfig(ModelConfig):
                        PartSpec("gqa_attention", {"prefix": "attn.", "hidden_size": h, "num_heads": 4, "num_kv_heads": 2,
                                                   "head_dim": 16, "scale": 0.25, "window": self.window}),
                        ffn(64), norm("n1.weight"), norm("n2.weight"),
-                       PartSpec("rope", {"head_dim": 16, "rotary_dim": 16, "theta": 1e4}))
+                       PartSpec("toy_linear_rotary", {"rotary_dim": 16, "step": 0.013}))
         l1 = LayerSpec("layers.1.", "prenorm", PartSpec("toy_ema", {"prefix": "ema.", "hidden_size": h}),
-                       ffn(80), norm("n1.weight"), norm("n2.weight"), None)
+                       PartSpec("toy_routed", {"prefix": "moe.", "hidden_size": h, "expert_size": 40, "num_experts": 3}),
+                       norm("n1.weight"), norm("n2.weight"), None)
         l2 = LayerSpec("layers.2.", "prenorm",
                        PartSpec("gqa_attention", {"prefix": "attn.", "hidden_size": h, "num_heads": 2, "num_kv_heads": 2,
                                                   "head_dim": 32, "scale": 32 ** -0.5, "qk_norm": True,
@@ -109,6 +168,8 @@ class ToyConfig(ModelConfig):
 
 
 register_mixer("toy_ema", ToyEMAMixer, replace=True)
+register_feed_forward("toy_routed", ToyRoutedFFN, replace=True)
+register_position_encoding("toy_linear_rotary", ToyLinearRotary, replace=True)
 register_architecture("ToyHybridForCausalLM", ToyConfig, replace=True)
 
 
@@ -123,6 +184,9 @@ def rope_partial_interleaved(x, positions, rotary_dim, theta):
     return torch.cat([out, rest], dim=-1).to(x.dtype)
 
 
+gaps: list[float] = []      # smallest distance between the two best router logits, per sequence run
+
+
 def toy_plain(w: dict[str, torch.Tensor], ids: list[int], cfg: ToyConfig) -> torch.Tensor:
     t = len(ids)
     pos = torch.arange(t)
@@ -133,13 +197,28 @@ def toy_plain(w: dict[str, torch.Tensor], ids: list[int], cfg: ToyConfig) -> tor
         hn = plain.rms_norm(x, w[p + "n2.weight"], cfg.eps)
         return x + plain.swiglu(hn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
 
+    def routed(x, p):
+        hn = plain.rms_norm(x, w[p + "n2.weight"], cfg.eps)
+        logits = hn.float() @ w[p + "moe.router.weight"].float().t()
+        top2 = logits.topk(2, dim=-1).values
+        gaps.append((top2[:, 0] - top2[:, 1]).min().item())
+        prob = torch.softmax(logits, dim=-1)
+        w1, w2 = w[p + "moe.w1"].view(3, 40, cfg.hidden_size), w[p + "moe.w2"].view(3, cfg.hidden_size, 40)
+        rows = []
+        for i in range(t):
+            e = int(logits[i].argmax())
+            hid = torch.relu(plain.linear(hn[i: i + 1], w1[e]))
+            rows.append((plain.linear(hid, w2[e]).float() * prob[i, e]).to(x.dtype))
+        return x + torch.cat(rows)
+
     def attn0(x):
         p = "layers.0."
         hn = plain.rms_norm(x, w[p + "n1.weight"], cfg.eps)
         q = plain.linear(hn, w[p + "attn.q_proj.weight"]).view(t, 4, 16)
         k = plain.linear(hn, w[p + "attn.k_proj.weight"]).view(t, 2, 16)
         v = plain.linear(hn, w[p + "attn.v_proj.weight"]).view(t, 2, 16)
-        cos, sin = plain.rope_angles(16, 1e4, pos)
+        angle = pos.double()[:, None] * (torch.arange(1, 9, dtype=torch.float64) * 0.013)
+        cos, sin = angle.cos().float(), angle.sin().float()
         a = plain.causal_gqa_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v, 0.25, cfg.window)
         return mlp(x + plain.linear(a.reshape(t, 64), w[p + "attn.o_proj.weight"]), p)
 
@@ -153,7 +232,7 @@ def toy_plain(w: dict[str, torch.Tensor], ids: list[int], cfg: ToyConfig) -> tor
             s = decay * s + u[i]
             ys.append(s)
         y = (torch.stack(ys) @ w[p + "ema.out.weight"].float().t()).to(x.dtype)
-        return mlp(x + y, p)
+        return routed(x + y, p)
 
     def attn2(x, call, reads=None):
         p = "layers.2."
@@ -182,11 +261,16 @@ def toy(tmp_path_factory):
     from tinyserve_b200.weights import write_random_model
 
     cfg = ToyConfig()
-    folder = write_random_model(tmp_path_factory.mktemp("toy"), cfg, 5, torch.bfloat16, std_scale=8.0)
+    folder = write_random_model(tmp_path_factory.mktemp("toy"), cfg, 7, torch.bfloat16, std_scale=8.0)
     assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyHybridForCausalLM"]
-    reqs = {f"r{i}": random_prompt(n, cfg.vocab_size, 30 + i) for i, n in enumerate([3, 20, 41, 70])}
+    # Prompts under which no token sits near the border between two experts: the two best router
+    # logits are at least 0.4 apart (bf16 moves them by some hundredths), so a different expert in
+    # the engine would be a fault and not rounding.
+    reqs = {f"r{i}": random_prompt(n, cfg.vocab_size, seed) for i, (n, seed) in enumerate([(3, 37), (20, 54), (41, 68), (70, 60)])}
     w32 = plain.read_weights(folder, torch.float32)
+    gaps.clear()
     want = {rid: toy_plain(w32, toks, cfg) for rid, toks in reqs.items()}
+    assert len(gaps) == 4 and min(gaps) > 0.4
     return folder, cfg, reqs, want
 
 
