@@ -95,16 +95,19 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(rows)}
 
 
-def reference_arm() -> int:
-    """The upstream engine cannot be installed offline here: its build backend (hatchling) is
-    neither in the image nor in the offline wheelhouse."""
-    ref = ROOT / "baseline" / "_ref" / "tinyserve"
-    why = ("the reference's build backend hatchling is not installed and not in the offline wheelhouse, "
-           "so pip cannot build it (baseline/_ref is empty)")
-    if ref.is_dir():
-        why = "baseline/_ref holds the reference, but no reference arm was wired for it in this build"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+def reference_arm(args: argparse.Namespace) -> int:
+    """The same metric by the unmodified upstream engine (``baseline/reference_arm.py``); nothing of
+    this repository's package is imported on that path."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_arm as arm
+
+    cfg_dict = dict(MODELS[args.model])
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    pk, pk_src = peaks()
+    args.warmup = max(args.warmup, 3)
+    return arm.run(args, cfg_dict, full_layers, ClockSampler, pk, pk_src)
 
 
 def main() -> int:
@@ -139,7 +142,7 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU only; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     args.warmup = max(args.warmup, 3)
 
     import torch
