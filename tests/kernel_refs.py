@@ -162,7 +162,7 @@ def exponential_noise(vocab: int, seed: int, draw: int) -> torch.Tensor:
     return -torch.log(torch.from_numpy(u))
 
 
-def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None) -> None:
+def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None, status_out=None) -> None:
     """Greedy rows: first argmax. Others (upstream src/tinyserve/sampling.py:56-102, with
     this framework's noise): p = softmax(logits / T); with top_p < 1 keep tokens whose strictly
     more likely tokens hold less than top_p; pick argmax of log p - log E."""
@@ -193,6 +193,8 @@ def sample(logits, out, temperature=None, top_p=None, seeds=None, draws=None) ->
         score = torch.where(keep, z - torch.log(noise), torch.full_like(z, -math.inf))
         res.append(int(score.argmax()))
     out.copy_(torch.tensor(res, dtype=torch.int32, device=out.device))
+    if status_out is not None:
+        status_out.zero_()
 
 
 _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",

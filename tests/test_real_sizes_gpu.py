@@ -12,16 +12,9 @@ import torch
 import plain_qwen3 as plain
 import replay_cases as cases
 from test_replay_gpu import check, run_steps
-from tiny_configs import random_prompt
+from tiny_configs import REAL_0_6B as REAL, REAL_8B, random_prompt
 
 pytestmark = pytest.mark.gpu
-
-REAL = {
-    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 151936, "hidden_size": 1024,
-    "intermediate_size": 3072, "num_hidden_layers": 2, "num_attention_heads": 16, "num_key_value_heads": 8,
-    "head_dim": 128, "hidden_act": "silu", "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
-    "max_position_embeddings": 4096, "tie_word_embeddings": True,
-}
 
 
 @pytest.fixture(scope="module")
@@ -71,3 +64,58 @@ def test_real_layer_sizes_under_every_cut(real, dtype, variant, monkeypatch) -> 
         assert bool(calls) == (variant != "separate_rope")
     if dtype == torch.bfloat16:
         assert bool(fused_norm_calls) == (variant != "separate_norms")
+
+
+@pytest.fixture(scope="module")
+def real_8b(tmp_path_factory):
+    """The Qwen3-8B widths (hidden 4096, 32 / 8 heads of 128, intermediate 12,288, the real
+    vocabulary, untied head), one layer."""
+    from tinyserve_b200.config import config_from_dict
+    from tinyserve_b200.weights import write_random_model
+
+    folder = write_random_model(tmp_path_factory.mktemp("real8b"), config_from_dict(REAL_8B), 4, torch.bfloat16, std_scale=1.0)
+    reqs = {"a": random_prompt(150, 151936, 5), "b": random_prompt(37, 151936, 6)}
+    pcfg = plain.read_config(folder)
+    w32, w16 = plain.read_weights(folder, torch.float32), plain.read_weights(folder, torch.bfloat16)
+    want = ({r: plain.forward(pcfg, w32, t) for r, t in reqs.items()},
+            {r: plain.forward(pcfg, w16, t) for r, t in reqs.items()})
+    return folder, reqs, want
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_8b_layer_widths_under_every_cut(real_8b, dtype, monkeypatch) -> None:
+    """At these widths another set of kernels runs than at the 0.6B ones: the decode rows' products
+    leave the skinny kernel for the library (the matrices are larger than it is tuned for), the
+    norms run as kernels of their own (the stream is wider than the fusion takes), the output and
+    down projections of many rows go to the tcgen05 product (4,096 columns), and four query heads
+    share a kv head. The test also checks that those are the kernels that ran."""
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.model import DecoderModel
+
+    seen = {"mm": 0, "tcgen05": 0, "norm": 0, "normed": 0, "skinny": 0, "fused_attention": 0}
+
+    def counted(name, fn):
+        def wrapper(*a, **k):
+            seen[name] += 1
+            return fn(*a, **k)
+        return wrapper
+
+    monkeypatch.setattr(ops.torch, "mm", counted("mm", torch.mm))
+    for name, attr in (("tcgen05", "gemm_tcgen05"), ("norm", "add_rms_norm"), ("normed", "gemm_normed"),
+                       ("skinny", "gemm_skinny"), ("fused_attention", "decode_attention_fused")):
+        monkeypatch.setattr(ops, attr, counted(name, getattr(ops, attr)))
+    folder, reqs, want = real_8b
+    model = DecoderModel.from_folder(folder, dtype, "cuda")
+    plans = [cases.mixed(reqs, 5)]
+    for rid, toks in reqs.items():
+        plans += [cases.whole(rid, toks), cases.tail_decoded(rid, toks, 32), cases.portions(rid, toks, 2)]
+    for steps in plans:
+        got = run_steps(model, 16, steps, cases.max_live_tokens(steps))
+        check(got, want, {r: reqs[r] for r in got}, dtype)
+    ops.check_device_errors()
+    assert seen["norm"] > 0 and seen["normed"] == 0
+    if dtype == torch.bfloat16:
+        assert seen["mm"] > 0 and seen["tcgen05"] > 0 and seen["fused_attention"] > 0
+        assert seen["skinny"] > 0          # the output head of a few rows still streams through the skinny kernel
+    else:
+        assert seen["mm"] == 0 and seen["tcgen05"] == 0

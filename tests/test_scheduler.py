@@ -246,3 +246,23 @@ def test_schedule_ahead_stops_before_the_length_limit_and_survives_an_end_token(
     s.update([a], [11])
     assert a.status is Status.FINISHED and not s.has_work()
     assert all(g.allocator.num_used == 0 for g in s.cache.groups)
+
+
+def test_a_portion_cut_down_to_one_token_is_charged_to_the_budget() -> None:
+    """Two requests in mid-prompt and room for one more token in the step: the first gets it, the
+    second waits (it keeps its place and its cache); the step never exceeds ``max_batch_tokens``."""
+    s = make(num_pages=64, page=4, seqs=4, budget=4, chunked=True)
+    reqs = [Request(0, [1] * 3, 8), Request(1, [2] * 12, 2), Request(2, [3] * 12, 2), Request(3, [4] * 12, 2)]
+    for r in reqs:
+        r.cache = s.cache.new_request()
+        r.status = Status.RUNNING
+        s.running.append(r)
+    # request 0 decodes; request 1 has 2 prompt tokens left (they fit); 2 and 3 are in mid-prompt
+    s.cache.append(reqs[0].cache, 3)
+    reqs[0].output.append(5)
+    s.cache.append(reqs[1].cache, 10)
+    s.cache.append(reqs[2].cache, 4)
+    s.cache.append(reqs[3].cache, 4)
+    s.schedule()
+    assert [(r.request_id, r.num_scheduled) for r in s.running] == [(0, 1), (1, 2), (2, 1), (3, 0)]
+    assert sum(r.num_scheduled for r in s.scheduled()) == s.max_batch_tokens

@@ -35,6 +35,18 @@ TINY_C = {
 }
 TINY_C_PAGE = 32
 
+# Real layer widths with few layers: the sizes at which the tensor-core kernels take over. At the
+# Qwen3-8B widths another set of kernels runs than at the 0.6B ones (library products for decode
+# rows, tcgen05 for the narrow outputs, separate norms, four query heads per kv head).
+REAL_0_6B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 151936, "hidden_size": 1024,
+    "intermediate_size": 3072, "num_hidden_layers": 2, "num_attention_heads": 16, "num_key_value_heads": 8,
+    "head_dim": 128, "hidden_act": "silu", "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "max_position_embeddings": 4096, "tie_word_embeddings": True,
+}
+REAL_8B = {**REAL_0_6B, "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 1,
+           "num_attention_heads": 32, "num_key_value_heads": 8, "tie_word_embeddings": False}
+
 TINIES = {"A": (TINY_A, TINY_A_PAGE, 0), "B": (TINY_B, TINY_B_PAGE, 1), "C": (TINY_C, TINY_C_PAGE, 2)}
 
 

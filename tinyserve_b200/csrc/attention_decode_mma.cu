@@ -15,6 +15,7 @@
 // Every mbarrier wait is bounded; a wait that runs out sets *error_flag and the CTA leaves.
 #define TS_PDL_CLASS PDL_ATTENTION
 #include "attention.cuh"
+#include "bounded_wait.cuh"
 
 namespace ts {
 
@@ -23,7 +24,6 @@ namespace ts {
 #endif
 constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_TK = 16, DM_STAGES = DM_STAGES_N;
 constexpr int DM_MAX_COUNTERS = 1 << 16;
-constexpr long long DM_WAIT_CYCLES = 2000000000ll;
 
 static __device__ unsigned int g_dm_arrivals[DM_MAX_COUNTERS];
 
@@ -56,16 +56,7 @@ __device__ __forceinline__ void dm_bar_arrive_tx(uint64_t* bar, uint32_t bytes) 
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(dm_smem(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool dm_bar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = dm_smem(bar);
-  const long long start = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if ((i & 1023u) == 1023u && clock64() - start > DM_WAIT_CYCLES) return false;
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
-  }
+  return bounded_mbar_wait(dm_smem(bar), parity);
 }
 // One row of the cache (bytes a multiple of 16, both addresses 16-byte aligned) -> shared memory.
 __device__ __forceinline__ void dm_bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -135,6 +126,7 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_mma_kernel(AttnArgs a,
   auto load_tile = [&](int tile, int stage) {
     // lanes 0-15 fetch the 16 key rows of the tile, lanes 16-31 its value rows (or zero them
     // if the position lies outside the request's range)
+    if (wait_test_unarmed()) return;
     const int row = lane & 15;
     const int kpos = lo_al + tile * DM_TK + row;
     bf16* dst = my_k + (size_t)stage * 2 * TILE_ELEMS + (lane >> 4) * TILE_ELEMS + row * DS;
@@ -244,7 +236,7 @@ __global__ void __launch_bounds__(DM_THREADS) decode_attn_mma_kernel(AttnArgs a,
     const int nxt = tile + DM_STAGES * DM_WARPS;
     if (nxt < tile_end) load_tile(nxt, stage);
   }
-  if (failed && lane == 0) atomicExch(error_flag, 1);
+  if (failed && lane == 0) atomicExch(error_flag, WAIT_FAILED_DECODE_BULK);
 
   // ---- row sums across the quad; then merge the warps through shared memory
 #pragma unroll
@@ -329,7 +321,7 @@ extern "C" int ts_decode_attention_mma(
     float* part_acc, float* part_ml, int* error_flag, cudaStream_t stream) {
   if (num_decode <= 0) return 0;
   if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 128 || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
-  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || page_size <= 0 || window < 0 || num_splits < 1)
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || page_size <= 0 || window < 0 || num_splits < 1 || num_splits > ATTN_MAX_SPLITS)
     return TS_ERR_BAD_ARGUMENT;
   if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return TS_ERR_BAD_ARGUMENT;
   if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache)) & 15) return TS_ERR_UNSUPPORTED;

@@ -26,6 +26,7 @@
 #include <tuple>
 
 #include "attention.cuh"
+#include "bounded_wait.cuh"
 
 namespace ts {
 
@@ -34,7 +35,6 @@ namespace ts {
 #endif
 constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_TK = 16, DM_STAGES = DM_STAGES_N;
 constexpr int DM_MAX_COUNTERS = 1 << 16;
-constexpr long long DM_WAIT_CYCLES = 2000000000ll;
 
 static __device__ unsigned int g_dt_arrivals[DM_MAX_COUNTERS];
 
@@ -67,16 +67,7 @@ __device__ __forceinline__ void dm_bar_arrive_tx(uint64_t* bar, uint32_t bytes) 
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(dm_smem(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool dm_bar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = dm_smem(bar);
-  const long long start = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if ((i & 1023u) == 1023u && clock64() - start > DM_WAIT_CYCLES) return false;
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
-  }
+  return bounded_mbar_wait(dm_smem(bar), parity);
 }
 // A box of rows x 64 columns of the cache matrix -> shared memory, 128-byte swizzled.
 __device__ __forceinline__ void dm_tensor_copy(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -252,7 +243,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
   // One lane fetches a tile: the 16 positions from k0 lie in one page (BR = 16) or in two pages
   // of 8. Row of the cache matrix = (page * kv_heads + kvh) * page_size + offset in the page.
   auto load_tile = [&](int tile, int stage) {
-    if (lane != 0) return;
+    if (lane != 0 || wait_test_unarmed()) return;
     const int k0 = lo_al + tile * DM_TK;
     unsigned char* kd = my + (size_t)stage * 2 * TILE_BYTES;
     unsigned char* vd = kd + TILE_BYTES;
@@ -468,7 +459,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     const int nxt = tile + DM_STAGES * WARPS;
     if (nxt < tile_end) load_tile(nxt, stage);
   }
-  if (failed && lane == 0) atomicExch(error_flag, 1);
+  if (failed && lane == 0) atomicExch(error_flag, WAIT_FAILED_DECODE_TMA);
 
   // ---- row sums across the quad; then merge the warps through shared memory
 #pragma unroll
@@ -669,7 +660,7 @@ extern "C" int ts_decode_attention_tma(
   if (num_decode <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
   if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
-  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || num_splits < 1 || num_pages_total <= 0)
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || num_splits < 1 || num_splits > ATTN_MAX_SPLITS || num_pages_total <= 0)
     return TS_ERR_BAD_ARGUMENT;
   if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return TS_ERR_BAD_ARGUMENT;
   if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache)) & 15) return TS_ERR_UNSUPPORTED;
@@ -705,7 +696,7 @@ extern "C" int ts_decode_attention_tma_fused(
   if (num_decode <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
   if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
-  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || num_splits < 1 || num_pages_total <= 0)
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || num_splits < 1 || num_splits > ATTN_MAX_SPLITS || num_pages_total <= 0)
     return TS_ERR_BAD_ARGUMENT;
   if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr)) return TS_ERR_BAD_ARGUMENT;
   if ((cos_t == nullptr) != (sin_t == nullptr) || slots == nullptr || qkv == nullptr) return TS_ERR_BAD_ARGUMENT;

@@ -280,7 +280,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
     constexpr int PARTS = BN / BR;
     constexpr int COPIES = PARTS * D64;                         // per tile; one lane each, in rounds of 32
     const int kmin = lo & ~(BR - 1), kmax = (ctx - 1) & ~(BR - 1);
-    bool ok = true;
+    bool ok = !wait_test_unarmed();
     int issued_k = 0, issued_v = 0;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % FA_KV_STAGES;
@@ -407,7 +407,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       }
     }
   }
-  if (*failed && (threadIdx.x & 31) == 0) atomicExch(error_flag, 1);
+  if (*failed && (threadIdx.x & 31) == 0) atomicExch(error_flag, WAIT_FAILED_PREFILL_TCGEN05);
   tc_fence_before();
   __syncthreads();
   if (warp == FA_SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, L::TMEM_COLS);

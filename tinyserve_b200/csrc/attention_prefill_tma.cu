@@ -19,11 +19,11 @@
 #include <tuple>
 
 #include "attention.cuh"
+#include "bounded_wait.cuh"
 
 namespace ts {
 
 constexpr int PT_BM = 64, PT_BN = 32, PT_THREADS = 128, PT_STAGES = 2;
-constexpr long long PT_WAIT_CYCLES = 2000000000ll;
 
 __device__ __forceinline__ uint32_t pt_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void pt_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
@@ -51,16 +51,7 @@ __device__ __forceinline__ void pt_bar_arrive_tx(uint64_t* bar, uint32_t bytes) 
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pt_smem(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool pt_bar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = pt_smem(bar);
-  const long long start = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if ((i & 1023u) == 1023u && clock64() - start > PT_WAIT_CYCLES) return false;
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
-  }
+  return bounded_mbar_wait(pt_smem(bar), parity);
 }
 __device__ __forceinline__ void pt_tensor_copy(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
@@ -131,6 +122,7 @@ __global__ void __launch_bounds__(PT_THREADS, 4) prefill_attn_tma_kernel(const _
     const int num_tiles = (qpos_last - k_begin) / PT_BN + 1;
 
     auto load_tile = [&](int tile, int slot) {            // thread 0 only
+      if (wait_test_unarmed()) return;
       const int k0 = k_begin + tile * PT_BN;
       unsigned char* kd = KVs + (size_t)slot * 2 * KV_BYTES;
       unsigned char* vd = kd + KV_BYTES;
@@ -316,7 +308,7 @@ __global__ void __launch_bounds__(PT_THREADS, 4) prefill_attn_tma_kernel(const _
       }
     }
   }
-  if (failed && lane == 0) atomicExch(error_flag, 1);
+  if (failed && lane == 0) atomicExch(error_flag, WAIT_FAILED_PREFILL_TMA);
 }
 
 // ---------------------------------------------------------------- host side

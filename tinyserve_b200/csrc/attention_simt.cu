@@ -32,7 +32,7 @@ extern "C" int ts_paged_attention_simt(
     if (st != 0) return st;
   }
   if (num_decode > 0) {
-    if (num_splits < 1 || (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr))) return TS_ERR_BAD_ARGUMENT;
+    if (num_splits < 1 || num_splits > ATTN_MAX_SPLITS || (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr))) return TS_ERR_BAD_ARGUMENT;
     a.seq_ids = decode_seqs; a.num_seqs = num_decode;
     a.num_splits = num_splits; a.part_acc = part_acc; a.part_ml = part_ml;
     st = dtype == TS_DTYPE_F32 ? launch_decode<float>(a, stream) : launch_decode<bf16>(a, stream);

@@ -7,6 +7,8 @@
 
 #include "attention_simt.cuh"
 
+static_assert(TS_STATIC_SCRATCH_MAX_SPLITS == ts::ATTN_MAX_SPLITS, "the header states the launchers' limit");
+
 namespace {
 
 // Partial (max, sum, accumulator) of every key range. In host code this name is only a
@@ -50,7 +52,7 @@ extern "C" int ts_decode_attention_static_scratch(const void* q, void* out, cons
   using namespace ts;
   if (num_decode <= 0) return 0;
   if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256) return TS_ERR_UNSUPPORTED;
-  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || page_size <= 0 || window < 0 || num_splits < 1)
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || page_size <= 0 || window < 0 || num_splits < 1 || num_splits > ATTN_MAX_SPLITS)
     return TS_ERR_BAD_ARGUMENT;
   if (dtype != TS_DTYPE_F32 && dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
   const long long need = ts_decode_attention_static_scratch_need(num_decode, num_heads, head_dim, num_splits);

@@ -21,6 +21,9 @@
  *    overwrite every element they later read, so nothing needs clearing; but two calls that
  *    run on the GPU at the same time (different streams, no dependency) would race on it.
  *    Order them on one stream or with an event.
+ *  - num_splits is at most TS_STATIC_SCRATCH_MAX_SPLITS (32, the limit of every decode launcher of
+ *    the library: the merge of the ranges stages two floats per range and head in shared memory
+ *    sized for that many); more is refused with TS_ERR_BAD_ARGUMENT (-1) and launches nothing.
  *  - Neither this function nor anything it calls allocates or frees device memory.
  *
  * Arguments are those of ts_paged_attention_simt for the decoding requests: q and out are
@@ -34,6 +37,7 @@
 
 #define TS_STATIC_SCRATCH_FLOATS (2 * 1024 * 1024)
 #define TS_ERR_SCRATCH_TOO_SMALL (-3)
+#define TS_STATIC_SCRATCH_MAX_SPLITS 32
 
 #ifdef __cplusplus
 extern "C" {

@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
 
   if (warp == 0) {
     // ---------------- TMA producer (one lane)
-    if (lane == 0) {
+    if (lane == 0 && !wait_test_unarmed()) {
       // The weights do not depend on the kernel before this one: the B tiles of the first stages
       // are requested before the wait for it, the A tiles (its output) after.
       auto load_b = [&](int s, int kb, int n0) {
@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
       const int b = t & 1;
       const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN_OUT;
       if (!mbar_wait(&acc_full[b], (t >> 1) & 1) || failed) {
-        if (lane == 0) atomicExch(error_flag, 1);
+        if (lane == 0) atomicExch(error_flag, WAIT_FAILED_GEMM_TCGEN05);
         break;
       }
       tc_fence_after();

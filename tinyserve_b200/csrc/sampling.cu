@@ -154,13 +154,17 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
                                                             const float* __restrict__ top_p,
                                                             const long long* __restrict__ seeds,
                                                             const long long* __restrict__ draws,
-                                                            int* __restrict__ out, int chunks) {
+                                                            int* __restrict__ out, int chunks,
+                                                            const int* __restrict__ status_in,
+                                                            int* __restrict__ status_out) {
   __shared__ float fscratch[33];
   __shared__ Best bscratch[32];
   __shared__ int is_last;
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x, chunk = blockIdx.y;
+  // the step's error word (set by a kernel whose bounded wait ran out) travels to the host with the tokens
+  if (status_out != nullptr && row == 0 && chunk == 0 && threadIdx.x == 0) *status_out = status_in ? *status_in : 0;
   const float* l = logits + (size_t)row * vocab;
   const float temp = temperature ? temperature[row] : 0.f;
   const float tp = (top_p && temp > 0.f) ? top_p[row] : 1.f;
@@ -235,10 +239,12 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
 
 using namespace ts;
 
-// temperature/top_p/seeds/draws may all be null for an all-greedy batch.
+// temperature/top_p/seeds/draws may all be null for an all-greedy batch. status_out (optional)
+// receives *status_in (0 if that is null): the device word that kernels with bounded waits set
+// when a wait ran out, so that one copy brings the tokens and the step's status to the host.
 extern "C" int ts_sample(const float* logits, int num_rows, int vocab, const float* temperature,
                          const float* top_p, const long long* seeds, const long long* draws, int* out,
-                         cudaStream_t stream) {
+                         const int* status_in, int* status_out, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (vocab <= 0 || num_rows > SM_MAX_ROWS) return TS_ERR_BAD_ARGUMENT;
   if (temperature != nullptr && (seeds == nullptr || draws == nullptr)) return TS_ERR_BAD_ARGUMENT;
@@ -250,5 +256,5 @@ extern "C" int ts_sample(const float* logits, int num_rows, int vocab, const flo
   if (chunks > SM_MAX_CHUNKS) chunks = SM_MAX_CHUNKS;
   if (chunks < 1) chunks = 1;
   return launch(sample_kernel, dim3(num_rows, chunks), SM_THREADS, 0, stream, logits, vocab, temperature, top_p,
-                seeds, draws, out, chunks);
+                seeds, draws, out, chunks, status_in, status_out);
 }

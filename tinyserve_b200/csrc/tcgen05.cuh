@@ -4,11 +4,10 @@
 #pragma once
 #include <cuda.h>
 
+#include "bounded_wait.cuh"
 #include "common.cuh"
 
 namespace ts {
-
-constexpr long long TG_WAIT_CYCLES = 2000000000ll;   // about a second: far beyond any real wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -23,21 +22,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 }
 // Bounded wait for the phase with the given parity. Returns false if the bound was hit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  const long long start = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if ((i & 1023u) == 1023u && clock64() - start > TG_WAIT_CYCLES) break;
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  return false;
+  return bounded_mbar_wait(smem_u32(bar), parity);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
@@ -116,6 +101,7 @@ __device__ __forceinline__ uint64_t sw128_desc_mn(uint32_t smem_addr, uint32_t c
 __device__ __forceinline__ bool mbar_wait_or_fail(uint64_t* bar, uint32_t parity, volatile int* failed) {
   const uint32_t addr = smem_u32(bar);
   const long long start = clock64();
+  const long long limit = wait_cycles();
   for (uint32_t i = 0;; ++i) {
     uint32_t ok;
     asm volatile(
@@ -126,9 +112,9 @@ __device__ __forceinline__ bool mbar_wait_or_fail(uint64_t* bar, uint32_t parity
         "}\n"
         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
     if (ok) return true;
-    if ((i & 255u) == 255u) {
+    if ((i & 63u) == 63u) {
       if (*failed) return false;
-      if (clock64() - start > TG_WAIT_CYCLES) { *failed = 1; return false; }
+      if (clock64() - start > limit) { *failed = 1; return false; }
     }
   }
 }

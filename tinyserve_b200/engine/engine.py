@@ -81,7 +81,8 @@ class Engine:
                  max_batch_tokens: int = 2048, clock: Callable[[], float] = time.perf_counter,
                  seed: int = 0, trace_steps: bool = False, chunked_prefill: bool = False,
                  runner: ModelRunner | None = None, decode_graphs: bool = False,
-                 graph_max_context: int | None = None, run_ahead: bool = True, prefill_graph: bool = True) -> None:
+                 graph_max_context: int | None = None, run_ahead: bool = True, prefill_graph: bool = True,
+                 record_logits: bool = False) -> None:
         """``decode_graphs``: record the decode step once per batch-size bucket (CUDA graphs)
         and replay it whenever every scheduled request brings one token (upstream passes a
         ``DecodeGraphs`` object for this, src/tinyserve/engine.py:96,188-196).
@@ -95,7 +96,11 @@ class Engine:
         leaves the device idle. It happens only when nothing about the next step depends on
         those tokens (see ``Scheduler.schedule_ahead``) except a possible end token: a request
         that draws one has then run one token too many, which is dropped. ``step()`` still
-        returns one step's finished requests per call, in order."""
+        returns one step's finished requests per call, in order.
+
+        ``record_logits`` (tests, debugging): every step's logits rows are copied on the device as
+        the step is launched and kept in ``logits_log`` as ``(request id, position, row)``: the
+        float32 logits that predict the token after ``position`` of that request's tokens."""
         self.model = model
         self.cache = cache
         self.runner = runner if runner is not None else ModelRunner(model, cache)
@@ -119,6 +124,7 @@ class Engine:
         self.run_ahead = run_ahead and trace_steps is False
         self.num_steps_ahead = 0
         self._inflight: _StepInFlight | None = None
+        self.logits_log: list[tuple[int, int, torch.Tensor]] | None = [] if record_logits else None
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], max_new_tokens: int,
@@ -187,6 +193,9 @@ class Engine:
             logits = self.runner.step(entries, want)
         self._mark(marks)
         sampled = reqs if ahead is not None else [r for r in reqs if not r.in_prefill()]
+        if self.logits_log is not None and sampled:
+            rows = logits[: len(sampled)].clone()      # a step launched ahead reuses the buffer before this one is read
+            self.logits_log.extend((r.request_id, r.cache.num_tokens - 1, rows[j]) for j, r in enumerate(sampled))
         ticket = None
         if sampled:
             drawn = 1 if ahead is not None else 0        # the token under way counts as drawn

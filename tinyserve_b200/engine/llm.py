@@ -35,7 +35,7 @@ class LLM:
                  kv_fraction: float = 0.85, max_num_seqs: int = 64, max_batch_tokens: int = 2048,
                  chunked_prefill: bool = False, seed: int = 0, trace_steps: bool = False,
                  decode_graphs: bool = True, graph_max_context: int | None = None, run_ahead: bool = True,
-                 prefill_graph: bool = True) -> None:
+                 prefill_graph: bool = True, record_logits: bool = False) -> None:
         """``num_pages``: size of every page pool; by default the pools together take
         ``kv_fraction`` of the device memory that is free once the weights are loaded."""
         self.model = model
@@ -56,7 +56,8 @@ class LLM:
         self.engine = Engine(model, self.cache, max_num_seqs=max_num_seqs, max_batch_tokens=max_batch_tokens,
                              chunked_prefill=chunked_prefill, seed=seed, trace_steps=trace_steps,
                              decode_graphs=decode_graphs and model.device.type == "cuda",
-                             graph_max_context=graph_max_context, run_ahead=run_ahead, prefill_graph=prefill_graph)
+                             graph_max_context=graph_max_context, run_ahead=run_ahead, prefill_graph=prefill_graph,
+                             record_logits=record_logits)
 
     @classmethod
     def from_folder(cls, model_dir: str | Path, dtype: str | torch.dtype = "bfloat16", device: str = "cuda",

@@ -15,6 +15,7 @@ import torch
 
 from ..cache.manager import CacheManager, RequestCache
 from ..model import DecoderModel
+from ..kernels import ops
 from .step import ModelRunner, StepEntry
 
 DEFAULT_PAGE_SIZE = 16
@@ -60,6 +61,8 @@ class Replayer:
             step_entries.append(StepEntry(req, list(tokens)))
             want.append(list(places))
         logits = self.runner.step(step_entries, want) if step_entries else None
+        if self.model.device.type == "cuda":
+            ops.check_device_errors()      # a kernel that gave up on a bounded wait: raise, never hand back its logits
         for req in {id(e.cache): e.cache for e in step_entries}.values():
             self.cache.release_passed(req)
         for rid in end:

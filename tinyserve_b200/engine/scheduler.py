@@ -93,7 +93,8 @@ class Scheduler:
         while queue:
             req = queue.popleft()
             n = req.num_pending()
-            if n > 1:
+            mid_prompt = n > 1          # not counted among the one-token requests when the budget was formed
+            if mid_prompt:
                 n = min(n, max(budget, 0))
             fits = True
             while n > 0 and self.cache.pages_short(req.cache, n):
@@ -113,8 +114,8 @@ class Scheduler:
             self.cache.append(req.cache, n)
             req.num_scheduled = n
             self.running.append(req)
-            if n > 1:
-                budget -= n
+            if mid_prompt:
+                budget -= n             # also when the portion was cut down to a single token
 
     def _admit_waiting(self) -> None:
         budget = self.max_batch_tokens - sum(r.num_scheduled for r in self.running)

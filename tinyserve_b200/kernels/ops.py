@@ -55,7 +55,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_gemm_tcgen05_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp, _vp],
-    "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _fns: dict[str, Any] = {}
 
@@ -114,6 +114,8 @@ def _check(status: int, name: str, kernels: int = 1) -> None:
         raise KernelError(f"{name}: bad argument")
     if status == -2:
         raise KernelError(f"{name}: size not supported by this kernel")
+    if status == -3:
+        raise KernelError(f"{name}: the job needs more scratch than the library's fixed array holds")
     raise KernelError(f"{name}: CUDA error {status}")
 
 
@@ -543,12 +545,40 @@ def _error_word(device: torch.device) -> torch.Tensor:
     return w
 
 
+# What a non-zero error word says (csrc/bounded_wait.cuh).
+WAIT_FAILURES = {1: "gemm_tcgen05", 2: "prefill_attention_tcgen05", 3: "prefill_attention_tma",
+                 4: "decode_attention_tma", 5: "decode_attention_mma"}
+
+
+def raise_for_status(code: int, device: torch.device | str | None = None) -> None:
+    """Raise ``KernelError`` for a non-zero error word read from the device (and clear the word, so
+    that the next step starts clean)."""
+    if code == 0:
+        return
+    for dev, w in _error_words.items():
+        if device is None or torch.device(device) == dev:
+            w.zero_()
+    raise KernelError(f"kernel {WAIT_FAILURES.get(code, code)!r} gave up waiting on its pipeline (a bounded wait "
+                      f"ran out): this step's results are not valid")
+
+
 def check_device_errors() -> None:
     """Raise if a kernel gave up on a bounded wait since the last check (synchronises)."""
     for dev, w in _error_words.items():
-        if int(w.item()) != 0:
-            w.zero_()
-            raise KernelError(f"a kernel on {dev} gave up waiting on its pipeline (bounded wait ran out)")
+        raise_for_status(int(w.item()), dev)
+
+
+def set_wait_control(cycles: int | None = None, unarmed: bool = False) -> None:
+    """How long the kernels' mbarrier waits may last, in clock cycles (``None``: the default, about a
+    second), and the test switch ``unarmed`` that makes every kernel skip its copies so that its
+    waits run out (``csrc/bounded_wait.cuh``). For the current device; call it with nothing in
+    flight, and never with ``unarmed`` outside a test."""
+    lib = build.library()
+    lib.ts_set_wait_control.argtypes = [_c.c_longlong, _i]
+    lib.ts_set_wait_control.restype = _i
+    status = lib.ts_set_wait_control(int(cycles or 0), int(bool(unarmed)))
+    if status != 0:
+        raise KernelError(f"set_wait_control: CUDA error {status}")
 
 
 # Default output-tile width of the tcgen05 product.
@@ -760,14 +790,18 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 # --------------------------------------------------------------------- sampling
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor | None = None,
            top_p: torch.Tensor | None = None, seeds: torch.Tensor | None = None,
-           draws: torch.Tensor | None = None) -> None:
+           draws: torch.Tensor | None = None, status_out: torch.Tensor | None = None) -> None:
     """One token per row of ``logits`` ``[R, V]`` float32 into ``out`` ``[R]`` int32. With no
     ``temperature`` every row is greedy; else rows with temperature 0 are greedy and the others
     are drawn (``seeds``/``draws`` int64 ``[R]``: the request's seed and how many tokens it
-    has drawn so far; ``top_p`` float32 ``[R]`` optional)."""
+    has drawn so far; ``top_p`` float32 ``[R]`` optional). ``status_out`` (int32, one element):
+    receives the device's error word, which kernels with bounded waits set when a wait ran out,
+    so that it reaches the host in the same copy as the tokens."""
     r, v = logits.shape
     if out.shape != (r,):
         raise KernelError("sample: one output per row")
     _check(_fn("ts_sample")(_dev(logits, "logits", torch.float32), r, v, _opt(temperature, "temperature", torch.float32),
                             _opt(top_p, "top_p", torch.float32), _opt(seeds, "seeds", torch.int64),
-                            _opt(draws, "draws", torch.int64), _dev(out, "out", torch.int32), _stream()), "sample")
+                            _opt(draws, "draws", torch.int64), _dev(out, "out", torch.int32),
+                            None if status_out is None else _error_word(logits.device).data_ptr(),
+                            _opt(status_out, "status_out", torch.int32), _stream()), "sample")

@@ -47,10 +47,15 @@ class SampleTicket:
         self._tokens: list[int] | None = None
 
     def wait(self) -> list[int]:
+        """The tokens; raises ``KernelError`` if a kernel of the step gave up on a bounded wait (the
+        device's error word arrives in the same copy, in front of the tokens)."""
         if self._tokens is None:
             if self._event is not None:
                 self._event.synchronize()
-            self._tokens = self._host[: self._rows].tolist()
+            got = self._host[: self._rows + 1].tolist()
+            self._tokens = got[1:]
+            if got[0] != 0:
+                ops.raise_for_status(got[0], self.device_tokens.device)
         return self._tokens
 
 
@@ -61,7 +66,7 @@ class _Staging:
     def __init__(self, max_rows: int, pin: bool) -> None:
         self.f_host = torch.empty(2 * max_rows, dtype=torch.float32, pin_memory=pin)
         self.i_host = torch.empty(2 * max_rows, dtype=torch.int64, pin_memory=pin)
-        self.out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=pin)
+        self.out_host = torch.zeros(max_rows + 1, dtype=torch.int32, pin_memory=pin)    # status, then the tokens
         self.event = torch.cuda.Event() if pin else None
         self.ticket: SampleTicket | None = None
 
@@ -77,7 +82,7 @@ class Sampler:
         self._turn = 0
         self._f_dev = torch.empty(2 * max_rows, dtype=torch.float32, device=self.device)
         self._i_dev = torch.empty(2 * max_rows, dtype=torch.int64, device=self.device)
-        self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
+        self._out = torch.zeros(max_rows + 1, dtype=torch.int32, device=self.device)    # status, then the tokens
 
     def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                draws: Sequence[int]) -> SampleTicket:
@@ -93,9 +98,9 @@ class Sampler:
         self._turn ^= 1
         if st.ticket is not None:
             st.ticket.wait()               # the launch that used these buffers last has been read
-        out = self._out[:r]
+        out, status = self._out[1: r + 1], self._out[:1]
         if all(p.greedy for p in params):
-            ops.sample(logits, out)
+            ops.sample(logits, out, status_out=status)
         else:
             f, i = st.f_host, st.i_host
             f[:r] = torch.tensor([p.temperature for p in params], dtype=torch.float32)
@@ -105,8 +110,8 @@ class Sampler:
             self._f_dev[: 2 * r].copy_(f[: 2 * r], non_blocking=True)
             self._i_dev[: 2 * r].copy_(i[: 2 * r], non_blocking=True)
             top_p = self._f_dev[r: 2 * r] if any(p.top_p < 1 for p in params) else None
-            ops.sample(logits, out, self._f_dev[:r], top_p, self._i_dev[:r], self._i_dev[r: 2 * r])
-        st.out_host[:r].copy_(out, non_blocking=True)
+            ops.sample(logits, out, self._f_dev[:r], top_p, self._i_dev[:r], self._i_dev[r: 2 * r], status_out=status)
+        st.out_host[: r + 1].copy_(self._out[: r + 1], non_blocking=True)
         if st.event is not None:
             st.event.record()
         st.ticket = SampleTicket(out, st.out_host, st.event, r)
