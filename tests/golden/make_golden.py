@@ -8,9 +8,10 @@ Upstream's package asks ``importlib.metadata`` for its installed version
 (src/tinyserve/__init__.py:3-5); it is not installed here, so that one lookup is answered
 with a constant. Nothing else of upstream is altered. For each tiny model the script writes
 ``tiny_<name>.safetensors`` holding the token ids, upstream's ``Qwen3.forward`` logits
-``[T, vocab]`` float32, and a checksum of the weights (so that a test can tell a changed
-random generator from a wrong formula). The weights themselves are re-made by the tests from
-the same seed.
+``[T, vocab]`` float32, the model's weights themselves (``w.<tensor name>``, float32: a few
+hundred KB), and their checksum. A test re-makes the weights from the same seed; if this torch
+build draws the same values it uses those (which also pins the random-weights mode), otherwise it
+falls back on the stored ones, so the comparison with upstream's logits always runs.
 """
 
 from __future__ import annotations
@@ -23,6 +24,7 @@ import tempfile
 from pathlib import Path
 
 import torch
+from safetensors import safe_open
 from safetensors.torch import save_file
 
 HERE = Path(__file__).resolve().parent
@@ -64,8 +66,12 @@ def main() -> None:
             ids = random_prompt(PROMPT_LEN[name], cfg_dict["vocab_size"], 100 + seed)
             logits = model.forward(torch.tensor(ids))
             digest = weights_checksum(folder)
+            stored = {}
+            with safe_open(str(folder / "model.safetensors"), framework="pt", device="cpu") as f:
+                for tensor_name in f.keys():
+                    stored["w." + tensor_name] = f.get_tensor(tensor_name).float().contiguous()
         save_file(
-            {"token_ids": torch.tensor(ids, dtype=torch.int32), "logits": logits.float().contiguous()},
+            {"token_ids": torch.tensor(ids, dtype=torch.int32), "logits": logits.float().contiguous(), **stored},
             str(HERE / f"tiny_{name}.safetensors"),
             metadata={"weights_sha256": digest, "seed": str(seed), "source": "upstream Qwen3.forward, float32, CPU"},
         )

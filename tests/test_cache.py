@@ -96,7 +96,7 @@ def test_groups_by_need_and_layout() -> None:
     assert [g.calls for g in c.groups] == [[0, 2], [1], [5]]
     assert c.groups[0].kv.shape == (2, 2, 11, 2, 4, 16)           # calls, k/v, pages + pad, heads, page, dim
     assert c.entries[2].k.data_ptr() == c.groups[0].kv[1, 0].data_ptr()
-    assert c.entries[3].state.shape == (3, 3, 4) and c.entries[4] is None
+    assert c.entries[3].state.shape == (3 + 1, 3, 4) and c.entries[4] is None     # one pad slot after the pool
     r = c.new_request()
     assert r.state_slot == 0 and len(r.tables) == 3
 
@@ -159,3 +159,46 @@ def test_random_orders_of_requests_leak_nothing(seed) -> None:
     for r in live:
         c.free(r)
     assert all(g.allocator.num_free == g.num_pages for g in c.groups) and c.state_pool.num_free == 5
+
+
+def test_a_need_of_another_kind_and_pools_of_different_sizes() -> None:
+    """A paged need defined outside the package gets a group, storage and entries of its own
+    through its own methods; pools may differ in size group by group; a window group is sized by
+    what the requests can hold of it; and a request is refused by what it can ever hold per
+    group."""
+    from dataclasses import dataclass
+
+    from tinyserve_b200.parts.base import PagedNeed
+
+    @dataclass(frozen=True)
+    class OneVector(PagedNeed):
+        width: int
+        window: int | None = None
+
+        def bytes_per_token(self, element_size):
+            return self.width * element_size
+
+        def allocate(self, num_calls, num_pages, page_size, dtype, device):
+            return torch.zeros(num_calls, num_pages, page_size, self.width, dtype=dtype, device=device)
+
+        def entry(self, storage, call_in_group, group, page_size):
+            return ("mine", group, storage[call_in_group])
+
+    needs = [KVNeed(2, 16), OneVector(24), KVNeed(2, 16, 8), OneVector(24), None]
+    c = CacheManager(needs, page_size=4, num_pages=[10, 6, 7], max_requests=3, dtype=torch.float32, device="cpu")
+    assert [(g.calls, g.num_pages) for g in c.groups] == [([0], 10), ([1, 3], 6), ([2], 7)]
+    assert c.groups[1].kv.shape == (2, 7, 4, 24) and c.entries[3][0] == "mine" and c.entries[3][2].shape == (7, 4, 24)
+    assert CacheManager.bytes_per_token(needs, 2) == 2 * (2 * 2 * 16 * 2) + 2 * 24 * 2
+    assert c.memory_bytes() == sum(g.kv.numel() * 4 for g in c.groups)
+    assert c.capacity_tokens == 6 * 4
+    assert c.can_ever_hold(24, 8) and not c.can_ever_hold(25, 8)          # the smallest full group decides
+    # one number for all, and the step's token budget known: the window group shrinks to what
+    # max_requests requests can hold of it (window 8 + 8 new tokens on pages of 4, one page of slack)
+    c = CacheManager(needs, page_size=4, num_pages=100, max_requests=3, dtype=torch.float32, device="cpu",
+                     allocate_memory=False, max_step_tokens=8)
+    assert [g.num_pages for g in c.groups] == [100, 100, 3 * 5]
+    r = c.new_request()
+    c.append(r, 8)
+    assert [t.num_tokens for t in r.tables] == [8, 8, 8]
+    with pytest.raises(TypeError, match="neither a PagedNeed nor a SlotNeed"):
+        CacheManager([object()], page_size=4, num_pages=4, max_requests=1, dtype=torch.float32, device="cpu")

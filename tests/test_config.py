@@ -62,7 +62,8 @@ def test_round_trip_and_spec(tmp_path) -> None:
     assert load_config(tmp_path) == c
     spec = c.to_spec()
     assert len(spec.layers) == 3 and [x.layer for x in spec.order] == [0, 1, 2]
-    a = spec.layers[0].mixer.args
+    assert set(spec.layers[0].parts) == {"mixer", "feed_forward", "mixer_norm", "feed_forward_norm"}
+    a = spec.layers[0].parts["mixer"].args
     assert a["scale"] == 32 ** -0.5 and a["qk_norm"] and a["qk_norm_eps"] == 1e-5 and a["window"] is None
     assert spec.layers[0].position.args["theta"] == 1e6
     assert spec.head.args["tied"] is False and spec.head.args["name"] == "lm_head.weight"
@@ -82,3 +83,15 @@ def test_registry_takes_another_architecture() -> None:
     assert isinstance(config_from_dict({"architectures": ["OtherForCausalLM"]}), Other)
     with pytest.raises(ValueError):
         register_architecture("OtherForCausalLM", Qwen3Config)
+
+
+def test_a_head_size_the_kernels_do_not_take_is_refused_when_the_model_is_built() -> None:
+    """head_dim 40 is a legal Qwen3 config.json (even, so rotary pairs exist), but the attention
+    kernels take head sizes in steps of 16 up to 256: the parts say so when they are built, before
+    any weight is loaded or any cache allocated."""
+    from tinyserve_b200.model import build_parts
+
+    c = config_from_dict({**TINY_A, "head_dim": 40})
+    with pytest.raises(ValueError, match="head_dim=40.*steps of 16"):
+        build_parts(c.to_spec())
+    build_parts(config_from_dict({**TINY_A, "head_dim": 48}).to_spec())

@@ -9,6 +9,7 @@ from pathlib import Path
 import pytest
 import torch
 from safetensors import safe_open
+from safetensors.torch import save_file
 
 import plain_qwen3 as plain
 from golden.make_golden import weights_checksum
@@ -19,15 +20,33 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 
 @pytest.mark.parametrize("name", sorted(TINIES))
 def test_plain_matches_upstream_logits(name: str, tmp_path: Path) -> None:
+    """The golden file holds upstream's own logits AND the weights they were made with. The
+    weights are re-made here from the same seed; should this torch build draw other values, the
+    stored ones take their place, so the formulas are always held against upstream's output."""
     with safe_open(str(GOLDEN / f"tiny_{name}.safetensors"), framework="pt", device="cpu") as f:
         ids = f.get_tensor("token_ids").tolist()
         want = f.get_tensor("logits")
         digest = f.metadata()["weights_sha256"]
+        stored = {k[2:]: f.get_tensor(k) for k in f.keys() if k.startswith("w.")}
+    assert stored, "the golden file holds no weights: make it again with tests/golden/make_golden.py"
     folder = write_tiny(tmp_path, name, torch.float32)
     if weights_checksum(folder) != digest:
-        pytest.skip("this torch build draws other random weights than the golden file was made with")
+        save_file(stored, str(folder / "model.safetensors"))       # same config.json, upstream's weights
+        assert weights_checksum(folder) == digest
     got = plain.forward_folder(folder, ids, torch.float32)
     torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+
+
+def test_stored_golden_weights_alone_reproduce_upstream_logits(tmp_path: Path) -> None:
+    """The fallback of the test above, exercised: the weights stored in the golden file, without
+    the random-weights mode."""
+    name = "A"
+    with safe_open(str(GOLDEN / f"tiny_{name}.safetensors"), framework="pt", device="cpu") as f:
+        ids, want = f.get_tensor("token_ids").tolist(), f.get_tensor("logits")
+        stored = {k[2:]: f.get_tensor(k) for k in f.keys() if k.startswith("w.")}
+    folder = write_tiny(tmp_path, name, torch.float32)
+    save_file(stored, str(folder / "model.safetensors"))
+    torch.testing.assert_close(plain.forward_folder(folder, ids, torch.float32), want, atol=1e-5, rtol=1e-5)
 
 
 def test_rms_norm_by_hand() -> None:

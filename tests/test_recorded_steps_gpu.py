@@ -273,3 +273,43 @@ def test_engine_with_recorded_steps_launched_ahead(real, ahead) -> None:
         pick = sorted({0, 1, len(places) // 2, len(places) - 1})
         at = [places[i] for i in pick]
         close_enough(rows[pick], plain_rows(pcfg, w32, seq, at), plain_rows(pcfg, w16, seq, at), torch.bfloat16)
+
+
+def test_a_row_at_eight_and_at_nine_rows(real) -> None:
+    """Up to 8 rows the RMSNorm is folded into the products around it (the product reads a bf16 copy
+    of the stream, multiplies by the norm weight and scales the finished sums by rstd), from 9 rows
+    on it is a kernel of its own (norm, cast, times weight, as upstream rounds): the rounding points
+    differ, so a request's logits depend, within bf16 rounding, on the batch-size bucket it runs
+    in. Both must be as close to the oracle as the plain implementation's own bf16 run, and their
+    difference is bounded by that run's error."""
+    from tinyserve_b200.engine.step import StepEntry
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.model import DecoderModel
+
+    _, pcfg, w32, w16 = real
+    model = DecoderModel.from_folder(real[0], torch.bfloat16, "cuda")
+    fleet = Fleet(model, buckets=[8, 16])
+    ids = [fleet.admit(60 + 11 * i) for i in range(9)]
+    entries = []
+    for rid in ids:
+        fleet.cache.append(fleet.caches[rid], 1)
+        entries.append(StepEntry(fleet.caches[rid], [fleet.tokens[rid][-1]]))
+    normed = []
+    real_normed = ops.gemm_normed
+    ops.gemm_normed = lambda *a, **k: (normed.append(a[0].shape[0]), real_normed(*a, **k))[1]
+    try:
+        saved, fleet.runner.graphs = fleet.runner.graphs, {}      # kernel by kernel, so that the calls can be seen
+        at8 = fleet.runner.step(entries[:8]).float().cpu()
+        seen8 = list(normed)
+        at9 = fleet.runner.step(entries).float().cpu()
+        fleet.runner.graphs = saved
+    finally:
+        ops.gemm_normed = real_normed
+    assert seen8 and len(normed) == len(seen8), "8 rows fold the norms into the products, 9 rows do not"
+    for j, rid in enumerate(ids[:8]):
+        toks = fleet.tokens[rid]
+        want32, want16 = plain_rows(pcfg, w32, toks, [len(toks) - 1]), plain_rows(pcfg, w16, toks, [len(toks) - 1])
+        close_enough(at8[j: j + 1], want32, want16, torch.bfloat16)
+        close_enough(at9[j: j + 1], want32, want16, torch.bfloat16)
+        between = float((at8[j] - at9[j]).pow(2).mean().sqrt())
+        assert between <= 1.25 * float((want16 - want32).pow(2).mean().sqrt()) + 1e-3

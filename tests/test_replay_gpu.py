@@ -23,24 +23,7 @@ ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"A": [5, 17, 33, 70, 130], "B": [1, 9, 24, 40, 63, 97], "C": [3, 50, 31, 64]}
 
 
-FP32_TOL = {"atol": 3e-5, "rtol": 3e-5}    # sums in another order than the CPU's
-
-
-def close_enough(rows: torch.Tensor, want32: torch.Tensor, want16: torch.Tensor | None, dtype: torch.dtype) -> None:
-    """float32: equal to the plain implementation up to summation order. bfloat16: the error
-    against the 32-bit oracle is measured against the error that the plain implementation
-    itself makes when it runs in bfloat16 with upstream's rounding points; the engine may not
-    be worse than that by more than a quarter in the root mean square, nor by more than twice
-    at the worst logit."""
-    if dtype == torch.float32:
-        torch.testing.assert_close(rows, want32, **FP32_TOL)
-        return
-    err = (rows - want32).abs()
-    ref = (want16 - want32).abs()
-    rms, ref_rms = float(err.pow(2).mean().sqrt()), float(ref.pow(2).mean().sqrt())
-    assert rms <= 1.25 * ref_rms + 1e-3, f"rms error {rms:.4f} against {ref_rms:.4f} of plain bfloat16"
-    assert float(err.max()) <= 2.0 * float(ref.max()) + 1e-2, \
-        f"worst error {float(err.max()):.4f} against {float(ref.max()):.4f} of plain bfloat16"
+from closeness import FP32_TOL, close_enough  # noqa: E402,F401  (re-exported to the other GPU tests)
 
 
 def run_steps(model, page: int, steps, max_tokens: int):

@@ -146,20 +146,20 @@ class Qwen3Config(ModelConfig):
             layers.append(LayerSpec(
                 prefix=f"model.layers.{i}.",
                 block="prenorm",
-                mixer=PartSpec("gqa_attention", {
+                parts={"mixer": PartSpec("gqa_attention", {
                     "prefix": "self_attn.", "hidden_size": h, "num_heads": self.num_heads,
                     "num_kv_heads": self.num_kv_heads, "head_dim": d, "scale": d ** -0.5,
                     "qk_norm": True, "qk_norm_eps": self.rms_norm_eps, "window": None,
                 }),
-                feed_forward=PartSpec("swiglu", {
+                "feed_forward": PartSpec("swiglu", {
                     "prefix": "mlp.", "hidden_size": h,
                     "intermediate_size": self.intermediate_size,
                 }),
-                mixer_norm=PartSpec("rms_norm", {
+                "mixer_norm": PartSpec("rms_norm", {
                     "name": "input_layernorm.weight", "size": h, "eps": self.rms_norm_eps}),
-                feed_forward_norm=PartSpec("rms_norm", {
+                "feed_forward_norm": PartSpec("rms_norm", {
                     "name": "post_attention_layernorm.weight", "size": h,
-                    "eps": self.rms_norm_eps}),
+                    "eps": self.rms_norm_eps})},
                 position=rope,
             ))
         return ModelSpec(

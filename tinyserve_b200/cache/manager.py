@@ -1,11 +1,17 @@
 """The cache manager: page pools for keys and values, and slots for fixed-size state.
 
-The model reports, per call of its run order, what that call keeps between steps
-(``KVNeed``, ``StateNeed`` or nothing). Calls with the same need share a **page group**:
-one pool of pages, one allocator and, per request, one block table. Groups with different
-needs (all positions, a window of them, another head layout) have pages of their own, so a
-window group can give pages back early without disturbing the others. Every call of a group
-has its own key and value tensors, indexed by the group's page ids:
+The model reports, per cache user (a call of its run order and a mixer of that call's block),
+what it keeps between steps: a ``PagedNeed``, a ``SlotNeed`` or nothing (``parts.base``). The
+manager serves the two families through their own methods (``allocate``, ``entry``,
+``bytes_per_token``), so a need of a new shape is a new subclass and no change here.
+
+Users with equal paged needs share a **page group**: one pool of pages, one allocator and, per
+request, one block table. Groups with different needs (all positions, a window of them, another
+layout) have pages of their own, so a window group can give pages back early without disturbing
+the others, and a pool of its own size: a request never holds more pages of a window group than
+its window and one step's tokens cover, so such a group is given only as many pages as
+``max_requests`` requests can hold at once (when the step's token budget is known). Every user of
+a group has its own part of the group's storage, indexed by the group's page ids; for ``KVNeed``
 
     kv[call_in_group, 0 = keys / 1 = values, page, kv_head, offset_in_page, head_dim]
 
@@ -13,9 +19,10 @@ so the keys of one (page, kv head) are one contiguous run of ``page_size * head_
 elements. One extra page after the pool (``pad_page``) is never handed out; fixed-shape
 padding rows may write there.
 
-Requests that hold fixed-size state get one slot id from ``StatePool``; every call with a
-``StateNeed`` has a tensor ``[slots, *shape]`` indexed by it, zeroed when the slot is
-handed out. An architecture without such calls has an empty pool.
+Requests that hold fixed-size state get one slot id from ``StatePool``; every user with a
+``SlotNeed`` has storage ``[slots + 1, ...]`` indexed by it, zeroed when the slot is handed out
+(the last row is the pad slot for padding rows). An architecture without such users has an empty
+pool.
 
 Upstream has one group and no state (src/tinyserve/kv_cache.py:21-50,
 src/tinyserve/block_table.py); groups and slots are this framework's own.
@@ -27,7 +34,9 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..parts.base import KVCacheEntry, KVNeed, StateCacheEntry, StateNeed
+from typing import Any, Sequence
+
+from ..parts.base import CacheNeed, PagedNeed, SlotNeed
 from .allocator import OutOfPagesError, PageAllocator
 from .block_table import BlockTable
 
@@ -39,24 +48,35 @@ class OutOfSlotsError(RuntimeError):
 @dataclass
 class PageGroup:
     index: int
-    need: KVNeed
+    need: PagedNeed
     page_size: int
     num_pages: int
     calls: list[int]
     allocator: PageAllocator
-    kv: torch.Tensor | None = None     # [calls, 2, pages + 1, kv_heads, page_size, head_dim]
+    kv: torch.Tensor | None = None     # the need's storage; KVNeed: [calls, 2, pages + 1, kv_heads, page_size, head_dim]
 
     @property
     def pad_page(self) -> int:
         return self.num_pages
 
     def bytes_per_page(self, element_size: int) -> int:
-        return 2 * len(self.calls) * self.need.num_kv_heads * self.page_size * self.need.head_dim * element_size
+        return len(self.calls) * self.need.bytes_per_token(element_size) * self.page_size
+
+    def most_pages_of(self, num_tokens: int, step_tokens: int) -> int:
+        """The most pages of this group that a request of up to ``num_tokens`` tokens ever holds
+        at one time when a step brings it at most ``step_tokens`` tokens: all of its pages, or,
+        with a window, those that the window and one step's tokens cover (before the pages the
+        window has passed are given back after the step)."""
+        pages = -(-num_tokens // self.page_size)
+        if self.need.window is not None:
+            pages = min(pages, -(-(self.need.window + min(step_tokens, num_tokens)) // self.page_size) + 1)
+        return pages
 
 
 class StatePool:
     def __init__(self, num_slots: int) -> None:
         self.num_slots = num_slots
+        self.pad_slot = num_slots        # a row after the pool, never handed out
         self._free = list(range(num_slots - 1, -1, -1))
         self._used: set[int] = set()
 
@@ -90,59 +110,81 @@ class RequestCache:
 
 
 class CacheManager:
-    def __init__(self, needs: list[KVNeed | StateNeed | None], *, page_size: int, num_pages: int,
+    def __init__(self, needs: Sequence[CacheNeed | None], *, page_size: int, num_pages: int | Sequence[int],
                  max_requests: int, dtype: torch.dtype, device: torch.device | str,
-                 allocate_memory: bool = True) -> None:
-        """``needs`` has one entry per call of the model's run order. ``num_pages`` is the
-        size of every page group's pool. ``allocate_memory=False`` keeps the bookkeeping
-        only (host-side tests, schedulers driven by a fake model)."""
+                 allocate_memory: bool = True, max_step_tokens: int | None = None) -> None:
+        """``needs`` has one entry per cache user of the model (``DecoderModel.cache_needs``).
+        ``num_pages``: the size of a page pool; one number for all groups, or one per group in the
+        order in which their needs first appear (``distinct_paged_needs``). With one number and
+        ``max_step_tokens`` (the most tokens a step brings one request) given, a window group gets
+        no more pages than ``max_requests`` requests can hold of it. ``allocate_memory=False`` keeps
+        the bookkeeping only (host-side tests, schedulers driven by a fake model)."""
         if page_size <= 0:
             raise ValueError(f"page_size must be positive, got {page_size}")
-        self.page_size, self.num_pages = page_size, num_pages
+        distinct = self.distinct_paged_needs(needs)
+        if isinstance(num_pages, int):
+            sizes = [num_pages] * len(distinct)
+            if max_step_tokens is not None:
+                for i, need in enumerate(distinct):
+                    if need.window is not None:
+                        per_request = -(-(need.window + max_step_tokens) // page_size) + 1
+                        sizes[i] = min(num_pages, max_requests * per_request)
+        else:
+            sizes = [int(n) for n in num_pages]
+            if len(sizes) != len(distinct):
+                raise ValueError(f"{len(sizes)} pool sizes for {len(distinct)} page groups")
+        self.page_size = page_size
+        self.num_pages = max(sizes, default=int(num_pages) if isinstance(num_pages, int) else 0)
+        self.max_step_tokens = max_step_tokens
         self.dtype, self.device = dtype, torch.device(device)
         self._next_uid = 0
         self.groups: list[PageGroup] = []
-        self.entries: list[KVCacheEntry | StateCacheEntry | None] = [None] * len(needs)
-        by_need: dict[KVNeed, PageGroup] = {}
-        state_calls: list[tuple[int, StateNeed]] = []
+        self.entries: list[Any] = [None] * len(needs)
+        by_need: dict[PagedNeed, PageGroup] = {}
+        slot_users: list[tuple[int, SlotNeed]] = []
         for call, need in enumerate(needs):
-            if isinstance(need, KVNeed):
+            if isinstance(need, PagedNeed):
                 g = by_need.get(need)
                 if g is None:
-                    g = PageGroup(len(self.groups), need, page_size, num_pages, [], PageAllocator(num_pages))
+                    n = sizes[len(self.groups)]
+                    g = PageGroup(len(self.groups), need, page_size, n, [], PageAllocator(n))
                     by_need[need] = g
                     self.groups.append(g)
                 g.calls.append(call)
-            elif isinstance(need, StateNeed):
-                state_calls.append((call, need))
+            elif isinstance(need, SlotNeed):
+                slot_users.append((call, need))
             elif need is not None:
-                raise TypeError(f"call {call}: unknown cache need {need!r}")
-        self.state_pool = StatePool(max_requests if state_calls else 0)
-        self.has_state = bool(state_calls)
+                raise TypeError(f"cache user {call}: {need!r} is neither a PagedNeed nor a SlotNeed")
+        self.state_pool = StatePool(max_requests if slot_users else 0)
+        self.has_state = bool(slot_users)
+        self._slot_storage: list[torch.Tensor] = []
         if allocate_memory:
             for g in self.groups:
-                n = g.need
-                g.kv = torch.zeros((len(g.calls), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
-                                   dtype=dtype, device=self.device)
+                g.kv = g.need.allocate(len(g.calls), g.num_pages + 1, page_size, dtype, self.device)
                 for j, call in enumerate(g.calls):
-                    self.entries[call] = KVCacheEntry(g.index, g.kv[j, 0], g.kv[j, 1], page_size)
-            for call, need in state_calls:
-                state = torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=self.device)
-                self.entries[call] = StateCacheEntry(state)
+                    self.entries[call] = g.need.entry(g.kv, j, g.index, page_size)
+            for call, need in slot_users:
+                storage = need.allocate(max_requests + 1, self.device)
+                self._slot_storage.append(storage)
+                self.entries[call] = need.entry(storage)
+
+    @staticmethod
+    def distinct_paged_needs(needs: Sequence[CacheNeed | None]) -> list[PagedNeed]:
+        """The paged needs that get a page group each, in the order of the groups."""
+        out: list[PagedNeed] = []
+        for need in needs:
+            if isinstance(need, PagedNeed) and need not in out:
+                out.append(need)
+        return out
 
     # ---- sizes
     def memory_bytes(self) -> int:
-        total = 0
-        for e in self.entries:
-            if isinstance(e, KVCacheEntry):
-                total += 2 * e.k.numel() * e.k.element_size()
-            elif isinstance(e, StateCacheEntry):
-                total += e.state.numel() * e.state.element_size()
-        return total
+        storages = [g.kv for g in self.groups if g.kv is not None] + self._slot_storage
+        return sum(t.numel() * t.element_size() for t in storages)
 
     @staticmethod
-    def bytes_per_token(needs: list[KVNeed | StateNeed | None], element_size: int) -> int:
-        return sum(2 * n.num_kv_heads * n.head_dim * element_size for n in needs if isinstance(n, KVNeed))
+    def bytes_per_token(needs: Sequence[CacheNeed | None], element_size: int) -> int:
+        return sum(n.bytes_per_token(element_size) for n in needs if isinstance(n, PagedNeed))
 
     @property
     def utilization(self) -> float:
@@ -155,9 +197,8 @@ class CacheManager:
         slot = -1
         if self.has_state:
             slot = self.state_pool.allocate()
-            for e in self.entries:
-                if isinstance(e, StateCacheEntry):
-                    e.state[slot].zero_()
+            for storage in self._slot_storage:
+                storage[slot].zero_()
         tables = [BlockTable(g.allocator, g.page_size, g.need.window) for g in self.groups]
         self._next_uid += 1
         return RequestCache(tables, slot, uid=self._next_uid)
@@ -186,9 +227,16 @@ class CacheManager:
             short = max(short, need - g.allocator.num_free)
         return max(short, 0)
 
-    def pages_for(self, num_tokens: int) -> int:
-        """Pages a request of ``num_tokens`` tokens holds at most in any group."""
-        return (num_tokens + self.page_size - 1) // self.page_size
+    def can_ever_hold(self, num_tokens: int, step_tokens: int) -> bool:
+        """Whether a request of up to ``num_tokens`` tokens, fed at most ``step_tokens`` a step,
+        fits every page group when it has the cache to itself."""
+        return all(g.most_pages_of(num_tokens, step_tokens) <= g.num_pages for g in self.groups)
+
+    @property
+    def capacity_tokens(self) -> int:
+        """Tokens of one request that the smallest group without a window holds."""
+        full = [g.num_pages for g in self.groups if g.need.window is None]
+        return (min(full) if full else self.num_pages) * self.page_size
 
     def append(self, req: RequestCache, n: int) -> None:
         """Reserve room for ``n`` more tokens in every group, or in none."""

@@ -7,9 +7,9 @@ Three kinds of object live here:
   ``ModelSpec`` (``to_spec``). No size or constant that ``config.json`` gives is repeated
   in code.
 * ``PartSpec`` / ``LayerSpec`` / ``LayerCall`` / ``ModelSpec``: plain data. A layer is a
-  mixer, a feed-forward and two norms arranged by a block; each is named by the key it was
-  registered under (``tinyserve_b200.parts.registry``) and carries its own sizes and
-  constants as arguments. Layers may differ from one another. The order in which layers
+  block and the parts that fill the block's roles (for the pre-norm block: a mixer, a
+  feed-forward and their two norms); each part is named by the key it was registered under
+  (``tinyserve_b200.parts.base``) and carries its own sizes and constants as arguments. Layers may differ from one another. The order in which layers
   run is a list of ``LayerCall`` too: it may name a layer twice, and a call may read the
   cache that an earlier call wrote instead of writing its own.
 
@@ -40,15 +40,14 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """What one layer is made of. ``prefix`` is where its tensors live in the checkpoint."""
+    """What one layer is made of. ``prefix`` is where its tensors live in the checkpoint;
+    ``block`` the registered block; ``parts`` maps each role that block names to the part that
+    fills it (``PreNormBlock``: "mixer", "feed_forward", "mixer_norm", "feed_forward_norm")."""
 
     prefix: str
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    position: PartSpec | None = None  # position encoding the mixer applies; None = none
+    parts: Mapping[str, PartSpec]
+    position: PartSpec | None = None  # position encoding the mixers apply; None = none
 
 
 @dataclass(frozen=True)

@@ -85,7 +85,8 @@ class Engine:
                  record_logits: bool = False) -> None:
         """``decode_graphs``: record the decode step once per batch-size bucket (CUDA graphs)
         and replay it whenever every scheduled request brings one token (upstream passes a
-        ``DecodeGraphs`` object for this, src/tinyserve/engine.py:96,188-196).
+        ``DecodeGraphs`` object for this, src/tinyserve/engine.py:96,188-196). A model with a
+        mixer that does not allow it (``Mixer.recordable``) runs kernel by kernel instead.
 
         ``prefill_graph`` (with ``decode_graphs`` and ``chunked_prefill``): the step of one request
         that brings a full portion of ``max_batch_tokens`` prompt tokens is recorded too.
@@ -105,9 +106,11 @@ class Engine:
         self.cache = cache
         self.runner = runner if runner is not None else ModelRunner(model, cache)
         if decode_graphs and not self.runner.graphs:
-            limit = min(model.spec.max_position_embeddings, cache.num_pages * cache.page_size)
-            self.runner.record_decode_graphs(max_num_seqs, graph_max_context or limit)
-            if prefill_graph and chunked_prefill and max_batch_tokens <= (graph_max_context or limit):
+            limit = min(model.spec.max_position_embeddings, cache.capacity_tokens)
+            if model.parts.recordable("decode"):
+                self.runner.record_decode_graphs(max_num_seqs, graph_max_context or limit)
+            if (prefill_graph and chunked_prefill and max_batch_tokens <= (graph_max_context or limit)
+                    and model.parts.recordable("prefill")):
                 self.runner.record_prefill_graph(max_batch_tokens, graph_max_context or limit)
         self.scheduler = Scheduler(cache, max_num_seqs, max_batch_tokens, chunked_prefill=chunked_prefill)
         self.sampler = Sampler(model.device, max_rows=max(max_num_seqs, 1))

@@ -52,7 +52,7 @@ class LLM:
             most = -(-model.spec.max_position_embeddings // page_size) * max_num_seqs
             num_pages = min(num_pages, most)
         self.cache = CacheManager(needs, page_size=page_size, num_pages=num_pages, max_requests=max_num_seqs,
-                                  dtype=model.dtype, device=model.device)
+                                  dtype=model.dtype, device=model.device, max_step_tokens=max_batch_tokens)
         self.engine = Engine(model, self.cache, max_num_seqs=max_num_seqs, max_batch_tokens=max_batch_tokens,
                              chunked_prefill=chunked_prefill, seed=seed, trace_steps=trace_steps,
                              decode_graphs=decode_graphs and model.device.type == "cuda",

@@ -48,9 +48,9 @@ class Scheduler:
         if not self.chunked_prefill and req.max_cached_tokens > self.max_batch_tokens:
             raise ValueError(f"request needs up to {req.max_cached_tokens} tokens in one step, "
                              f"max_batch_tokens is {self.max_batch_tokens}")
-        if self.cache.pages_for(req.max_cached_tokens) > self.cache.num_pages:
+        if not self.cache.can_ever_hold(req.max_cached_tokens, self.max_batch_tokens):
             raise ValueError(f"request needs up to {req.max_cached_tokens} cached tokens, the cache holds "
-                             f"{self.cache.num_pages * self.cache.page_size}")
+                             f"{self.cache.capacity_tokens}")
         req.status = Status.WAITING
         self.waiting.append(req)
         return req

@@ -98,7 +98,7 @@ class DecodeGraph:
         buf[self.s_tokens][live:] = 0
         buf[self.s_pos][live:] = 0
         buf[self.s_ctx][live:] = 1
-        buf[self.s_state][live:] = 0
+        buf[self.s_state][live:] = runner.cache.state_pool.pad_slot      # a row of state that belongs to nobody
         for g, ss, st in zip(runner.cache.groups, self.s_slots, self.s_tables):
             buf[ss][live:] = g.pad_page * g.page_size
             buf[st].reshape(n, self.width)[live:, 0] = g.pad_page
@@ -417,7 +417,7 @@ class ModelRunner:
         kernel by kernel."""
         if self.device.type != "cuda":
             raise RuntimeError("decode graphs need a CUDA device")
-        if not all(layer.block.mixer.graph_safe for layer in self.model.parts.layers):
+        if not self.model.parts.recordable("decode"):
             raise RuntimeError("a mixer of this model reads the step on the host; its decode step cannot be recorded")
         self.graph_max_context = max_context
         for rows in sorted(set(buckets or default_buckets(max_batch))):
@@ -434,8 +434,8 @@ class ModelRunner:
         those of its last token) is replayed from the recording."""
         if self.device.type != "cuda":
             raise RuntimeError("prefill graphs need a CUDA device")
-        if not all(layer.block.mixer.graph_safe for layer in self.model.parts.layers):
-            raise RuntimeError("a mixer of this model reads the step on the host; its steps cannot be recorded")
+        if not self.model.parts.recordable("prefill"):
+            raise RuntimeError("a mixer of this model reads the step on the host; its prompt portions cannot be recorded")
         if self.tune_launch_overlap:
             ops.use_pdl_mask(ops.PREFILL_PDL_MASK)
         g = PrefillGraph(self, tokens, max_context)

@@ -12,7 +12,9 @@ the whole sequence for every token instead. ``--temperature > 0`` or ``--num-sam
 the samples as one batch, sample ``i`` with seed ``seed + i``. Options beyond upstream's:
 ``--dtype bfloat16``, ``--prompt-ids``, ``--random-weights`` (write a random model folder for
 the ``config.json`` found in ``--model-dir`` first), ``--max-num-seqs``, ``--max-batch-tokens``,
-``--chunked-prefill``, ``--num-blocks``.
+``--chunked-prefill``, ``--num-blocks``, ``--no-cuda-graphs`` (decode steps are recorded once per
+batch size and replayed, and launched ahead of their tokens, unless this is given). The engine
+is set up before the clock starts, so the tokens/s line is about generation alone.
 """
 
 from __future__ import annotations
@@ -50,6 +52,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-num-seqs", type=int, default=None)
     p.add_argument("--max-batch-tokens", type=int, default=2048)
     p.add_argument("--chunked-prefill", action="store_true")
+    p.add_argument("--no-cuda-graphs", action="store_true", help="launch every decode step kernel by kernel")
     p.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                    help="first write model.safetensors with random weights for --model-dir's config.json")
     return p
@@ -60,9 +63,9 @@ def main(argv: list[str] | None = None) -> int:
     import torch
 
     from . import architectures  # noqa: F401
-    from .cache.manager import CacheManager
     from .config.registry import load_config
     from .engine.engine import Engine
+    from .engine.llm import LLM
     from .model import DecoderModel
     from .sampling.params import SamplingParams
     from .weights.random_init import write_random_model
@@ -93,18 +96,18 @@ def main(argv: list[str] | None = None) -> int:
     num_blocks = args.num_blocks or n * per_seq
 
     def make_engine(max_seqs: int) -> Engine:
-        cache = CacheManager(model.cache_needs(), page_size=args.block_size, num_pages=num_blocks,
-                             max_requests=max_seqs, dtype=dtype, device=model.device)
-        return Engine(model, cache, max_num_seqs=max_seqs, max_batch_tokens=max(args.max_batch_tokens, max_seqs),
-                      chunked_prefill=args.chunked_prefill)
+        # the same sizing and switches as the Python entry point
+        return LLM(model, page_size=args.block_size, num_pages=num_blocks, max_num_seqs=max_seqs,
+                   max_batch_tokens=max(args.max_batch_tokens, max_seqs), chunked_prefill=args.chunked_prefill,
+                   decode_graphs=not args.no_cuda_graphs).engine
 
     def show(ids: list[int]) -> str:
         return repr(tok.decode(ids)) if tok is not None else str(ids)
 
     sampled = args.temperature > 0 or n > 1
-    start = time.perf_counter()
     if sampled:
         engine = make_engine(args.max_num_seqs or n)
+        start = time.perf_counter()
         rids = []
         for i in range(n):
             seed = None if args.seed is None else args.seed + i
@@ -125,6 +128,8 @@ def main(argv: list[str] | None = None) -> int:
         mode = "no cache between steps"
         new: list[int] = []
         ids = list(prompt_ids)
+        args.no_cuda_graphs = True      # every token is a prompt step of a fresh engine: nothing to replay
+        start = time.perf_counter()
         for _ in range(args.max_new_tokens):
             engine = make_engine(1)     # nothing is kept from one token to the next
             nxt = engine.generate([ids], 1)[0][0]
@@ -134,7 +139,11 @@ def main(argv: list[str] | None = None) -> int:
                 break
     else:
         mode = f"paged cache, {num_blocks} blocks x {args.block_size} tokens"
-        new = make_engine(1).generate([prompt_ids], args.max_new_tokens, eos)[0]
+        engine = make_engine(1)
+        start = time.perf_counter()
+        new = engine.generate([prompt_ids], args.max_new_tokens, eos)[0]
+        if engine.runner.graphs:
+            mode += f", {engine.runner.num_graph_steps} of {engine.num_steps} steps replayed from recordings"
     secs = time.perf_counter() - start
     print(f"prompt ids: {prompt_ids}")
     print(f"new ids:    {new}")

@@ -19,8 +19,8 @@ import torch
 from . import parts as _parts  # noqa: F401  (registers the built-in parts)
 from .config.base import LayerSpec, ModelConfig, ModelSpec
 from .parts.base import (
-    BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
-    Block, KVNeed, PositionEncoding, ResidualStream, StateNeed, StepContext, TensorSpec,
+    BLOCKS, EMBEDDINGS, HEADS, NORMS, PART_FAMILIES, POSITION_ENCODINGS,
+    Block, CacheNeed, PagedNeed, PositionEncoding, ResidualStream, StepContext, TensorSpec,
 )
 from .weights.loader import load_tensors, merge_specs
 from .weights.random_init import random_bound_tensors
@@ -43,38 +43,65 @@ class ModelParts:
         self.head = HEADS.build(spec.head.kind, **spec.head.args)
         self._positions: dict[Any, PositionEncoding] = {}
         self.layers: list[Layer] = []
-        for ls in spec.layers:
-            mixer = MIXERS.build(ls.mixer.kind, **ls.mixer.args)
-            ffn = FEED_FORWARDS.build(ls.feed_forward.kind, **ls.feed_forward.args)
-            n1 = NORMS.build(ls.mixer_norm.kind, **ls.mixer_norm.args)
-            n2 = NORMS.build(ls.feed_forward_norm.kind, **ls.feed_forward_norm.args)
-            block = BLOCKS.build(ls.block, mixer, ffn, n1, n2)
+        for n, ls in enumerate(spec.layers):
+            block = self._build_block(n, ls)
             pos = None
             if ls.position is not None:
                 cand = POSITION_ENCODINGS.build(ls.position.kind, **ls.position.args)
                 pos = self._positions.setdefault(cand.key(), cand)
             self.layers.append(Layer(ls, block, pos))
+        # One cache user per (call of the order, mixer role of its block), in that order: the
+        # cache manager gets their needs as a flat list and hands back one entry for each.
+        self.cache_users: list[tuple[int, str]] = []
+        self._user_index: dict[tuple[int, str], int] = {}
+        for n, call in enumerate(spec.order):
+            for role in self.layers[call.layer].block.mixers():
+                self._user_index[(n, role)] = len(self.cache_users)
+                self.cache_users.append((n, role))
         self._check_order()
+
+    @staticmethod
+    def _build_block(n: int, ls: LayerSpec) -> Block:
+        """The block class names its roles; every role is built from the registry of its family."""
+        block_cls = BLOCKS.get(ls.block)
+        roles = getattr(block_cls, "roles", None)
+        if not roles:
+            raise TypeError(f"block {ls.block!r} names no roles (a Block subclass with a ``roles`` mapping is needed)")
+        optional = getattr(block_cls, "optional_roles", frozenset())
+        unknown = set(ls.parts) - set(roles)
+        missing = set(roles) - set(ls.parts) - set(optional)
+        if unknown or missing:
+            raise ValueError(f"layer {n} ({ls.block!r}): parts for unknown roles {sorted(unknown)}, "
+                             f"no parts for roles {sorted(missing)}; the block's roles are {dict(roles)}")
+        parts = {}
+        for role, family in roles.items():
+            if role not in ls.parts:
+                continue
+            if family not in PART_FAMILIES:
+                raise ValueError(f"block {ls.block!r}: role {role!r} names the unknown family {family!r}")
+            parts[role] = PART_FAMILIES[family].build(ls.parts[role].kind, **ls.parts[role].args)
+        return block_cls(parts)
 
     def _check_order(self) -> None:
         for n, call in enumerate(self.spec.order):
             src = call.reads_cache_of
             if src is None:
                 continue
-            mine = self.layers[call.layer].block.mixer.cache_need()
-            theirs = self.layers[self.spec.order[src].layer].block.mixer.cache_need()
-            same = (isinstance(mine, KVNeed) and isinstance(theirs, KVNeed)
-                    and (mine.num_kv_heads, mine.head_dim) == (theirs.num_kv_heads, theirs.head_dim))
-            if not same:
-                raise ValueError(
-                    f"order[{n}] reads the cache of call {src}, whose layout differs: {mine} vs {theirs}")
+            mine = {r: m.cache_need() for r, m in self.layers[call.layer].block.mixers().items()}
+            theirs = {r: m.cache_need() for r, m in self.layers[self.spec.order[src].layer].block.mixers().items()}
+            for role, need in mine.items():
+                other = theirs.get(role)
+                same = (isinstance(need, PagedNeed) and type(other) is type(need)
+                        and {**vars(need), "window": None} == {**vars(other), "window": None})
+                if not same:
+                    raise ValueError(
+                        f"order[{n}] reads the cache of call {src}, whose layout differs: {need} vs {other}")
 
     # ---- weights
     def _each_part(self):
         yield "", self.embedding
         for layer in self.layers:
-            b = layer.block
-            for part in (b.mixer_norm, b.mixer, b.feed_forward_norm, b.feed_forward):
+            for part in layer.block.parts.values():
                 yield layer.spec.prefix, part
         yield "", self.final_norm
         yield "", self.head
@@ -96,16 +123,35 @@ class ModelParts:
             part.bind(prefix, tensors)
 
     # ---- cache
-    def cache_needs(self) -> list[KVNeed | StateNeed | None]:
-        """One entry per call of the order: what that call keeps between steps (``None``
-        for a call that keeps nothing or that reads another call's cache)."""
-        needs: list[KVNeed | StateNeed | None] = []
-        for call in self.spec.order:
+    def cache_needs(self) -> list[CacheNeed | None]:
+        """One entry per cache user (a call of the order and a mixer role of its block; with one
+        mixer per block, one entry per call): what it keeps between steps (``None`` for a
+        mixer that keeps nothing or a call that reads another call's cache)."""
+        needs: list[CacheNeed | None] = []
+        for n, role in self.cache_users:
+            call = self.spec.order[n]
             if call.reads_cache_of is not None:
                 needs.append(None)
             else:
-                needs.append(self.layers[call.layer].block.mixer.cache_need())
+                needs.append(self.layers[call.layer].block.parts[role].cache_need())
         return needs
+
+    def caches_of_call(self, n: int, entries: list[Any]) -> dict[str, Any]:
+        """The cache entries that call ``n`` of the order works on, by mixer role: its own, or
+        those of the call whose cache it reads."""
+        call = self.spec.order[n]
+        src = n if call.reads_cache_of is None else call.reads_cache_of
+        out = {}
+        for role in self.layers[call.layer].block.mixers():
+            entry = entries[self._user_index[(src, role)]]
+            if entry is not None:
+                out[role] = entry
+        return out
+
+    def recordable(self, kind: str) -> bool:
+        """Whether steps of this kind ("decode", "prefill") can be recorded: every part allows it."""
+        parts = [part for _, part in self._each_part()] + [l.position for l in self.layers if l.position is not None]
+        return all(kind in part.recordable for part in parts)
 
 
 def build_parts(spec: ModelSpec) -> ModelParts:
@@ -150,7 +196,7 @@ class DecoderModel:
     def vocab_size(self) -> int:
         return self.spec.vocab_size
 
-    def cache_needs(self) -> list[KVNeed | StateNeed | None]:
+    def cache_needs(self) -> list[CacheNeed | None]:
         return self.parts.cache_needs()
 
     def weight_bytes(self) -> int:
@@ -176,9 +222,7 @@ class DecoderModel:
                 if key not in ctx.position_tables:
                     ctx.position_tables[key] = layer.position.prepare(ctx)
                 tables = ctx.position_tables[key]
-            src = call.reads_cache_of
-            entry = caches[n if src is None else src]
-            layer.block.forward(stream, ctx, entry, src is None, tables)
+            layer.block.forward(stream, ctx, parts.caches_of_call(n, caches), call.reads_cache_of is None, tables)
         ctx.arena.step_region()
         if num_want == 0:
             return None

@@ -17,12 +17,12 @@ from typing import Any, Mapping
 import torch
 
 from ..kernels import ops
-from .base import (KVCacheEntry, KVNeed, LazyNormed, Mixer, ResidualStream, StepContext, TensorSpec, project,
+from .base import (EVERY_STEP, KVCacheEntry, KVNeed, LazyNormed, Mixer, ResidualStream, StepContext, TensorSpec, project,
                    project_to_stream, register_mixer)
 
 
 class GQAAttention(Mixer):
-    graph_safe = True
+    recordable = EVERY_STEP
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, scale: float, qk_norm: bool = False, qk_norm_eps: float = 1e-6,
@@ -31,6 +31,8 @@ class GQAAttention(Mixer):
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
         if window is not None and window <= 0:
             raise ValueError(f"window must be positive or None, got {window}")
+        if head_dim <= 0 or head_dim % 16 or head_dim > 256:
+            raise ValueError(f"head_dim={head_dim}: the attention kernels take head sizes in steps of 16 up to 256")
         self.prefix = prefix
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.head_dim, self.scale = int(head_dim), float(scale)
@@ -77,10 +79,12 @@ class GQAAttention(Mixer):
         width = self.q_size + 2 * self.kv_size if writes_cache else self.q_size
         qkv = arena.take((t, width), ctx.dtype)
         project(x, self.w_qkv if writes_cache else self.w_q, qkv, ctx)
-        cos = None if position is None else position.cos
-        sin = None if position is None else position.sin
-        rotary_dim = 0 if position is None else position.rotary_dim
-        interleaved = False if position is None else position.interleaved
+        # what the layer's position encoding asks to be done to q and k: a rotation, or nothing
+        rot = None if position is None else position.qk_rotation()
+        cos = None if rot is None else rot.cos
+        sin = None if rot is None else rot.sin
+        rotary_dim = 0 if rot is None else rot.rotary_dim
+        interleaved = False if rot is None else rot.interleaved
         attn = arena.take((t, self.q_size), ctx.dtype)
         join = None
         if ops.PREFETCH_WEIGHTS and ctx.num_prefill == 0 and ctx.num_decode <= ops.PREFETCH_MAX_ROWS and x_device.type == "cuda":

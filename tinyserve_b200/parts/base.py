@@ -11,13 +11,17 @@ Kinds of part and what each must provide:
   norm folds that output into the stream before normalising, so the residual sum is made
   in 32-bit and costs no extra pass. ``forward_rows`` does the same for selected rows only
   without changing the stream (used before the output head).
-* ``PositionEncoding``: ``prepare(ctx)`` once per step returns whatever tables the mixers
-  of this step need (for rotary encodings: cos/sin per token). The mixer applies them.
-* ``Mixer``: ``cache_need()`` says what it keeps between steps (pages of keys/values for
-  all or a window of the positions, a fixed-size state slot, or nothing);
-  ``forward(x, ctx, cache, writes_cache) -> [T, hidden]``.
+* ``PositionEncoding``: ``prepare(ctx)`` once per step returns the step's position data, an
+  object with one method, ``qk_rotation()``: the rotation the mixer applies to its queries and
+  keys (``Rotation``: cos/sin per token, how many elements of a head turn, how they pair up),
+  or ``None`` if queries and keys stay as they are.
+* ``Mixer``: ``cache_need()`` says what it keeps between steps, as a ``CacheNeed``: a
+  ``PagedNeed`` (pages per token: ``KVNeed`` is keys and values for all or a window of the
+  positions; a mixer may define its own), a ``SlotNeed`` (``StateNeed``: a fixed-size state per
+  request), or nothing; ``forward(x, ctx, cache, writes_cache) -> [T, hidden]``.
 * ``FeedForward``: ``forward(x, ctx) -> [T, hidden]``.
-* ``Block``: arranges one mixer, one feed-forward and their norms around the stream.
+* ``Block``: names the roles it wants filled (``roles``: role -> family of part) and arranges
+  those parts around the stream; ``PreNormBlock`` wants a mixer, a feed-forward and their norms.
 
 Registering a class under a name (``register_mixer("my_mixer", MyMixer)`` and so on) is all
 it takes to make it available to a ``LayerSpec``; nothing else in the framework changes.
@@ -55,23 +59,81 @@ class TensorSpec:
 
 
 # ------------------------------------------------------------------------ cache needs
+class CacheNeed:
+    """What one call of a mixer keeps between steps. The cache manager knows two families and
+    serves any subclass of them through the methods below, so a mixer with a cache of another
+    shape (one latent vector per token, keys of another width than the values, ...) defines its
+    own frozen dataclass deriving ``PagedNeed`` or ``SlotNeed`` and nothing in the manager changes."""
+
+
+class PagedNeed(CacheNeed):
+    """Memory per token, in pages. Calls whose needs compare equal share a page group (one pool
+    of pages, one block table per request). ``window``: only the last ``window`` positions are
+    ever read again (pages behind it are given back early); ``None`` keeps every position."""
+
+    window: int | None = None
+
+    def bytes_per_token(self, element_size: int) -> int:
+        raise NotImplementedError
+
+    def allocate(self, num_calls: int, num_pages: int, page_size: int, dtype: torch.dtype,
+                 device: torch.device) -> torch.Tensor:
+        """The storage of a whole group: ``num_pages`` already counts the pad page (the last one,
+        never handed out, where fixed-shape padding rows may write). Zero-filled."""
+        raise NotImplementedError
+
+    def entry(self, storage: torch.Tensor, call_in_group: int, group: int, page_size: int) -> Any:
+        """What the mixer's ``forward`` receives as ``cache`` for one call: views into ``storage``
+        and ``group``, the key of this call's block tables and slots in ``StepContext.kv``."""
+        raise NotImplementedError
+
+
+class SlotNeed(CacheNeed):
+    """Memory of fixed size per request, in slots: zero at the request's first token, carried from
+    step to step, lost (recomputed) on preemption. One extra slot after the pool is never handed
+    out; fixed-shape padding rows of a recorded step use it."""
+
+    def allocate(self, num_slots: int, device: torch.device) -> torch.Tensor:
+        """``[num_slots, ...]`` zero-filled; ``num_slots`` already counts the pad slot."""
+        raise NotImplementedError
+
+    def entry(self, storage: torch.Tensor) -> Any:
+        raise NotImplementedError
+
+
 @dataclass(frozen=True)
-class KVNeed:
+class KVNeed(PagedNeed):
     """Pages of keys and values: ``num_kv_heads x head_dim`` per token, for every position
-    (``window=None``) or only the last ``window`` positions."""
+    (``window=None``) or only the last ``window`` positions. Storage
+    ``[call, k|v, page, kv_head, offset, head_dim]``: the keys of one (page, kv head) are one
+    contiguous run of ``page_size * head_dim`` elements, the unit a bulk copy moves."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
 
+    def bytes_per_token(self, element_size: int) -> int:
+        return 2 * self.num_kv_heads * self.head_dim * element_size
+
+    def allocate(self, num_calls, num_pages, page_size, dtype, device):
+        return torch.zeros((num_calls, 2, num_pages, self.num_kv_heads, page_size, self.head_dim), dtype=dtype, device=device)
+
+    def entry(self, storage, call_in_group, group, page_size):
+        return KVCacheEntry(group, storage[call_in_group, 0], storage[call_in_group, 1], page_size)
+
 
 @dataclass(frozen=True)
-class StateNeed:
-    """A slot of fixed size per request: ``shape`` elements of ``dtype``, zero at the
-    request's first token, carried from step to step."""
+class StateNeed(SlotNeed):
+    """A slot of fixed size per request: ``shape`` elements of ``dtype``."""
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+    def allocate(self, num_slots, device):
+        return torch.zeros((num_slots, *self.shape), dtype=self.dtype, device=device)
+
+    def entry(self, storage):
+        return StateCacheEntry(storage)
 
 
 @dataclass
@@ -87,7 +149,8 @@ class KVCacheEntry:
 
 @dataclass
 class StateCacheEntry:
-    """``state`` is ``[slots, *shape]``; row ``ctx.state_slots[b]`` belongs to request b."""
+    """``state`` is ``[slots + 1, *shape]``; row ``ctx.state_slots[b]`` belongs to request b (the
+    last row is the pad slot of recorded steps' padding rows)."""
 
     state: torch.Tensor
 
@@ -220,7 +283,19 @@ def project_to_stream(x: torch.Tensor, w: torch.Tensor, stream: ResidualStream |
 
 
 # ------------------------------------------------------------------------- interfaces
+EVERY_STEP = frozenset({"decode", "prefill"})
+
+
 class Part:
+    # The kinds of step in which the part reads nothing of the step on the host (no lengths, no
+    # slot lists, no result of a device computation) and launches the same work whatever the step's
+    # values: "decode" (every request brings one token) and/or "prefill" (one request brings a
+    # fixed number of tokens). Only such steps can be recorded once and replayed as a graph; one
+    # part that does not allow a kind switches its recording off for the whole model. The default
+    # allows nothing; the built-in parts allow both (``EVERY_STEP``). A mixer with state of its own
+    # can allow "decode" by indexing its state with ``ctx.state_slots`` on the device.
+    recordable: frozenset = frozenset()
+
     def tensor_specs(self, prefix: str) -> list[TensorSpec]:
         return []
 
@@ -245,25 +320,40 @@ class Norm(Part):
         raise NotImplementedError
 
 
+@dataclass
+class Rotation:
+    """A rotation of the first ``rotary_dim`` elements of every query and key head by the
+    token's angles: ``cos``/``sin`` are ``[T, rotary_dim / 2]`` float32 on the device; pairs are
+    ``(i, i + rotary_dim / 2)`` or, ``interleaved``, neighbours ``(2i, 2i + 1)``."""
+
+    cos: torch.Tensor
+    sin: torch.Tensor
+    rotary_dim: int
+    interleaved: bool = False
+
+    def qk_rotation(self) -> "Rotation":
+        return self
+
+
 class PositionEncoding(Part):
     def key(self) -> Any:
         """Encodings with equal keys share one set of tables per step."""
         raise NotImplementedError
 
     def prepare(self, ctx: StepContext) -> Any:
+        """Once per step: the step's position data, an object with the method ``qk_rotation()``
+        that returns the ``Rotation`` a mixer applies to its queries and keys, or ``None`` when
+        they stay as they are (a ``Rotation`` is such an object itself)."""
         raise NotImplementedError
 
 
 class Mixer(Part):
-    # True if ``forward`` reads nothing of the step on the host (no lengths, no slot lists):
-    # only then can a decode step with this mixer be recorded once and replayed as a graph.
-    graph_safe: bool = False
     # True if ``forward`` accepts a ``LazyNormed`` for ``x`` (and hands it to ``project``).
     takes_lazy_input: bool = False
     # True if ``forward`` has a keyword ``stream`` and may add its output to it (returning None).
     adds_to_stream: bool = False
 
-    def cache_need(self) -> KVNeed | StateNeed | None:
+    def cache_need(self) -> CacheNeed | None:
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Any, writes_cache: bool,
@@ -285,15 +375,28 @@ class FeedForward(Part):
 
 
 class Block:
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                 feed_forward_norm: Norm) -> None:
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+    """Arranges the parts of one layer around the residual stream. A block class names the roles
+    it wants filled: ``roles`` maps a role (a name of the block's own choosing, the key under which
+    ``LayerSpec.parts`` gives the part) to the family the part comes from ("mixer",
+    "feed_forward" or "norm"); roles in ``optional_roles`` may be left out. The model builds the
+    parts in the order of ``roles`` (which is also the order of their tensors) and hands them
+    over as a dict. A block with a third norm, two mixers side by side or no feed-forward at all
+    is another ``Block`` class and a ``register_block`` call."""
 
-    def forward(self, stream: ResidualStream, ctx: StepContext, cache: Any, writes_cache: bool,
+    roles: Mapping[str, str] = {}
+    optional_roles: frozenset = frozenset()
+
+    def __init__(self, parts: Mapping[str, Part]) -> None:
+        self.parts = dict(parts)
+
+    def mixers(self) -> dict[str, Mixer]:
+        """The parts that may keep a cache, by role."""
+        return {role: p for role, p in self.parts.items() if isinstance(p, Mixer)}
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches: Mapping[str, Any], writes_cache: bool,
                 position: Any) -> None:
+        """``caches[role]`` is the cache entry of the mixer in that role for this call of the
+        layer (absent if it keeps nothing)."""
         raise NotImplementedError
 
 
@@ -308,10 +411,13 @@ class _Registry:
             raise ValueError(f"{self.what} {name!r} is already registered")
         self._items[name] = factory
 
-    def build(self, kind: str, /, *args: Any, **kwargs: Any) -> Any:
+    def get(self, kind: str) -> Callable[..., Any]:
         if kind not in self._items:
             raise KeyError(f"unknown {self.what} {kind!r}; known: {sorted(self._items)}")
-        return self._items[kind](*args, **kwargs)
+        return self._items[kind]
+
+    def build(self, kind: str, /, *args: Any, **kwargs: Any) -> Any:
+        return self.get(kind)(*args, **kwargs)
 
     def names(self) -> list[str]:
         return sorted(self._items)
@@ -324,6 +430,8 @@ POSITION_ENCODINGS = _Registry("position encoding")
 BLOCKS = _Registry("block")
 EMBEDDINGS = _Registry("embedding")
 HEADS = _Registry("output head")
+# the families a block's roles may name
+PART_FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
 
 
 def register_mixer(name: str, factory: Callable[..., Mixer], **kw: Any) -> None:

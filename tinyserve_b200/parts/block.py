@@ -5,18 +5,27 @@ output is left pending on the stream and the next norm adds it in 32-bit.
 
 from __future__ import annotations
 
-from typing import Any
+from typing import Any, Mapping
 
-from .base import Block, ResidualStream, StepContext, register_block
+from .base import Block, Part, ResidualStream, StepContext, register_block
 
 
 class PreNormBlock(Block):
-    def forward(self, stream: ResidualStream, ctx: StepContext, cache: Any, writes_cache: bool,
+    # the order is the order of the layer's tensors in ``tensor_specs``
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+
+    def __init__(self, parts: Mapping[str, Part]) -> None:
+        super().__init__(parts)
+        self.mixer, self.feed_forward = parts["mixer"], parts["feed_forward"]
+        self.mixer_norm, self.feed_forward_norm = parts["mixer_norm"], parts["feed_forward_norm"]
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches: Mapping[str, Any], writes_cache: bool,
                 position: Any) -> None:
         # Scratch of this layer goes to the other half of the arena than the previous
         # layer's, whose pending output the first norm below still has to read.
         ctx.arena.next_frame()
         mixer, ff = self.mixer, self.feed_forward
+        cache = caches.get("mixer")
         ctx.upcoming_weights = ff.streamed_weights()
         hn = self.mixer_norm.lazy(stream, ctx) if mixer.takes_lazy_input else self.mixer_norm.forward(stream, ctx)
         if mixer.adds_to_stream:

@@ -10,10 +10,12 @@ from typing import Mapping
 import torch
 
 from ..kernels import ops
-from .base import EMBEDDINGS, HEADS, Part, StepContext, TensorSpec
+from .base import EMBEDDINGS, EVERY_STEP, HEADS, Part, StepContext, TensorSpec
 
 
 class TokenEmbedding(Part):
+    recordable = EVERY_STEP
+
     def __init__(self, name: str, vocab_size: int, hidden_size: int) -> None:
         self.name, self.vocab_size, self.hidden_size = name, int(vocab_size), int(hidden_size)
         self.table: torch.Tensor | None = None
@@ -32,6 +34,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    recordable = EVERY_STEP
+
     def __init__(self, name: str, tied: bool, vocab_size: int, hidden_size: int,
                  ignored_when_tied: str | None = None) -> None:
         self.name, self.tied = name, bool(tied)

@@ -13,11 +13,13 @@ from typing import Mapping
 import torch
 
 from ..kernels import ops
-from .base import (FeedForward, LazyNormed, ResidualStream, StepContext, TensorSpec, project, project_to_stream,
+from .base import (EVERY_STEP, FeedForward, LazyNormed, ResidualStream, StepContext, TensorSpec, project, project_to_stream,
                    register_feed_forward)
 
 
 class SwiGLU(FeedForward):
+    recordable = EVERY_STEP
+
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int) -> None:
         self.prefix = prefix
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)

@@ -13,10 +13,12 @@ from typing import Mapping
 import torch
 
 from ..kernels import ops
-from .base import LazyNormed, Norm, ResidualStream, StepContext, TensorSpec, register_norm
+from .base import EVERY_STEP, LazyNormed, Norm, ResidualStream, StepContext, TensorSpec, register_norm
 
 
 class RMSNorm(Norm):
+    recordable = EVERY_STEP
+
     def __init__(self, name: str, size: int, eps: float) -> None:
         self.name, self.size, self.eps = name, int(size), float(eps)
         self.weight: torch.Tensor | None = None

@@ -9,24 +9,19 @@ former) is applied by the mixer's fused kernel, which receives these tables.
 
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Any
 
 import torch
 
 from ..kernels import ops
-from .base import PositionEncoding, StepContext, register_position_encoding
+from .base import EVERY_STEP, PositionEncoding, Rotation, StepContext, register_position_encoding
 
-
-@dataclass
-class RotaryTables:
-    cos: torch.Tensor        # [T, rotary_dim / 2] float32
-    sin: torch.Tensor
-    rotary_dim: int
-    interleaved: bool
+RotaryTables = Rotation      # the step's position data of a rotary encoding is the rotation itself
 
 
 class RotaryEncoding(PositionEncoding):
+    recordable = EVERY_STEP
+
     def __init__(self, head_dim: int, rotary_dim: int, theta: float, pairing: str = "half") -> None:
         if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
             raise ValueError(f"rotary_dim={rotary_dim} must be even and at most head_dim={head_dim}")
