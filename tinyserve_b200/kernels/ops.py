@@ -49,7 +49,7 @@ _SIGNATURES: dict[str, list[Any]] = {
                                      _f, _i, _i, _vp, _vp],
     "ts_gemm_skinny_normed": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_to_stream": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
-    "ts_prefetch_l2": [_vp, _vp, _i, _vp],
+    "ts_prefetch_l2": [_vp, _vp, _i, _i, _vp],
     "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
@@ -685,7 +685,8 @@ def gemm_normed(resid16: torch.Tensor, sumsq: torch.Tensor, norm_weight: torch.T
 
 # -------------------------------------------------------------------- L2 prefetch
 # Decode steps of a few requests fetch the weights of the products that follow the attention
-# kernel into L2 while that kernel runs (it leaves memory bandwidth idle). Measured on B200 at the
+# kernel into L2 while that kernel runs (it leaves memory bandwidth idle), from a kernel of their
+# own on a side stream (other placements were measured and are worse: csrc/prefetch.cu). Measured on B200 at the
 # Qwen3-0.6B sizes with 1,024-token contexts: with their weights in L2 the products take 2.6-3.8 us
 # instead of 3.4-5.4 us each; the decode step gains 1.5 % at batch 1 and 4.7 % at batch 8, nothing
 # at 16, and loses 3 % from batch 32 on, where attention needs the bandwidth itself. Fetching the
@@ -696,9 +697,34 @@ PREFETCH_MAX_BYTES = 48 << 20          # per call: well under L2's size
 _side_streams: dict[int, "torch.cuda.Stream"] = {}
 
 
-def prefetch_l2(tensors: Sequence[torch.Tensor]) -> None:
+# The attention kernel of a decode step lasts about this long: a fixed part and its cache at the rate
+# it reaches beside the prefetch. A recorded step is recorded for the longest context it may carry,
+# so the typical context is assumed for anything longer.
+PREFETCH_ATTENTION_FIXED_US = 3.0
+PREFETCH_ATTENTION_GBS = 4000.0
+PREFETCH_TYPICAL_CONTEXT = 1024
+PREFETCH_THREADS = 0             # non-zero: requests per CTA, whatever the step (measurements)
+PREFETCH_SM_GBS = 150.0          # what one SM passes on of such requests (measured on B200)
+PREFETCH_PIECE = 16 * 1024
+
+
+def prefetch_threads(total_bytes: int, beside_us: float) -> int:
+    """Requests per CTA of the prefetch kernel so that it lasts about ``beside_us`` microseconds (the
+    kernel lasts until its requests are served, and it is joined again after the kernel it runs
+    beside, so it should end with that one: slower and the step waits for it, faster and it takes
+    bandwidth the other kernel could use)."""
+    if PREFETCH_THREADS:
+        return PREFETCH_THREADS
+    ctas = max(1.0, total_bytes / (PREFETCH_SM_GBS * 1e3 * max(beside_us, 1.0)))
+    pieces = max(1, total_bytes // PREFETCH_PIECE)
+    per_cta = pieces / ctas
+    return int(min(128, max(16, 16 * round(per_cta / 16))))
+
+
+def prefetch_l2(tensors: Sequence[torch.Tensor], threads: int = 128) -> None:
     """Ask for the memory of ``tensors`` (contiguous, on the device; at most 8) to be brought
-    into L2. Returns at once; nothing waits for the data."""
+    into L2. Returns at once; nothing waits for the data. ``threads``: requests of 16 KB per CTA
+    (16 to 128 in steps of 16; fewer means more CTAs and a higher rate, see ``prefetch_threads``)."""
     tensors = [t for t in tensors if t is not None and t.numel()]
     if not tensors:
         return
@@ -706,10 +732,10 @@ def prefetch_l2(tensors: Sequence[torch.Tensor]) -> None:
         raise KernelError("prefetch_l2: at most 8 tensors per call")
     bases = (_c.c_void_p * len(tensors))(*[_dev(t, "tensor") for t in tensors])
     sizes = (_c.c_ulonglong * len(tensors))(*[t.numel() * t.element_size() for t in tensors])
-    _check(_fn("ts_prefetch_l2")(bases, sizes, len(tensors), _stream()), "prefetch_l2")
+    _check(_fn("ts_prefetch_l2")(bases, sizes, len(tensors), int(threads), _stream()), "prefetch_l2")
 
 
-def prefetch_l2_beside(tensors: Sequence[torch.Tensor]) -> "Callable[[], None]":
+def prefetch_l2_beside(tensors: Sequence[torch.Tensor], threads: int = 128) -> "Callable[[], None]":
     """:func:`prefetch_l2` on a stream of its own that starts where the current stream stands,
     so that it runs beside the kernels launched next. Returns the function that makes the
     current stream wait for it again (call it after those kernels; a recording of the step
@@ -720,7 +746,7 @@ def prefetch_l2_beside(tensors: Sequence[torch.Tensor]) -> "Callable[[], None]":
         side = _side_streams[cur.device.index] = torch.cuda.Stream(device=cur.device)
     side.wait_stream(cur)
     with torch.cuda.stream(side), stream_scope():
-        prefetch_l2(tensors)
+        prefetch_l2(tensors, threads)
     return lambda: cur.wait_stream(side)
 
 

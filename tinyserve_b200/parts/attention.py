@@ -90,9 +90,15 @@ class GQAAttention(Mixer):
         if ops.PREFETCH_WEIGHTS and ctx.num_prefill == 0 and ctx.num_decode <= ops.PREFETCH_MAX_ROWS and x_device.type == "cuda":
             # decode: attention streams the cache and leaves bandwidth idle; the weights of the
             # products after it (output projection, feed-forward) come into L2 meanwhile
-            ahead = [w for w in [self.w_o, *ctx.upcoming_weights] if w is not None]
-            if ahead and sum(w.numel() * w.element_size() for w in ahead) <= ops.PREFETCH_MAX_BYTES:
-                join = ops.prefetch_l2_beside(ahead[:8])
+            ahead = [w for w in [self.w_o, *ctx.upcoming_weights] if w is not None][:8]
+            nbytes = sum(w.numel() * w.element_size() for w in ahead)
+            if ahead and nbytes <= ops.PREFETCH_MAX_BYTES:
+                # at the rate that makes it last as long as the attention kernel is expected to: that
+                # kernel's fixed part and the cache it streams
+                cache_bytes = 2.0 * ctx.num_decode * min(ctx.max_context_len, ops.PREFETCH_TYPICAL_CONTEXT) \
+                    * self.kv_size * self.w_o.element_size()
+                beside_us = ops.PREFETCH_ATTENTION_FIXED_US + cache_bytes / (ops.PREFETCH_ATTENTION_GBS * 1e3)
+                join = ops.prefetch_l2_beside(ahead, ops.prefetch_threads(nbytes, beside_us))
         if writes_cache and ops.can_fuse_decode(ctx, ctx.dtype, self.num_heads, self.num_kv_heads, self.head_dim,
                                                 cache.page_size, cache.k.shape[0], rotary_dim, interleaved,
                                                 cache.k.device):
