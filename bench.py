@@ -381,6 +381,8 @@ class Bench:
         def work(name: str, a: tuple) -> float:
             if name in ("gemm", "gemm_swiglu"):
                 return nbytes(a[0], a[1], a[2])
+            if name == "qk_norm_rope_write":      # the rows it reads and writes, not the cache tensors
+                return 2.0 * nbytes(a[0])
             if name == "embed":                   # the rows it gathers, not the table
                 return nbytes(a[0], a[2]) + a[0].numel() * a[1].shape[1] * a[1].element_size()
             if name == "gemm_to_stream":
@@ -453,6 +455,45 @@ class Bench:
         return table
 
 
+def gemm_table() -> int:
+    """The tcgen05 product of this engine against the vendor library's at the four layer shapes of the
+    three model sizes, 512 and 2,048 rows, kernel by kernel with CUDA events (20 launches after 3)."""
+    import torch
+
+    from tinyserve_b200.kernels import ops
+
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+
+    def timed(fn) -> float:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_.record()
+        for _ in range(20):
+            fn()
+        e_.record()
+        torch.cuda.synchronize()
+        return s_.elapsed_time(e_) / 20 * 1e3
+
+    print(f"{'rows':>5} {'shape':<14} {'N':>6} {'K':>6} {'library us':>10} {'TFLOP/s':>8} {'tcgen05 us':>10} {'TFLOP/s':>8}")
+    for m in (512, 2048):
+        for name, d in MODELS.items():
+            h, inter = d["hidden_size"], d["intermediate_size"]
+            q, kv = d["num_attention_heads"] * d["head_dim"], d["num_key_value_heads"] * d["head_dim"]
+            for what, n, k in (("qkv", q + 2 * kv, h), ("o", h, q), ("gate_up", 2 * inter, h), ("down", h, inter)):
+                w = (torch.randn(n, k, device=dev) * 0.02).to(bf)
+                x = torch.randn(m, k, device=dev).to(bf)
+                out = torch.empty(m, n, device=dev, dtype=bf)
+                lib = timed(lambda: torch.mm(x, w.t(), out=out))
+                own = timed(lambda: ops.gemm_tcgen05(x, w, out, 256))
+                fl = 2.0 * m * n * k
+                print(f"{m:>5} {name + ' ' + what:<14} {n:>6} {k:>6} {lib:>10.1f} {fl / lib / 1e6:>8.0f} {own:>10.1f} {fl / own / 1e6:>8.0f}")
+                del w, x, out
+    ops.check_device_errors()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -469,9 +510,11 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--kernels", action="store_true", help="add the per-kernel-class table of the decode step")
-    ap.add_argument("--profile", choices=["decode", "prefill", "timeline"], default=None,
-                    help="run a small case kernel by kernel between cudaProfilerStart/Stop and exit "
-                         "(for ncu --profile-from-start off); combine with --layers, --batch")
+    ap.add_argument("--profile", choices=["decode", "prefill", "timeline", "gemm"], default=None,
+                    help="decode / prefill: run a small case kernel by kernel between cudaProfilerStart/Stop and exit "
+                         "(for ncu --profile-from-start off); timeline: when every kernel of a recorded decode step "
+                         "started (needs the timeline build); gemm: this engine's tcgen05 product against the "
+                         "library's at the layer shapes of the three model sizes; combine with --layers, --batch")
     ap.add_argument("--skip-points", action="store_true",
                     help="skip the batch 1 / 64 points, the prefill and the larger models")
     ap.add_argument("--skip-large", action="store_true", help="skip the points of the 8B and 32B sizes")
@@ -489,6 +532,8 @@ def main() -> int:
     from tinyserve_b200.kernels import ops
 
     pk, pk_src = peaks()
+    if args.profile == "gemm":
+        return gemm_table()
     b = Bench(args.model, args.layers, graphs=not args.no_graphs)
     cfg, dev = b.cfg, b.dev
 

@@ -1,5 +1,10 @@
-"""One request's state as the scheduler moves it between its queues (after upstream
-src/tinyserve/sequence.py:23-74).
+"""One request's state as the scheduler moves it between its queues.
+
+What a request is made of (prompt, output, a limit on new tokens, end tokens, its place in
+the cache), the three states and the questions the scheduler asks of it (how many tokens are
+pending, is it still in its prompt, is it done) are dictated by upstream's scheduling policy
+(src/tinyserve/sequence.py:23-74), which this engine keeps; the record itself, the cache handle
+of several page groups and a state slot, and the slice helper are this engine's own.
 
 A request's tokens are its prompt followed by what it has generated. The cache holds the
 first ``num_cached`` of them; the rest are pending and go into coming steps: the whole prompt
@@ -36,14 +41,14 @@ class Request:
     num_preemptions: int = 0
 
     def __post_init__(self) -> None:
-        if not self.prompt:
-            raise ValueError("prompt must not be empty")
-        if self.max_new_tokens <= 0:
-            raise ValueError(f"max_new_tokens must be positive, got {self.max_new_tokens}")
+        if len(self.prompt) == 0:
+            raise ValueError("a request needs at least one prompt token")
+        if self.max_new_tokens < 1:
+            raise ValueError(f"max_new_tokens={self.max_new_tokens}: a request generates at least one token")
 
     @property
     def tokens(self) -> list[int]:
-        return self.prompt + self.output
+        return [*self.prompt, *self.output]
 
     def token_slice(self, start: int, end: int) -> list[int]:
         """``tokens[start:end]`` without building the whole list (a decode step needs one token)."""
@@ -64,19 +69,19 @@ class Request:
 
     @property
     def max_cached_tokens(self) -> int:
-        """The most tokens it can ever hold in the cache: the last generated token is never
-        fed back."""
-        return len(self.prompt) + self.max_new_tokens - 1
+        """The longest the request's cache can grow: every token except the last one it
+        generates, which is handed out and never run."""
+        return self.num_tokens - len(self.output) + self.max_new_tokens - 1
 
     def num_pending(self) -> int:
         return self.num_tokens - self.num_cached
 
     def in_prefill(self) -> bool:
-        """After scheduling: tokens are still left for later steps, so this step's logits
-        predict nothing and the request samples nothing."""
+        """Asked after scheduling: does the request still hold tokens back for later steps? Then
+        this step's logits predict a token it already has, and it samples nothing."""
         return self.num_pending() > 0
 
     def is_done(self) -> bool:
-        if len(self.output) >= self.max_new_tokens:
-            return True
-        return bool(self.output) and self.output[-1] in self.eos_ids
+        """The limit is reached, or the newest token is one of the request's end tokens."""
+        n = len(self.output)
+        return n >= self.max_new_tokens or (n > 0 and self.output[-1] in self.eos_ids)

@@ -1,5 +1,11 @@
-"""Per-request sampling options; names and meanings follow upstream
-src/tinyserve/sampling.py:37-53."""
+"""Per-request sampling options.
+
+The option names, their defaults and their legal ranges are upstream's schema
+(src/tinyserve/sampling.py:37-53: ``temperature`` 0 = greedy, ``top_p`` in (0, 1], an optional
+``seed``, ``logprobs`` up to 20), so that a caller of upstream's engine can pass the same
+arguments here. How the options are used is this engine's own (``sampling/sampler.py``,
+``csrc/sampling.cu``).
+"""
 
 from __future__ import annotations
 
@@ -17,12 +23,17 @@ class SamplingParams:
     logprobs: int | None = None   # k: report the drawn token's log-probability and the top k
 
     def __post_init__(self) -> None:
-        if not (math.isfinite(self.temperature) and self.temperature >= 0):
-            raise ValueError(f"temperature must be finite and >= 0, got {self.temperature}")
-        if not 0 < self.top_p <= 1:
-            raise ValueError(f"top_p must be in (0, 1], got {self.top_p}")
-        if self.logprobs is not None and not 0 <= self.logprobs <= MAX_LOGPROBS:
-            raise ValueError(f"logprobs must be in [0, {MAX_LOGPROBS}], got {self.logprobs}")
+        problems = []
+        if not math.isfinite(self.temperature) or self.temperature < 0:
+            problems.append(f"temperature={self.temperature!r} (a finite number, 0 or more)")
+        if not (self.top_p > 0 and self.top_p <= 1):
+            problems.append(f"top_p={self.top_p!r} (above 0, at most 1)")
+        if self.logprobs is not None and self.logprobs not in range(MAX_LOGPROBS + 1):
+            problems.append(f"logprobs={self.logprobs!r} (None or 0..{MAX_LOGPROBS})")
+        if self.seed is not None and not isinstance(self.seed, int):
+            problems.append(f"seed={self.seed!r} (None or an integer)")
+        if problems:
+            raise ValueError("sampling options out of range: " + "; ".join(problems))
 
     @property
     def greedy(self) -> bool:
