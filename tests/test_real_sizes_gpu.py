@@ -86,9 +86,9 @@ def real_8b(tmp_path_factory):
 def test_8b_layer_widths_under_every_cut(real_8b, dtype, monkeypatch) -> None:
     """At these widths another set of kernels runs than at the 0.6B ones: the decode rows' products
     leave the skinny kernel for the library (the matrices are larger than it is tuned for), the
-    norms run as kernels of their own (the stream is wider than the fusion takes), the output and
-    down projections of many rows go to the tcgen05 product (4,096 columns), and four query heads
-    share a kv head. The test also checks that those are the kernels that ran."""
+    norms run as kernels of their own (the stream is wider than the fusion takes), products of a
+    hundred-odd rows go to the library too (their tiles would not fill the machine), and four
+    query heads share a kv head. The test also checks that those are the kernels that ran."""
     from tinyserve_b200.kernels import ops
     from tinyserve_b200.model import DecoderModel
 
@@ -115,7 +115,43 @@ def test_8b_layer_widths_under_every_cut(real_8b, dtype, monkeypatch) -> None:
     ops.check_device_errors()
     assert seen["norm"] > 0 and seen["normed"] == 0
     if dtype == torch.bfloat16:
-        assert seen["mm"] > 0 and seen["tcgen05"] > 0 and seen["fused_attention"] > 0
+        # (the only tcgen05 product here is the output head over a whole prompt's 150 rows: 1,188 tiles)
+        assert seen["mm"] > 100 and seen["tcgen05"] <= 2 and seen["fused_attention"] > 0
         assert seen["skinny"] > 0          # the output head of a few rows still streams through the skinny kernel
     else:
         assert seen["mm"] == 0 and seen["tcgen05"] == 0
+
+
+def test_8b_layer_widths_long_prompt_on_the_tcgen05_products(real_8b, monkeypatch) -> None:
+    """A prompt of 1,100 tokens at the 8B widths: nine row tiles, so the output, gate/up (with the
+    activation in its epilogue) and down products fill the machine and run on this engine's tcgen05
+    kernel, the prompt's attention on the tcgen05 attention kernel; then three tokens decoded one by
+    one. Logits at the tile edges and at the end against the plain implementation."""
+    from test_recorded_steps_gpu import plain_rows
+    from test_replay_gpu import close_enough
+    from tinyserve_b200.engine.replay import Replayer
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.model import DecoderModel
+
+    seen = {"tcgen05": 0, "swiglu": 0}
+    plain_gemm, fused = ops.gemm_tcgen05, ops._fn("ts_gemm_tcgen05_swiglu")
+    monkeypatch.setattr(ops, "gemm_tcgen05", lambda *a, **k: (seen.__setitem__("tcgen05", seen["tcgen05"] + 1), plain_gemm(*a, **k))[1])
+    monkeypatch.setitem(ops._fns, "ts_gemm_tcgen05_swiglu",
+                        lambda *a: (seen.__setitem__("swiglu", seen["swiglu"] + 1), fused(*a))[1])
+    folder = real_8b[0]
+    pcfg = plain.read_config(folder)
+    w32, w16 = plain.read_weights(folder, torch.float32), plain.read_weights(folder, torch.bfloat16)
+    toks = random_prompt(1103, 151936, 9)
+    rep = Replayer(DecoderModel.from_folder(folder, torch.bfloat16, "cuda"), 1152, page_size=16)
+    for g in rep.cache.groups:
+        g.kv.fill_(float("nan"))
+    places = [0, 127, 128, 1023, 1099]
+    got = [rep.run_step([("a", toks[:1100], places)]).float().cpu()]
+    for i in range(1100, 1103):
+        got.append(rep.run_step([("a", [toks[i]], [0])], ["a"] if i == 1102 else []).float().cpu())
+    ops.check_device_errors()
+    assert seen["tcgen05"] >= 2 and seen["swiglu"] >= 1
+    rows = torch.cat(got)
+    assert not rows.isnan().any()
+    at = places + [1100, 1101, 1102]
+    close_enough(rows, plain_rows(pcfg, w32, toks, at), plain_rows(pcfg, w16, toks, at), torch.bfloat16)

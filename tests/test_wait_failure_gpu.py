@@ -44,14 +44,16 @@ def error_code() -> int:
 
 
 def gemm_case(swiglu: bool):
-    x, w = rnd(256, 256, dtype=BF16, seed=1), rnd(4096, 256, dtype=BF16, seed=2, scale=0.05)
+    rows = 1152        # nine row tiles x sixteen column tiles fill the machine, so the fused product is this kernel
+    x, w = rnd(rows, 256, dtype=BF16, seed=1), rnd(4096, 256, dtype=BF16, seed=2, scale=0.05)
     if swiglu:
-        out = torch.zeros(256, 2048, device="cuda", dtype=BF16)
+        assert ops.tcgen05_fills_the_machine(rows, 2048, 128)
+        out = torch.zeros(rows, 2048, device="cuda", dtype=BF16)
         run = lambda: ops.gemm_swiglu(x, w, out, None)
         want = torch.empty_like(out)
         ref.gemm_swiglu(x, w, want, None)
     else:
-        out = torch.zeros(256, 4096, device="cuda", dtype=BF16)
+        out = torch.zeros(rows, 4096, device="cuda", dtype=BF16)
         run = lambda: ops.gemm_tcgen05(x, w, out, 256)
         want = torch.empty_like(out)
         ref.gemm(x, w, want)

@@ -505,7 +505,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if m <= SKINNY_MAX_ROWS and k % 32 == 0 and n % 16 == 0 and (n * k <= SKINNY_MAX_WEIGHTS or out.dtype != x.dtype):
         gemm_skinny(x, w, out)
         return
-    if m >= TCGEN05_MIN_ROWS and n >= TCGEN05_MIN_COLS and k % 8 == 0:
+    if m >= TCGEN05_MIN_ROWS and n >= TCGEN05_MIN_COLS and k % 8 == 0 and tcgen05_fills_the_machine(m, n, 256):
         gemm_tcgen05(x, w, out, 256)
         return
     _dev(x, "x"), _dev(w, "w"), _dev(out, "out")
@@ -589,6 +589,26 @@ TCGEN05_TILE_N = 256
 # without a tile and stay with the library until the kernel learns to split K).
 TCGEN05_MIN_ROWS = 128
 TCGEN05_MIN_COLS = 2048
+TCGEN05_MIN_FILL = 0.85
+SM_COUNT = 148
+
+
+def tcgen05_fills_the_machine(m: int, n: int, tile_cols: int) -> bool:
+    """Whether the 128 x ``tile_cols`` output tiles of an ``m`` x ``n`` product keep the persistent
+    CTAs of the tcgen05 kernel busy: the tiles fill at least 85 % of the rounds they take (one tile
+    per SM and round). The kernel does not split K, so fewer tiles than SMs, or a nearly empty last
+    round, leave SMs idle for a whole tile's time; those shapes go to the vendor library, which
+    cuts them differently. Measured on B200, kernel by kernel (``python bench.py --profile gemm``):
+    512 rows of the Qwen3-8B shapes (64 to 96 tiles) 27 / 76 / 30 us against the library's 17 / 42 /
+    24 us for o / down / qkv; 2,048 x 5,120 outputs with K = 25,600 (320 tiles, 2.2 rounds) 604
+    against 438 us; where the rounds are full the two are within a tenth of each other. (Cutting
+    the last round's k blocks over all SMs, with the last CTA to arrive adding a tile's parts in
+    the order of K, was written and passed its tests, but the reducing CTA's 128 epilogue threads
+    read a tile's 128 to 384 KB of partial sums with 16 KB in flight, which cost 20 us a launch;
+    the reduction has to go through bulk copies into the then idle operand buffers first.)"""
+    tiles = -(-m // 128) * -(-n // tile_cols)
+    rounds = -(-tiles // SM_COUNT)
+    return tiles >= TCGEN05_MIN_FILL * rounds * SM_COUNT
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_n: int | None = None) -> None:
@@ -618,7 +638,8 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
         _check(_fn("ts_gemm_skinny_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
                                             _stream()), "gemm_swiglu")
         return
-    if x.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and 2 * inter >= TCGEN05_MIN_COLS and k % 8 == 0:
+    if (x.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and 2 * inter >= TCGEN05_MIN_COLS and k % 8 == 0
+            and tcgen05_fills_the_machine(m, inter, 128)):
         # many rows: the tcgen05 product with the activation in its epilogue
         _check(_fn("ts_gemm_tcgen05_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
                                              _error_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_swiglu")
