@@ -557,3 +557,42 @@ def test_timeline_is_empty_without_the_timeline_build() -> None:
     ops.silu_mul(x.to(torch.bfloat16), torch.empty(4, 32, device="cuda", dtype=torch.bfloat16))
     assert ops.build.TIMELINE or ops.timeline() == []
 
+
+
+def test_index_checks_refuse_a_corrupted_table_before_any_launch(monkeypatch) -> None:
+    """With the index checks on, a block-table entry or a cache slot that points outside the cache
+    is refused on the host, before a kernel could follow it; entries that no request reaches may
+    hold anything."""
+    monkeypatch.setattr(ops, "CHECK_INDICES", True)
+    dtype, hq, hkv, d, page, pages = torch.bfloat16, 4, 2, 64, 16, 8
+    k_cache = rnd(pages, hkv, page, d, dtype=dtype, seed=1)
+    v_cache = rnd(pages, hkv, page, d, dtype=dtype, seed=2)
+    q = rnd(2, hq, d, dtype=dtype, seed=3)
+    lens = [40, 17]
+    tables = torch.tensor([[0, 1, 2, 10_000], [3, 4, 10_000, -5]], dtype=torch.int32, device="cuda")
+
+    def ctx():
+        return SimpleNamespace(
+            num_seqs=2, query_lens=[1, 1], cu_query_lens=torch.tensor([0, 1, 2], dtype=torch.int32, device="cuda"),
+            context_lens_dev=torch.tensor(lens, dtype=torch.int32, device="cuda"),
+            decode_seqs=torch.tensor([0, 1], dtype=torch.int32, device="cuda"),
+            prefill_seqs=torch.zeros(2, dtype=torch.int32, device="cuda"), num_decode=2, num_prefill=0,
+            max_query_len=1, max_context_len=max(lens), arena=Arena("cuda"))
+
+    out, want = torch.empty(2, hq * d, device="cuda", dtype=dtype), torch.empty(2, hq * d, device="cuda", dtype=dtype)
+    ops.paged_attention(q, k_cache, v_cache, page, tables, ctx(), d ** -0.5, 0, out)      # the bad entries are out of reach
+    ref.paged_attention(q, k_cache, v_cache, page, tables, ctx(), d ** -0.5, 0, want)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    tables[1, 1] = 8                                                                       # the cache has pages 0..7
+    with pytest.raises(ops.KernelError, match="request 1, entry 1 is page 8"):
+        ops.paged_attention(q, k_cache, v_cache, page, tables, ctx(), d ** -0.5, 0, out)
+    tables[1, 1] = 4
+    lens[0] = 70                                                                           # needs five pages of a table of four
+    with pytest.raises(ops.KernelError, match="needs 5 pages"):
+        ops.paged_attention(q, k_cache, v_cache, page, tables, ctx(), d ** -0.5, 0, out)
+    qkv = rnd(2, (hq + 2 * hkv) * d, dtype=dtype, seed=4)
+    slots = torch.tensor([5, pages * page], dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="cache slot 128 is outside"):
+        ops.qk_norm_rope_write(qkv, torch.empty(2, hq, d, device="cuda", dtype=dtype), None, None, 1e-6, None, None, 0,
+                               False, slots, k_cache, v_cache, page, hq, hkv, d, True)
+    torch.cuda.synchronize()

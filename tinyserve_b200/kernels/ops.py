@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Any, Callable, Sequence
 
 import torch
@@ -237,12 +238,51 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: torch.T
         raise KernelError("qk_norm_rope_write: rotary tables missing or of the wrong shape")
     if slots.shape != (t,):
         raise KernelError("qk_norm_rope_write: one slot per token")
+    if write_kv:
+        _check_indices("qk_norm_rope_write", None, None, page_size, k_cache.shape[0], slots)
     _check(_fn("ts_qk_norm_rope_write")(
         _dev(qkv, "qkv"), _dev(q_out, "q_out"), _opt(q_weight, "q_weight", dt), _opt(k_weight, "k_weight", dt),
         float(eps), _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), int(rotary_dim),
         int(bool(interleaved)), _dev(slots, "slots", torch.int32), _dev(k_cache, "k_cache"),
         _dev(v_cache, "v_cache"), page_size, t, num_heads, num_kv_heads, head_dim, int(bool(write_kv)),
         _code(dt), _stream()), "qk_norm_rope_write")
+
+
+# ------------------------------------------------------------------ index checks
+# TINYSERVE_B200_CHECK_INDICES=1 (or ``ops.CHECK_INDICES = True``): before a kernel that follows
+# block tables or cache slots is launched, the step's indices are read back and checked on the
+# host: every block-table entry that the launch can reach names a page of the cache, every slot
+# lies inside it. A violation raises ``KernelError`` and nothing is launched, so a corrupted table
+# never becomes a read outside the cache. Each check waits for the device: a debugging aid, off in
+# serving (the launchers' own host checks of shapes, sizes and alignment are always on). It plays
+# the part that device-side index asserts play in a debug build, without a device trap.
+CHECK_INDICES = os.environ.get("TINYSERVE_B200_CHECK_INDICES", "") not in ("", "0")
+
+
+def _check_indices(name: str, block_tables: torch.Tensor | None, ctx: Any, page_size: int, num_pages: int,
+                   slots: torch.Tensor | None = None) -> None:
+    if not CHECK_INDICES:
+        return
+    if torch.cuda.is_current_stream_capturing():
+        return                       # nothing can be read back while a step is being recorded
+    if block_tables is not None:
+        lens = ctx.context_lens_dev[: ctx.num_seqs].to(torch.int64)
+        if int(lens.min()) < 1:
+            raise KernelError(f"{name}: a request of the step holds no token")
+        need = (lens + page_size - 1) // page_size
+        if int(need.max()) > block_tables.shape[1]:
+            raise KernelError(f"{name}: a request needs {int(need.max())} pages, its block table holds {block_tables.shape[1]}")
+        cols = torch.arange(block_tables.shape[1], device=block_tables.device)[None, :]
+        used = cols < need[:, None]
+        bad = used & ((block_tables < 0) | (block_tables >= num_pages))
+        if bool(bad.any()):
+            row, col = [int(v) for v in bad.nonzero()[0]]
+            raise KernelError(f"{name}: block table of request {row}, entry {col} is page {int(block_tables[row, col])}; "
+                              f"the cache has pages 0..{num_pages - 1}")
+    if slots is not None and slots.numel():
+        lo, hi = int(slots.min()), int(slots.max())
+        if lo < 0 or hi >= num_pages * page_size:
+            raise KernelError(f"{name}: cache slot {lo if lo < 0 else hi} is outside 0..{num_pages * page_size - 1}")
 
 
 # -------------------------------------------------------------------- attention
@@ -328,6 +368,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         raise KernelError(f"paged_attention: head_dim={d} must be a multiple of 16 up to 256")
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
         raise KernelError("paged_attention: block_tables must be [requests, width]")
+    _check_indices("paged_attention", block_tables, ctx, page_size, k_cache.shape[0])
     num_prefill = ctx.num_prefill
     tma_ok = (dt == torch.bfloat16 and d in (64, 128) and (page_size == 8 or page_size % 16 == 0)
               and k_cache.shape[0] * hkv * page_size < 2 ** 31)
@@ -456,6 +497,7 @@ def decode_attention_fused(qkv: torch.Tensor, q_weight: torch.Tensor | None, k_w
         raise KernelError("decode_attention_fused: a step of decode tokens only, one token per request")
     if (cos is None) != (sin is None) or (cos is not None and tuple(cos.shape) != (t, d // 2)):
         raise KernelError("decode_attention_fused: rotary tables must be [tokens, head_dim / 2]")
+    _check_indices("decode_attention_fused", block_tables, ctx, page_size, k_cache.shape[0], slots)
     ctas = t * hkv * (-(-(num_heads // hkv) // 16))
     splits = choose_splits(ctas, _decode_slots(d, True), ctx.max_context_len // 64, cluster=True)
     part_acc = part_ml = None

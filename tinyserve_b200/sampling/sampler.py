@@ -3,9 +3,13 @@ device-to-host copy of the chosen tokens (the step's only synchronisation).
 
 Every request draws from its own noise stream: a Philox key made of its seed (its own, or one
 derived from the engine's seed and the request's id) and a counter made of how many tokens it
-has drawn so far. So what a request generates does not depend on its batch-mates, on how its
+has drawn so far. So the noise a request draws does not depend on its batch-mates, on how its
 prompt was cut into portions, or on being recomputed after a preemption (upstream keeps a
-``torch.Generator`` per seeded request for the same end, src/tinyserve/engine.py:126-147).
+``torch.Generator`` per seeded request for the same end, src/tinyserve/engine.py:126-147). The
+logits it is applied to are the model's: in float32 they do not depend on the batch either; in
+bfloat16 they do within rounding (decode steps of up to 8 rows fold the RMSNorm into the products
+around it, with other rounding points than the norm kernel that larger steps run), so a bfloat16
+request may draw another token at a near-tie when it runs in a batch of another size.
 """
 
 from __future__ import annotations
