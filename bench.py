@@ -356,24 +356,46 @@ class Bench:
             "layers_of_configuration": self.full_layers,
         }
 
-    def kernel_table(self, batch: int, prompt_len: int, pk: dict) -> dict:
-        """Where a decode step's device time goes, by kernel class: the step is launched kernel by
+    def kernel_table(self, batch: int, prompt_len: int, pk: dict, prefill_tokens: int = 0) -> dict:
+        """Where a step's device time goes, by kernel class: the step is launched kernel by
         kernel with a pair of CUDA events around every call of ``ops`` (no recording, no launch
         overlap; the step is queued behind a spin kernel so that the host's launch time is not in
         it), and the median of three steps is summed per class. ``gb_s`` relates the bytes a call
         must move (its weights, its rows, the cache of the live requests), from its arguments, to
-        its time."""
+        its time; ``tflops`` its multiply-adds (products and attention). The step is a decode step
+        of ``batch`` requests, or, with ``prefill_tokens``, one prompt of that many tokens."""
         from tinyserve_b200.engine.step import StepEntry
         from tinyserve_b200.kernels import ops
 
         torch = self.torch
         saved_graphs, self.graphs = self.graphs, False
-        e = self.prefilled(batch, prompt_len, 16, run_ahead=False)
+        if prefill_tokens:
+            e = self.new_engine(1, prefill_tokens + 8, run_ahead=False)
+            prompt = self.prompts([prefill_tokens])[0]
+            reqs = []
+        else:
+            e = self.prefilled(batch, prompt_len, 16, run_ahead=False)
+            reqs = list(e.requests.values())
         self.graphs = saved_graphs
-        reqs = list(e.requests.values())
         e.runner.tune_launch_overlap = False
         ops.set_programmatic_launch(0)
-        records: list[tuple[str, object, object, float]] = []
+        records: list[tuple[str, object, object, float, float]] = []
+
+        def flops(name: str, a: tuple) -> float:
+            if name == "gemm":
+                return 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
+            if name == "gemm_swiglu":
+                return 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
+            if name == "gemm_to_stream":
+                return 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
+            if name == "gemm_normed":
+                return 2.0 * a[0].shape[0] * a[4].shape[0] * a[4].shape[1]
+            if name in ("paged_attention", "decode_attention_fused"):
+                ctx = a[5] if name == "paged_attention" else a[11]
+                heads, d = (a[0].shape[1], a[0].shape[2]) if name == "paged_attention" else (a[14], a[7].shape[3])
+                pairs = sum(n * (c - n) + n * (n + 1) / 2 for n, c in zip(ctx.query_lens, ctx.context_lens))
+                return 4.0 * heads * d * pairs
+            return 0.0
 
         def nbytes(*ts) -> float:
             return float(sum(t.numel() * t.element_size() for t in ts if isinstance(t, torch.Tensor)))
@@ -414,7 +436,7 @@ class Bench:
                 finally:
                     depth[0] -= 1
                 e_.record()
-                records.append((name, s_, e_, work(name, a)))
+                records.append((name, s_, e_, work(name, a), flops(name, a)))
                 return r
             return timed
 
@@ -426,21 +448,28 @@ class Bench:
             for it in range(5):
                 records.clear()
                 entries = []
+                if prefill_tokens:
+                    req = e.cache.new_request()
+                    e.cache.append(req, prefill_tokens)
+                    entries.append(StepEntry(req, prompt))
                 for r in reqs:
                     e.cache.append(r.cache, 1)
                     entries.append(StepEntry(r.cache, [r.output[-1]]))
                 # the device idles behind a spin kernel while the host queues the whole step, so that
                 # the kernels then run back to back and an event pair brackets device time only
-                torch.cuda._sleep(40_000_000)
-                ops.sample(e.runner.step(entries), out)
+                torch.cuda._sleep(40_000_000 if not prefill_tokens else 100_000_000)
+                ops.sample(e.runner.step(entries), out[: len(entries)])
                 torch.cuda.synchronize()
+                if prefill_tokens:
+                    e.cache.free(req)
                 if it >= 2:
                     acc: dict[str, list[float]] = {}
-                    for name, s_, e_, by in records:
-                        a = acc.setdefault(name, [0.0, 0.0, 0.0])
+                    for name, s_, e_, by, fl in records:
+                        a = acc.setdefault(name, [0.0, 0.0, 0.0, 0.0])
                         a[0] += s_.elapsed_time(e_)
                         a[1] += by
                         a[2] += 1
+                        a[3] += fl
                     rounds.append(acc)
         finally:
             for n in names:
@@ -449,9 +478,12 @@ class Bench:
         table = {}
         for name in rounds[0]:
             ms = statistics.median(r[name][0] for r in rounds)
-            _, by, calls = rounds[0][name]
+            _, by, calls, fl = rounds[0][name]
             table[name] = {"calls": int(calls), "ms": round(ms, 4), "gb_s": round(by / (ms * 1e-3) / 1e9, 1),
                            "hbm_frac": round(by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}
+            if fl:
+                table[name]["tflops"] = round(fl / (ms * 1e-3) / 1e12, 1)
+                table[name]["tensor_frac"] = round(fl / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 3)
         return table
 
 
@@ -637,10 +669,15 @@ def main() -> int:
         b.graphs = not args.no_graphs
         result["step_ms"] = {"recorded": round(ms, 4), "kernel_by_kernel": round(eager_ms, 4),
                              "sum_of_kernel_classes": round(sum(r["ms"] for r in result["kernels"].values()), 4)}
-        width = max(len(n) for n in result["kernels"])
-        print(f"{'kernel class':<{width}} {'calls':>5} {'ms':>8} {'GB/s':>8} {'of HBM peak':>11}", file=sys.stderr)
-        for name, r in sorted(result["kernels"].items(), key=lambda kv: -kv[1]["ms"]):
-            print(f"{name:<{width}} {r['calls']:>5} {r['ms']:>8.4f} {r['gb_s']:>8.1f} {r['hbm_frac']:>11.1%}", file=sys.stderr)
+        result["prefill_kernels"] = b.kernel_table(1, 0, pk, prefill_tokens=2048)
+        for title, table in ((f"decode step, batch {args.batch}", result["kernels"]),
+                             ("one prompt of 2,048 tokens", result["prefill_kernels"])):
+            width = max(len(n) for n in table)
+            print(f"{title}\n{'kernel class':<{width}} {'calls':>5} {'ms':>8} {'GB/s':>8} {'of HBM peak':>11} {'TFLOP/s':>8} "
+                  f"{'of bf16 peak':>12}", file=sys.stderr)
+            for name, r in sorted(table.items(), key=lambda kv: -kv[1]["ms"]):
+                print(f"{name:<{width}} {r['calls']:>5} {r['ms']:>8.4f} {r['gb_s']:>8.1f} {r['hbm_frac']:>11.1%} "
+                      f"{r.get('tflops', 0):>8.1f} {r.get('tensor_frac', 0):>12.1%}", file=sys.stderr)
     check_rel, checks = b.check_rel, b.checks
     if not args.skip_points:
         points: dict[str, float] = {}
