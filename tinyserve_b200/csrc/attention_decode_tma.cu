@@ -205,7 +205,12 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
   extern __shared__ __align__(16) unsigned char dm_raw[];
   __shared__ __align__(8) uint64_t bars[WARPS][DM_STAGES];
   __shared__ int is_last;
-  __shared__ __align__(16) bf16 q_stage[FUSED ? 16 * 128 : 8];     // this CTA's query heads, ready for the mma
+  // this CTA's query heads, ready for the mma. Rows are 8 elements (16 bytes) further apart than a
+  // head is long: the fragment loads below read rows g = 0..7 at the same column, and rows that are
+  // a multiple of 128 bytes apart would all fall into the same banks (an 8-way conflict on each of
+  // the 32 loads of a warp: 320 k conflicts in a launch of 320 CTAs)
+  constexpr int QS = FUSED ? D + 8 : D;
+  __shared__ __align__(16) bf16 q_stage[FUSED ? 16 * (128 + 8) : 8];
   __shared__ __align__(16) bf16 new_kv[FUSED ? 2 * 128 : 8];       // the new token's key and value rows
   pdl_trigger();
   unsigned char* tiles = (unsigned char*)(((uintptr_t)dm_raw + 1023) & ~(uintptr_t)1023);
@@ -306,9 +311,9 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     const float* sn = f.sin_t ? f.sin_t + (size_t)qrow * (D / 2) : nullptr;
     for (int r = warp; r < 16; r += WARPS) {
       if (r < ng) {
-        fused_head_row<D>(row + (size_t)(kvh * G + g0 + r) * D, q_w, f.eps, c, sn, q_stage + r * D, nullptr, lane);
+        fused_head_row<D>(row + (size_t)(kvh * G + g0 + r) * D, q_w, f.eps, c, sn, q_stage + r * QS, nullptr, lane);
       } else {
-        for (int i = lane * 8; i < D; i += 256) *reinterpret_cast<uint4*>(q_stage + r * D + i) = make_uint4(0u, 0u, 0u, 0u);
+        for (int i = lane * 8; i < D; i += 256) *reinterpret_cast<uint4*>(q_stage + r * QS + i) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
     if (owns_last) {
@@ -343,8 +348,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
         const int r = g + 8 * h;
         uint32_t lo_w = 0u, hi_w = 0u;
         if (FUSED || r < ng) {
-          lo_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + kk * 16 + 2 * t);
-          hi_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * D + kk * 16 + 8 + 2 * t);
+          lo_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * QS + kk * 16 + 2 * t);
+          hi_w = *reinterpret_cast<const uint32_t*>(qbase + (size_t)r * QS + kk * 16 + 8 + 2 * t);
         }
         qf[kk][h] = lo_w;
         qf[kk][2 + h] = hi_w;
@@ -468,8 +473,11 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
   }
   __syncthreads();                                 // all warps are done with their tiles
-  float* red = reinterpret_cast<float*>(tiles);    // [WARPS][16][D + 2], reusing the tile memory
-  constexpr int WS = D + 2;
+  // [WARPS][16][D + 8], reusing the tile memory. A row is D sums, the maximum and the weight; rows
+  // are D + 8 floats apart so that the 8-byte stores below (a half-warp: rows g = 0..3, column pairs
+  // t = 0..3) fall into 16 different bank pairs (a stride of D + 2 put up to four lanes on one bank)
+  float* red = reinterpret_cast<float*>(tiles);
+  constexpr int WS = D + 8;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = g + 8 * h;
@@ -477,8 +485,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
       float* w = red + ((size_t)warp * 16 + r) * WS;
 #pragma unroll
       for (int i = 0; i < 2 * D16; ++i) {
-        w[i * 8 + 2 * t] = o[i][2 * h];
-        w[i * 8 + 2 * t + 1] = o[i][2 * h + 1];
+        *reinterpret_cast<float2*>(w + i * 8 + 2 * t) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
       }
       if (t == 0) { w[D] = m[h]; w[D + 1] = l[h]; }
     }
@@ -501,7 +508,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_tma_kernel(const __gri
     if (a.num_splits == 1) {
       ((bf16*)a.out)[((size_t)qrow * a.num_heads + head) * D + d] = __float2bfloat16_rn(num / den);
     } else if constexpr (CLUSTER) {
-      float* part = red + (size_t)WARPS * 16 * WS;          // [16][D + 2]: this range's sums, max and weight
+      float* part = red + (size_t)WARPS * 16 * WS;          // [16][D + 8]: this range's sums, max and weight
       part[r * WS + d] = num;
       if (d == 0) { part[r * WS + D] = mm; part[r * WS + D + 1] = den; }
     } else {
@@ -608,7 +615,7 @@ static int launch_dt_w(const AttnArgs& a, long long cache_rows, int* error_flag,
   const CUtensorMap* mv = cache_map(a.v_cache, cache_rows, D, BR);
   if (mk == nullptr || mv == nullptr) return TS_ERR_UNSUPPORTED;
   const size_t tiles = (size_t)WARPS * DM_STAGES * 2 * DM_TK * D * 2 + 1024;
-  const size_t red = sizeof(float) * (size_t)(WARPS + 1) * 16 * (D + 2) + 1024;     // the warps' results and the CTA's
+  const size_t red = sizeof(float) * (size_t)(WARPS + 1) * 16 * (D + 8) + 1024;     // the warps' results and the CTA's
   const size_t smem = tiles > red ? tiles : red;
   auto kern = decode_attn_tma_kernel<D64, BR, FUSED, WARPS, CLUSTER>;
   if (smem > 48 * 1024) {
