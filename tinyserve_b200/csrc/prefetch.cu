@@ -24,9 +24,44 @@ namespace ts {
 // after it waits for its end).
 __global__ void prefetch_l2_kernel(PrefetchRanges r) { prefetch_piece(r, blockIdx.x * blockDim.x + threadIdx.x); }
 
+// The pages of a paged cache that the listed requests hold, for the keys and for the values: thread
+// (request, page of its table, keys | values, piece) asks for one piece of its page, if the
+// request's context reaches that page. Block tables and lengths are read on the device, so the
+// kernel can be part of a recorded step.
+__global__ void prefetch_pages_kernel(const char* k_base, const char* v_base, unsigned long long page_bytes,
+                                      const int* __restrict__ block_tables, int table_width,
+                                      const int* __restrict__ ctx_lens, int num_seqs, int page_size, int pieces_per_page) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int piece = (int)(idx % pieces_per_page);
+  const int which = (int)((idx / pieces_per_page) & 1);
+  const long long bp = idx / (2 * pieces_per_page);
+  const int p = (int)(bp % table_width), b = (int)(bp / table_width);
+  if (b >= num_seqs || p * page_size >= ctx_lens[b]) return;
+  const int page = block_tables[(size_t)b * table_width + p];
+  const unsigned long long off = (unsigned long long)piece * PF_PIECE;
+  const unsigned long long left = page_bytes - off;
+  const unsigned int n = left < PF_PIECE ? (unsigned int)left : PF_PIECE;
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((which ? v_base : k_base) + (unsigned long long)page * page_bytes + off), "r"(n) : "memory");
+}
+
 }  // namespace ts
 
 using namespace ts;
+
+// Prefetch into L2 the cache pages (keys and values, `page_bytes` each, 16-byte aligned) that the
+// first `num_seqs` requests of `block_tables` [*, table_width] hold up to their `ctx_lens`.
+extern "C" int ts_prefetch_pages(const void* k_cache, const void* v_cache, unsigned long long page_bytes,
+                                 const int* block_tables, int table_width, const int* ctx_lens, int num_seqs,
+                                 int page_size, int threads, cudaStream_t stream) {
+  if (num_seqs <= 0 || table_width <= 0) return 0;
+  if (threads < 16 || threads > 128 || threads % 16 != 0 || page_size <= 0) return TS_ERR_BAD_ARGUMENT;
+  if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache) | page_bytes) & 15) return TS_ERR_UNSUPPORTED;
+  const int pieces = (int)((page_bytes + PF_PIECE - 1) / PF_PIECE);
+  const long long total = (long long)num_seqs * table_width * 2 * pieces;
+  return launch(prefetch_pages_kernel, (unsigned int)((total + threads - 1) / threads), threads, 0, stream,
+                (const char*)k_cache, (const char*)v_cache, page_bytes, block_tables, table_width, ctx_lens, num_seqs,
+                page_size, pieces);
+}
 
 // Prefetch `count` (at most 8) ranges into L2. Every base must be 16-byte aligned; sizes are
 // rounded down to a multiple of 16.

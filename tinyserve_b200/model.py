@@ -222,8 +222,12 @@ class DecoderModel:
                 if key not in ctx.position_tables:
                     ctx.position_tables[key] = layer.position.prepare(ctx)
                 tables = ctx.position_tables[key]
+            ctx.upcoming_caches = parts.caches_of_call(n + 1, caches) if n + 1 < len(self.spec.order) else {}
             layer.block.forward(stream, ctx, parts.caches_of_call(n, caches), call.reads_cache_of is None, tables)
         ctx.arena.step_region()
+        for join in ctx.at_step_end:
+            join()
+        ctx.at_step_end.clear()
         if num_want == 0:
             return None
         hn = parts.final_norm.forward_rows(stream, want_rows, num_want, ctx)

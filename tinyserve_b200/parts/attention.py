@@ -115,6 +115,14 @@ class GQAAttention(Mixer):
                                 self.scale, self.window or 0, attn)
         if join is not None:
             join()
+        nxt = ctx.upcoming_caches.get("mixer")
+        if (ops.PREFETCH_NEXT_CACHE and join is not None and isinstance(nxt, KVCacheEntry) and nxt.k is not cache.k
+                and nxt.group in ctx.kv):
+            # the products that follow read their weights from L2 and leave the memory idle: the next
+            # layer's pages of these requests come into L2 meanwhile (nothing waits for them)
+            later = ops.prefetch_pages_later(nxt.k, nxt.v, ctx.kv[nxt.group].block_tables, ctx, nxt.page_size)
+            if not ctx.at_step_end:
+                ctx.at_step_end.append(later)
         return project_to_stream(attn, self.w_o, stream, ctx)
 
 

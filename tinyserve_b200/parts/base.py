@@ -193,6 +193,12 @@ class StepContext:
     # Weights that the kernels after the current mixer will stream (set by the block): a mixer
     # with a long kernel that leaves memory bandwidth idle may have them fetched into L2 beside it.
     upcoming_weights: list[torch.Tensor] = field(default_factory=list)
+    # The cache entries of the next call of the order, by mixer role (set by the model): a mixer may
+    # have their pages fetched into L2 once its own kernel has gone over the memory.
+    upcoming_caches: Mapping[str, Any] = field(default_factory=dict)
+    # Side branches that a part has opened and that nothing later in the step reads from (such a
+    # prefetch): functions that join them, called once at the end of the step.
+    at_step_end: list[Callable[[], None]] = field(default_factory=list)
 
 
 class ResidualStream:
