@@ -451,6 +451,19 @@ def test_gemm_to_stream_and_normed(m, n, k) -> None:
         held(out, want, torch.nn.functional.silu(gu[:, :n2]) * gu[:, n2:])
 
 
+@pytest.mark.parametrize("m", [9, 16])
+def test_gemm_skinny_streaming_form_with_wide_rows(m) -> None:
+    """The streaming form keeps the rows of x in shared memory; at a width of 4,096 they leave room
+    for one CTA an SM only."""
+    n, k = 75808, 4096
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=1), rnd(n, k, dtype=torch.bfloat16, seed=2, scale=0.02)
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
+    want = torch.empty_like(out)
+    ops.gemm_skinny(x, w, out)
+    ref.gemm(x, w, want)
+    torch.testing.assert_close(out, want, atol=2e-4, rtol=1e-4)
+
+
 def test_gemm_skinny_refuses_what_it_cannot_take() -> None:
     x, w = rnd(4, 80, dtype=torch.bfloat16), rnd(32, 80, dtype=torch.bfloat16)
     with pytest.raises(ops.KernelError, match="not supported"):

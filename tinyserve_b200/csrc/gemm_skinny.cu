@@ -113,9 +113,13 @@ __device__ __forceinline__ uint4 normed_fragment(const uint4& rv, const uint4& w
 }
 
 // WARPS: warps of a CTA, which split K between them (8; 16 in the tall form, see launch_skinny).
+// The forms of up to 16 rows are held to 128 registers so that two CTAs of 8 warps fit an SM: the
+// fused gate/up product of 9 to 16 rows took 146 and ran its 192 CTAs in two rounds (10.4 us in a
+// recorded decode step of 16 rows, against 6.6 us for the 8-row form).
 template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool XRING, bool NORMX = false, bool RESID = false,
           int WARPS = SK_WARPS>
-__global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+__global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 && NT <= 2) ? 2 : 1)
+gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                  TOut* __restrict__ out, int M, int N, int K,
                                                                  SkinnyNorm nrm) {
   static_assert(!(RESID && FUSE), "the fused activation is not added to the stream");
@@ -123,7 +127,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const bf16* __r
   constexpr int KSTEP = WARPS * 32;      // distance between a warp's k blocks
   constexpr int TILES = FUSE ? 2 * RT : RT;
   constexpr int COLS = 8 * NT;
-  extern __shared__ float red[];   // [WARPS][TILES][16][COLS]
+  // a row of partial sums is COLS + 1 long: the threads that add them up take consecutive rows, which
+  // would otherwise fall into two or four banks (16- and 8-fold conflicts on every read)
+  constexpr int CS = COLS + 1;
+  extern __shared__ float red[];   // [WARPS][TILES][16][CS]
   __shared__ int is_last;
   __shared__ float rstd_s[16];
   pdl_trigger();
@@ -251,16 +258,16 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const bf16* __r
     }
   }
   // partial sums of this warp -> shared memory; element (row, col) of tile (r, j)
-  float* mine = red + (size_t)warp * TILES * 16 * COLS;
+  float* mine = red + (size_t)warp * TILES * 16 * CS;
 #pragma unroll
   for (int r = 0; r < TILES; ++r)
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
-      float* tile = mine + (size_t)r * 16 * COLS + j * 8;
-      tile[g * COLS + 2 * t] = acc[r][j][0];
-      tile[g * COLS + 2 * t + 1] = acc[r][j][1];
-      tile[(g + 8) * COLS + 2 * t] = acc[r][j][2];
-      tile[(g + 8) * COLS + 2 * t + 1] = acc[r][j][3];
+      float* tile = mine + (size_t)r * 16 * CS + j * 8;
+      tile[g * CS + 2 * t] = acc[r][j][0];
+      tile[g * CS + 2 * t + 1] = acc[r][j][1];
+      tile[(g + 8) * CS + 2 * t] = acc[r][j][2];
+      tile[(g + 8) * CS + 2 * t + 1] = acc[r][j][3];
     }
   __syncthreads();
   // thread -> (column m, weight row): consecutive threads take consecutive weight rows, so a
@@ -289,10 +296,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const bf16* __r
     float s = 0.f, u = 0.f;
     if (m < M) {
 #pragma unroll
-      for (int wq = 0; wq < WARPS; ++wq) s += red[(size_t)wq * TILES * 16 * COLS + row * COLS + m];
+      for (int wq = 0; wq < WARPS; ++wq) s += red[(size_t)wq * TILES * 16 * CS + row * CS + m];
       if constexpr (FUSE) {
 #pragma unroll
-        for (int wq = 0; wq < WARPS; ++wq) u += red[(size_t)wq * TILES * 16 * COLS + (RT * 16 + row) * COLS + m];
+        for (int wq = 0; wq < WARPS; ++wq) u += red[(size_t)wq * TILES * 16 * CS + (RT * 16 + row) * CS + m];
       }
       if (ksplit > 1) {
         part[(size_t)m * width + n0 + row] = s;
@@ -354,7 +361,7 @@ template <typename TOut, int NT, int RT, bool FUSE, int SK_PF, bool NORMX = fals
 static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream,
                          const SkinnyNorm& nrm = SkinnyNorm()) {
   constexpr int TILES = FUSE ? 2 * RT : RT;
-  const size_t smem = sizeof(float) * SK_WARPS * TILES * 16 * 8 * NT;
+  const size_t smem = sizeof(float) * SK_WARPS * TILES * 16 * (8 * NT + 1);
   // Split K across CTAs when the row tiles alone leave most SMs idle.
   const int tiles = N / (16 * RT);
   int ksplit = 1;
@@ -362,7 +369,7 @@ static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, 
     while (ksplit < SK_MAX_SPLIT && tiles * ksplit < 148 && K % (64 * ksplit) == 0 && K / (2 * ksplit) >= SK_KSTEP)
       ksplit *= 2;
   }
-  constexpr bool CAN_RING = (!FUSE && RT == 1 && NT == 1);
+  constexpr bool CAN_RING = (!FUSE && RT == 1 && NT <= 2);
   const bool ring = CAN_RING && K / ksplit <= SK_PF * SK_KSTEP;
   // The tall form: when the row tiles alone leave SMs idle and a CTA of 16 warps can have its
   // whole share of the weights in flight (6 k blocks a warp: K up to 3,072), K is split between
@@ -372,7 +379,7 @@ static int launch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, 
   if constexpr (CAN_RING && !NORMX) {
     if (ksplit > 1 && K <= SK_TALL_PF * SK_TALL_WARPS * 32) {
       auto tall = gemm_skinny_kernel<TOut, NT, RT, FUSE, SK_TALL_PF, true, NORMX, RESID, SK_TALL_WARPS>;
-      const size_t tall_smem = sizeof(float) * SK_TALL_WARPS * TILES * 16 * 8 * NT;
+      const size_t tall_smem = sizeof(float) * SK_TALL_WARPS * TILES * 16 * (8 * NT + 1);
       return launch(tall, dim3(tiles, 1), SK_TALL_WARPS * 32, tall_smem, stream, x, w, out, M, N, K, nrm);
     }
   }
@@ -402,15 +409,23 @@ static int row_tiles_for(int N, int most) {
 // requests never pause. (With one tile per CTA, a CTA's loads stop while it reduces and stores,
 // and the next CTA on the SM starts with an empty pipeline: 16 rows on the head of 151,936 x 1,024
 // take 184 us that way and 103 us in this form.)
+// The rows of x are the same for every tile, so the CTA copies them to shared memory once and takes
+// its B fragments from there: read from L2 for every tile instead, 16 rows of x were half as many
+// bytes again as the weights themselves (134 us for that head inside a decode step of 16 rows, 73 us
+// with 9 rows). A row of x in shared memory is K + 32 values long, so that the two rows that a
+// quarter warp reads with one 16-byte load per lane fall into different halves of the banks.
 // K must be a multiple of SK_ST_PF * 256, so that the ring of weight registers turns over in step
 // with the tiles.
 constexpr int SK_ST_PF = 4;
+constexpr int SK_ST_XPAD = 32;
 template <typename TOut, int NT, int RT>
 __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const bf16* __restrict__ x,
                                                                         const bf16* __restrict__ w,
                                                                         TOut* __restrict__ out, int M, int N, int K) {
-  constexpr int PF = SK_ST_PF, COLS = 8 * NT;
-  extern __shared__ float red[];   // [SK_WARPS][RT][16][COLS]
+  constexpr int PF = SK_ST_PF, COLS = 8 * NT, CS = COLS + 1;      // CS: see gemm_skinny_kernel
+  extern __shared__ __align__(16) float red[];   // [SK_WARPS][RT][16][CS], then x [COLS][K + SK_ST_XPAD] bf16
+  bf16* xs = reinterpret_cast<bf16*>(red + SK_WARPS * RT * 16 * CS);
+  const int xstride = K + SK_ST_XPAD;
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -429,14 +444,19 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
       }
   }
   pdl_wait();
-  const bf16* xrow[NT];
-  bool xok[NT];
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    const int m = 8 * j + g;
-    xok[j] = m < M;
-    xrow[j] = x + (size_t)(xok[j] ? m : 0) * K + 8 * t + warp * 32;
+  // x -> shared memory, rows from M on as zeros
+  {
+    const int per_row = K / 8;
+    for (int idx = threadIdx.x; idx < COLS * per_row; idx += SK_THREADS) {
+      const int m = idx / per_row, c = idx - m * per_row;
+      const uint4 v = m < M ? ld_cg(x + (size_t)m * K + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(xs + (size_t)m * xstride + 8 * c) = v;
+    }
   }
+  __syncthreads();
+  const bf16* xrow[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) xrow[j] = xs + (size_t)(8 * j + g) * xstride + 8 * t + warp * 32;
   for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
     const bool has_next = tile + (int)gridDim.x < tiles;
     const bf16* cur = lane_w + (size_t)tile * tile_stride;
@@ -454,7 +474,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
         const int kb = kb0 + p * SK_KSTEP;
         uint4 b[NT];
 #pragma unroll
-        for (int j = 0; j < NT; ++j) b[j] = xok[j] ? ld_cached(xrow[j] + kb) : make_uint4(0u, 0u, 0u, 0u);
+        for (int j = 0; j < NT; ++j) b[j] = *reinterpret_cast<const uint4*>(xrow[j] + kb);
 #pragma unroll
         for (int r = 0; r < RT; ++r)
 #pragma unroll
@@ -474,16 +494,16 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
         }
       }
     }
-    float* mine = red + (size_t)warp * RT * 16 * COLS;
+    float* mine = red + (size_t)warp * RT * 16 * CS;
 #pragma unroll
     for (int r = 0; r < RT; ++r)
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        float* tl = mine + (size_t)r * 16 * COLS + j * 8;
-        tl[g * COLS + 2 * t] = acc[r][j][0];
-        tl[g * COLS + 2 * t + 1] = acc[r][j][1];
-        tl[(g + 8) * COLS + 2 * t] = acc[r][j][2];
-        tl[(g + 8) * COLS + 2 * t + 1] = acc[r][j][3];
+        float* tl = mine + (size_t)r * 16 * CS + j * 8;
+        tl[g * CS + 2 * t] = acc[r][j][0];
+        tl[g * CS + 2 * t + 1] = acc[r][j][1];
+        tl[(g + 8) * CS + 2 * t] = acc[r][j][2];
+        tl[(g + 8) * CS + 2 * t + 1] = acc[r][j][3];
       }
     __syncthreads();
     const int n0 = tile * 16 * RT;
@@ -492,7 +512,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
       if (m < M) {
         float sum = 0.f;
 #pragma unroll
-        for (int wq = 0; wq < SK_WARPS; ++wq) sum += red[(size_t)wq * RT * 16 * COLS + row * COLS + m];   // a fixed order
+        for (int wq = 0; wq < SK_WARPS; ++wq) sum += red[(size_t)wq * RT * 16 * CS + row * CS + m];   // a fixed order
         out[(size_t)m * N + n0 + row] = from_float<TOut>(sum);
       }
     }
@@ -500,12 +520,24 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
   }
 }
 
+// Shared memory of the streaming form: the partial sums and the rows of x.
+template <int NT, int RT>
+static size_t skinny_stream_smem(int K) {
+  return sizeof(float) * SK_WARPS * RT * 16 * (8 * NT + 1) + sizeof(bf16) * 8 * NT * (size_t)(K + SK_ST_XPAD);
+}
+constexpr size_t SK_ST_MAX_SMEM = 200 * 1024;      // one CTA an SM; up to half of it, two
+
 template <typename TOut, int NT, int RT>
 static int launch_skinny_stream(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
   const int tiles = N / (16 * RT);
-  const size_t smem = sizeof(float) * SK_WARPS * RT * 16 * 8 * NT;
+  const size_t smem = skinny_stream_smem<NT, RT>(K);
   auto kern = gemm_skinny_stream_kernel<TOut, NT, RT>;
-  return launch(kern, dim3(tiles < 2 * 148 ? tiles : 2 * 148), SK_THREADS, smem, stream, x, w, out, M, N, K);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int ctas = (smem <= SK_ST_MAX_SMEM / 2 ? 2 : 1) * 148;
+  return launch(kern, dim3(tiles < ctas ? tiles : ctas), SK_THREADS, smem, stream, x, w, out, M, N, K);
 }
 
 template <typename TOut, int NT>
@@ -515,7 +547,7 @@ static int dispatch_skinny_nt(const bf16* x, const bf16* w, TOut* out, int M, in
     // 9 to 16 rows and at least eight tiles for each CTA. (Up to 8 rows the streaming form is
     // faster alone, 64 against 71 us for the head of 151,936 x 1,024, but slower inside a decode
     // step, 110 against 77 us, for a reason that was not found; so those keep one tile per CTA.)
-    if (rt == 2 && K % (SK_ST_PF * SK_KSTEP) == 0 && N / 32 >= 8 * 2 * 148)
+    if (rt == 2 && K % (SK_ST_PF * SK_KSTEP) == 0 && N / 32 >= 8 * 2 * 148 && skinny_stream_smem<NT, 2>(K) <= SK_ST_MAX_SMEM)
       return launch_skinny_stream<TOut, NT, 2>(x, w, out, M, N, K, stream);
   }
   if (rt == 2) return launch_skinny<TOut, NT, 2, false, 4>(x, w, out, M, N, K, stream);
