@@ -416,8 +416,15 @@ static int row_tiles_for(int N, int most) {
 // quarter warp reads with one 16-byte load per lane fall into different halves of the banks.
 // K must be a multiple of SK_ST_PF * 256, so that the ring of weight registers turns over in step
 // with the tiles.
+// A CTA takes its first tile by its index and claims every further one from a counter, one tile
+// ahead: inside a decode step some CTAs start late (the kernels before and after hold part of the
+// machine: the sampling kernel's CTAs are launched early and wait for this one), and with a fixed
+// share of tiles per CTA the late ones set the kernel's time (16 rows on that head: 59 us alone,
+// 105 us inside a step). The CTA that finishes last puts the counters back, so launches of this
+// kernel must not overlap (as for the products that split K across CTAs).
 constexpr int SK_ST_PF = 4;
 constexpr int SK_ST_XPAD = 32;
+static __device__ unsigned int g_stream_claimed, g_stream_finished;
 template <typename TOut, int NT, int RT>
 __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const bf16* __restrict__ x,
                                                                         const bf16* __restrict__ w,
@@ -425,6 +432,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
   constexpr int PF = SK_ST_PF, COLS = 8 * NT, CS = COLS + 1;      // CS: see gemm_skinny_kernel
   extern __shared__ __align__(16) float red[];   // [SK_WARPS][RT][16][CS], then x [COLS][K + SK_ST_XPAD] bf16
   bf16* xs = reinterpret_cast<bf16*>(red + SK_WARPS * RT * 16 * CS);
+  __shared__ int next_tile_s;
   const int xstride = K + SK_ST_XPAD;
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -444,6 +452,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
       }
   }
   pdl_wait();
+  if (threadIdx.x == 0) next_tile_s = (int)(gridDim.x + atomicAdd(&g_stream_claimed, 1u));
   // x -> shared memory, rows from M on as zeros
   {
     const int per_row = K / 8;
@@ -457,10 +466,14 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
   const bf16* xrow[NT];
 #pragma unroll
   for (int j = 0; j < NT; ++j) xrow[j] = xs + (size_t)(8 * j + g) * xstride + 8 * t + warp * 32;
-  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-    const bool has_next = tile + (int)gridDim.x < tiles;
+  int next_tile = next_tile_s;
+  for (int tile = blockIdx.x; tile < tiles;) {
+    const bool has_next = next_tile < tiles;
     const bf16* cur = lane_w + (size_t)tile * tile_stride;
-    const bf16* nxt_tile = cur + (size_t)gridDim.x * tile_stride;
+    const bf16* nxt_tile = lane_w + (size_t)next_tile * tile_stride;
+    // the tile after the next one: claimed now, needed when this tile is done
+    int after = tiles;
+    if (threadIdx.x == 0 && has_next) after = (int)(gridDim.x + atomicAdd(&g_stream_claimed, 1u));
     float acc[RT][NT][4];
 #pragma unroll
     for (int r = 0; r < RT; ++r)
@@ -516,7 +529,15 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_stream_kernel(const
         out[(size_t)m * N + n0 + row] = from_float<TOut>(sum);
       }
     }
+    if (threadIdx.x == 0) next_tile_s = after;
     __syncthreads();      // the sums are read; the next tile may overwrite them
+    tile = next_tile;
+    next_tile = next_tile_s;
+  }
+  if (threadIdx.x == 0 && atomicAdd(&g_stream_finished, 1u) == gridDim.x - 1) {
+    g_stream_claimed = 0;      // every CTA has made its last claim
+    g_stream_finished = 0;
+    __threadfence();
   }
 }
 
@@ -543,10 +564,9 @@ static int launch_skinny_stream(const bf16* x, const bf16* w, TOut* out, int M, 
 template <typename TOut, int NT>
 static int dispatch_skinny_nt(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
   const int rt = row_tiles_for(N, 2);
-  if constexpr (NT == 2) {
-    // 9 to 16 rows and at least eight tiles for each CTA. (Up to 8 rows the streaming form is
-    // faster alone, 64 against 71 us for the head of 151,936 x 1,024, but slower inside a decode
-    // step, 110 against 77 us, for a reason that was not found; so those keep one tile per CTA.)
+  if constexpr (NT <= 2) {
+    // up to 16 rows and at least eight tiles for each CTA (the head of 151,936 x 1,024 inside a decode
+    // step: 8 rows 62 us with one tile per CTA and 53 us in this form; 16 rows 53 us)
     if (rt == 2 && K % (SK_ST_PF * SK_KSTEP) == 0 && N / 32 >= 8 * 2 * 148 && skinny_stream_smem<NT, 2>(K) <= SK_ST_MAX_SMEM)
       return launch_skinny_stream<TOut, NT, 2>(x, w, out, M, N, K, stream);
   }

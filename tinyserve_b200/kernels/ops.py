@@ -323,6 +323,7 @@ def decode_splits(num_decode: int, num_kv_heads: int, group: int, max_context_le
 CLUSTER_MERGE = True       # the TMA decode kernel merges 2 to 8 key ranges inside a thread-block cluster
 CLUSTER_MAX = 8            # the portable cluster size
 CLUSTER_ROOM = 16          # CTA slots left free per CTA of a cluster
+CLUSTER_FILL = 0.82        # and clusters of three or more fill at most this much of the machine
 
 
 def choose_splits(ctas: int, slots: int, most: int, cluster: bool = False) -> int:
@@ -337,12 +338,15 @@ def choose_splits(ctas: int, slots: int, most: int, cluster: bool = False) -> in
     kernel before it is still leaving. The more CTAs a cluster has, the more of the machine must
     stay free for that: measured at batch 1 to 24 (16 / 8 heads of 128), the best number of ranges
     was each time the largest s <= 8 with ``s * ctas <= slots - 16 s`` (batch 8: 5 ranges, 0.95 ms
-    a step; 6 ranges, which fill 86% of the slots, 1.04 ms; without clusters 1.02 ms)."""
+    a step; 6 ranges, which fill 86% of the slots, 1.04 ms; without clusters 1.02 ms), except at
+    batch 16, where 3 ranges pass that rule and fill 86%: 1.31 ms a step, with now and then a layer
+    whose attention takes twice as long, against 1.21 ms with 2 ranges. Hence the second bound on
+    what clusters of three or more may fill."""
     if 2 * ctas > slots:
         return 1
     if cluster and CLUSTER_MERGE:
         for s in range(min(CLUSTER_MAX, most, MAX_SPLITS), 1, -1):
-            if s * ctas <= slots - CLUSTER_ROOM * s:
+            if s * ctas <= slots - CLUSTER_ROOM * s and (s == 2 or s * ctas <= CLUSTER_FILL * slots):
                 return s
         return 1
     return max(1, min(slots // ctas, most, 12, MAX_SPLITS))
