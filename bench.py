@@ -508,8 +508,9 @@ def gemm_table() -> int:
         torch.cuda.synchronize()
         return s_.elapsed_time(e_) / 20 * 1e3
 
-    print(f"{'rows':>5} {'shape':<14} {'N':>6} {'K':>6} {'library us':>10} {'TFLOP/s':>8} {'tcgen05 us':>10} {'TFLOP/s':>8}")
-    for m in (512, 2048):
+    print(f"{'rows':>5} {'shape':<14} {'N':>6} {'K':>6} {'library us':>10} {'TFLOP/s':>8} {'tcgen05 us':>10} {'TFLOP/s':>8} "
+          f"{'by pairs us':>11} {'TFLOP/s':>8}")
+    for m in (512, 2048, 8192):
         for name, d in MODELS.items():
             h, inter = d["hidden_size"], d["intermediate_size"]
             q, kv = d["num_attention_heads"] * d["head_dim"], d["num_key_value_heads"] * d["head_dim"]
@@ -519,8 +520,10 @@ def gemm_table() -> int:
                 out = torch.empty(m, n, device=dev, dtype=bf)
                 lib = timed(lambda: torch.mm(x, w.t(), out=out))
                 own = timed(lambda: ops.gemm_tcgen05(x, w, out, 256))
+                pair = timed(lambda: ops.gemm_tcgen05(x, w, out, ops.TCGEN05_PAIR_TILE))
                 fl = 2.0 * m * n * k
-                print(f"{m:>5} {name + ' ' + what:<14} {n:>6} {k:>6} {lib:>10.1f} {fl / lib / 1e6:>8.0f} {own:>10.1f} {fl / own / 1e6:>8.0f}")
+                print(f"{m:>5} {name + ' ' + what:<14} {n:>6} {k:>6} {lib:>10.1f} {fl / lib / 1e6:>8.0f} {own:>10.1f} {fl / own / 1e6:>8.0f} "
+                      f"{pair:>11.1f} {fl / pair / 1e6:>8.0f}")
                 del w, x, out
     ops.check_device_errors()
     return 0

@@ -398,6 +398,24 @@ def test_gemm_swiglu(dtype, m, inter, k) -> None:
     torch.testing.assert_close(out.float(), want.float(), **t)
 
 
+@pytest.mark.parametrize("m", [128, 300, 1152, 2048])
+@pytest.mark.parametrize("inter,k", [(3072, 1024), (1024, 64), (1100, 200), (12288, 4096)])
+def test_gemm_swiglu_by_pairs_of_ctas(m, inter, k, monkeypatch) -> None:
+    """The tcgen05 product with the activation in its epilogue, 256 x 256 tiles by pairs of CTAs: the even
+    CTA of a pair loads the gate rows, the odd one the up rows."""
+    monkeypatch.setattr(ops, "TCGEN05_PAIR", True)
+    monkeypatch.setattr(ops, "TCGEN05_MIN_FILL", 0.0)
+    monkeypatch.setattr(ops, "TCGEN05_MIN_COLS", 0)
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1)
+    w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=2, scale=0.1 if k < 2048 else 0.03)
+    out = torch.full((m, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
+    want = torch.empty_like(out)
+    ops.gemm_swiglu(x, w, out, Arena("cuda"))
+    ops.check_device_errors()
+    ref.gemm_swiglu(x, w, want)
+    torch.testing.assert_close(out.float(), want.float(), atol=3e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(1024, 2048), (1024, 3072), (96, 64), (2048, 1024), (48, 1024)])
 def test_gemm_to_stream_and_normed(m, n, k) -> None:
@@ -476,7 +494,7 @@ def test_gemm_skinny_refuses_what_it_cannot_take() -> None:
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("tile_n", [64, 128, 256, ops.TCGEN05_PAIR_TILE])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 256), (1, 72, 80), (200, 1000, 1024), (2048, 4096, 1024),
                                    (300, 1024, 3072), (77, 151936, 1024), (129, 130, 136)])
 def test_gemm_tcgen05(out_dtype, tile_n, m, n, k) -> None:

@@ -43,26 +43,28 @@ def error_code() -> int:
     return int(ops._error_word(torch.device("cuda", torch.cuda.current_device())).item())
 
 
-def gemm_case(swiglu: bool):
-    rows = 1152        # nine row tiles x sixteen column tiles fill the machine, so the fused product is this kernel
+def gemm_case(swiglu: bool, pairs: bool):
+    # single CTAs: nine row tiles x sixteen column tiles fill the machine; pairs: nine 256-row tiles x sixteen
+    rows = 2304 if pairs else 1152
     x, w = rnd(rows, 256, dtype=BF16, seed=1), rnd(4096, 256, dtype=BF16, seed=2, scale=0.05)
     if swiglu:
-        assert ops.tcgen05_fills_the_machine(rows, 2048, 128)
+        assert ops.tcgen05_tiles(rows, 2048, 128) == ("pairs" if pairs else "single")
         out = torch.zeros(rows, 2048, device="cuda", dtype=BF16)
         run = lambda: ops.gemm_swiglu(x, w, out, None)
         want = torch.empty_like(out)
         ref.gemm_swiglu(x, w, want, None)
     else:
         out = torch.zeros(rows, 4096, device="cuda", dtype=BF16)
-        run = lambda: ops.gemm_tcgen05(x, w, out, 256)
+        run = lambda: ops.gemm_tcgen05(x, w, out, ops.TCGEN05_PAIR_TILE if pairs else 256)
         want = torch.empty_like(out)
         ref.gemm(x, w, want)
     return run, out, want
 
 
+@pytest.mark.parametrize("pairs", [False, True])
 @pytest.mark.parametrize("swiglu", [False, True])
-def test_gemm_tcgen05_gives_up_and_recovers(swiglu) -> None:
-    run, out, want = gemm_case(swiglu)
+def test_gemm_tcgen05_gives_up_and_recovers(swiglu, pairs) -> None:
+    run, out, want = gemm_case(swiglu, pairs)
     with lost_copies():
         run()
         assert error_code() == 1

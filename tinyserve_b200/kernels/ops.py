@@ -56,7 +56,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_skinny": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
-    "ts_gemm_tcgen05_swiglu": [_vp, _vp, _vp, _i, _i, _i, _vp, _vp],
+    "ts_gemm_tcgen05_swiglu": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _fns: dict[str, Any] = {}
@@ -552,9 +552,11 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if m <= SKINNY_MAX_ROWS and k % 32 == 0 and n % 16 == 0 and (n * k <= SKINNY_MAX_WEIGHTS or out.dtype != x.dtype):
         gemm_skinny(x, w, out)
         return
-    if m >= TCGEN05_MIN_ROWS and n >= TCGEN05_MIN_COLS and k % 8 == 0 and tcgen05_fills_the_machine(m, n, 256):
-        gemm_tcgen05(x, w, out, 256)
-        return
+    if m >= TCGEN05_MIN_ROWS and n >= TCGEN05_MIN_COLS and k % 8 == 0:
+        tiles = tcgen05_tiles(m, n, 256)
+        if tiles:
+            gemm_tcgen05(x, w, out, TCGEN05_PAIR_TILE if tiles == "pairs" else 256)
+            return
     _dev(x, "x"), _dev(w, "w"), _dev(out, "out")
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)                       # vendor library matrix product
@@ -630,6 +632,12 @@ def set_wait_control(cycles: int | None = None, unarmed: bool = False) -> None:
 
 # Default output-tile width of the tcgen05 product.
 TCGEN05_TILE_N = 256
+# 256-row tiles by pairs of CTAs (tcgen05 cta_group::2) where they fill the machine: a CTA then fetches a
+# third less from L2 per flop. Measured on B200 (``python bench.py --profile gemm``), 2,048 rows, library /
+# one CTA a tile / pairs: Qwen3-8B gate-up 267 / 291 / 275 us, Qwen3-32B gate-up 651 / 739 / 694 us;
+# 8,192 rows of the Qwen3-8B o shape 221 / 228 / 194 us; level at the Qwen3-0.6B shapes.
+TCGEN05_PAIR = True
+TCGEN05_PAIR_TILE = 512      # the value of ``tile_n`` that asks for them
 # The tcgen05 kernel takes the bf16 products with at least this many rows and output columns
 # (measured on B200 at 2,048 rows: 17.9 / 26.6 / 564 us against the vendor library's 15.3 / 21.5 /
 # 473 us for the qkv, gate-up and head shapes of Qwen3-0.6B; narrower outputs leave most SMs
@@ -656,6 +664,21 @@ def tcgen05_fills_the_machine(m: int, n: int, tile_cols: int) -> bool:
     tiles = -(-m // 128) * -(-n // tile_cols)
     rounds = -(-tiles // SM_COUNT)
     return tiles >= TCGEN05_MIN_FILL * rounds * SM_COUNT
+
+
+def tcgen05_pairs_fill_the_machine(m: int, n: int, tile_cols: int) -> bool:
+    """The same for tiles of 256 rows, each computed by a pair of CTAs (one tile per pair of SMs and round)."""
+    tiles = -(-m // 256) * -(-n // tile_cols)
+    rounds = -(-tiles // (SM_COUNT // 2))
+    return tiles >= TCGEN05_MIN_FILL * rounds * (SM_COUNT // 2)
+
+
+def tcgen05_tiles(m: int, n: int, tile_cols: int) -> str:
+    """How the tcgen05 product cuts an ``m`` x ``n`` output: "pairs" (256-row tiles by pairs of CTAs),
+    "single" (128-row tiles), or "" when neither fills the machine and the vendor library takes it."""
+    if TCGEN05_PAIR and tcgen05_pairs_fill_the_machine(m, n, tile_cols):
+        return "pairs"
+    return "single" if tcgen05_fills_the_machine(m, n, tile_cols) else ""
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_n: int | None = None) -> None:
@@ -685,11 +708,12 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
         _check(_fn("ts_gemm_skinny_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
                                             _stream()), "gemm_swiglu")
         return
-    if (x.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and 2 * inter >= TCGEN05_MIN_COLS and k % 8 == 0
-            and tcgen05_fills_the_machine(m, inter, 128)):
+    tiles = tcgen05_tiles(m, inter, 128)
+    if x.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and 2 * inter >= TCGEN05_MIN_COLS and k % 8 == 0 and tiles:
         # many rows: the tcgen05 product with the activation in its epilogue
         _check(_fn("ts_gemm_tcgen05_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(out, "out"), m, inter, k,
-                                             _error_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_swiglu")
+                                             int(tiles == "pairs"), _error_word(x.device).data_ptr(), _stream()),
+               "gemm_tcgen05_swiglu")
         return
     gate_up = arena.take((m, 2 * inter), x.dtype)
     gemm(x, w_gate_up, gate_up)
