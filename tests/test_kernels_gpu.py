@@ -62,6 +62,32 @@ def test_add_rms_norm(dtype, hidden, with_delta) -> None:
     torch.testing.assert_close(out2.float(), want2.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [256, 512, 1024, 2048])
+@pytest.mark.parametrize("t", [256, 1027])
+def test_add_rms_norm_of_many_rows(dtype, hidden, t) -> None:
+    """From 256 rows of 256 / 512 / 1,024 / 2,048 values on, a warp takes a row; a last CTA of fewer than four rows."""
+    resid = rnd(t, hidden, seed=1, scale=3.0)
+    delta = rnd(t, hidden, dtype=dtype, seed=2)
+    w = (1 + rnd(hidden, seed=3, scale=0.1)).to(dtype)
+    for d in (delta, None):
+        r1, r2 = resid.clone(), resid.clone()
+        out = torch.full((t, hidden), float("nan"), device="cuda", dtype=dtype)
+        want = torch.empty(t, hidden, device="cuda", dtype=dtype)
+        ops.add_rms_norm(r1, d, w, 1e-5, out)
+        ref.add_rms_norm(r2, d, w, 1e-5, want)
+        torch.testing.assert_close(r1, r2, atol=0, rtol=0)
+        torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    rows = torch.randint(0, t, (300,), device="cuda", dtype=torch.int32)
+    r3 = resid.clone()
+    out2 = torch.empty(300, hidden, device="cuda", dtype=dtype)
+    want2 = torch.empty_like(out2)
+    ops.add_rms_norm(r3, delta, w, 1e-5, out2, rows=rows)
+    ref.add_rms_norm(resid.clone(), delta, w, 1e-5, want2, rows=rows)
+    assert torch.equal(r3, resid)
+    torch.testing.assert_close(out2.float(), want2.float(), **tol(dtype))
+
+
 def test_rope_tables_far_positions() -> None:
     pos = torch.tensor([0, 1, 2, 4095, 40959, 1_000_003], device="cuda", dtype=torch.int32)
     two_i = torch.arange(0, 128, 2, dtype=torch.float64)
