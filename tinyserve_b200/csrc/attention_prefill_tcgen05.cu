@@ -18,25 +18,34 @@
 // tensor core alternates between the heads (P V of head 0, S of head 0's next tile, P V of head 1,
 // S of head 1's next tile), so it works for one head while the other head's softmax runs.
 // Roles:
-//   warps 0 .. 4 NQ - 1 : softmax, four warps per head, one thread per row: reads its row of S (tcgen05.ld), masks, keeps the
-//               running maximum and sum, writes P as bf16 over the first 64 columns of the same
-//               buffer (tcgen05.st), and scales O in tensor memory only when the maximum has
-//               grown by more than 2^8 (the sum and O then simply carry a common factor that the
-//               final division removes); at the end divides O by the sum and stores it
-//   next warp : TMA producer: K and V tiles of 128 positions (three stages, two for NQ = 2), a
-//               box per page part and 64 columns, one lane per box
+//   softmax warps : four per head, one thread per row (two heads a CTA), or eight for the one head of a
+//               CTA, two threads per row with half of a tile's columns each, which exchange the row
+//               maximum through shared memory and meet at a named barrier. A thread reads its part of
+//               S (tcgen05.ld), masks, keeps the running maximum and its part of the sum, writes P as
+//               bf16 over the first 64 columns of the same buffer (tcgen05.st), and scales O in tensor
+//               memory only when the maximum has grown by more than 2^8 (the sum and O then simply carry
+//               a common factor that the final division removes); at the end divides O by the sum and
+//               stores it
+//   TMA warps : K and V tiles of 128 positions (three stages, two for NQ = 2), a box per page part and
+//               64 columns, one lane per box; keys and values have warps of their own (one each, or two
+//               each for NQ = 1), and the block-table look-up of a tile is made a tile ahead
 //   last warp : allocates tensor memory; one lane issues every tcgen05.mma and the
 //               tcgen05.commit that tells the other roles what has finished; zeroes V rows
 //               outside the live key range (0 x garbage would not be 0). A product that
 //               overwrites a buffer is always issued after the product that read P from it, and
 //               the tensor core runs them in order.
-// Where the time goes (B200, 16 / 8 heads of 128): a tile step (128 rows x 128 keys) costs 1,024
-// cycles of tensor core (16 instructions of 128 x 128 x 16 at the measured 64 cycles each) and
-// 1,024 cycles of the exponential unit, but one softmax warp per sub-core needs about 3,000 cycles
-// for it (load, maximum, exponentials, pack, store, each waiting for the one before), and with one
-// head that is the pace: 8,192 tokens run at 640 TFLOP/s. With two heads the tensor core works
-// for one while the other's softmax runs: 940 TFLOP/s. Every operand read from shared memory and
-// every TMA write goes through the same 128 bytes per cycle, which is why P stays in tensor
+// Where the time goes (B200, 16 / 8 heads of 128; device clock stamps of one CTA's roles): a tile step
+// (128 rows x 128 keys) costs 1,024 cycles of tensor core (16 instructions of 128 x 128 x 16 at the
+// measured 64 cycles each) and 1,024 cycles of the exponential unit. With one TMA warp for both
+// tensors that warp set the pace: a copy costs its issuing warp about 100 cycles, a tile has 32 of
+// them, 3,050 cycles a step; with warps of their own for keys and values the softmax warps set it:
+// 2,550 cycles a step with two threads per row (wait for S 210, load 130, maximum 260, exchange 390,
+// exponentials and pack 1,240 of which the exponential unit is busy for 1,024, store and hand-over 300):
+// 2,048 tokens 41 -> 35 us, 8,192 tokens 640 -> 810 TFLOP/s with one head a CTA. Doing every second
+// exponential as a polynomial on the FMA pipe made the step longer (the softmax warps are short of
+// issue slots, not only of the exponential unit). With two heads a CTA the tensor core works for one
+// head while the other's softmax runs: 920 TFLOP/s at 8,192 tokens. Every operand read from shared
+// memory and every TMA write goes through the same 128 bytes per cycle, which is why P stays in tensor
 // memory.
 // Every wait is on an mbarrier, is bounded and gives up at once when another role has: the CTA
 // then records the failure in *error_flag, waits for its copies in flight, frees its tensor
@@ -76,8 +85,13 @@ struct FaLayout {
   static constexpr int D = 64 * D64;
   static constexpr int STAGES = NQ == 1 ? 3 : 2;              // K / V tiles in flight
   static constexpr int SPB = NQ == 1 ? 2 : 1;                 // score / probability buffers per head
-  static constexpr int SOFTMAX_WARPS = 4 * NQ;
-  static constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+  // softmax warps per quarter of the rows, each with BN / HS of a tile's columns: two with one head (the
+  // softmax of a tile is the pace there, and two threads per row halve it); with two heads the register
+  // file has no room for sixteen softmax warps
+  static constexpr int HS = NQ == 1 ? 2 : 1;
+  static constexpr int SOFTMAX_WARPS = 4 * HS * NQ;
+  static constexpr int PW = NQ == 1 ? 2 : 1;                  // TMA warps per tensor (keys, values)
+  static constexpr int THREADS = (SOFTMAX_WARPS + 2 * PW + 1) * 32;      // + the TMA warps and the MMA warp
   static constexpr uint32_t Q_BYTES = FA_BM * D * 2;          // per head
   static constexpr uint32_t KV_BYTES = FA_BN * D * 2;         // one K or V tile
   static constexpr uint32_t OFF_Q = 0;
@@ -92,11 +106,12 @@ struct FaLayout {
 // D64 = head_dim / 64; BR = rows of a tensor box (16, or 8 for pages of 8); NQ = heads per CTA.
 // blockIdx = (group of NQ query heads, tile of 128 tokens counted from the end, request in the list).
 template <int D64, int BR, int NQ>
-__global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+__global__ void __launch_bounds__((4 * (NQ == 1 ? 2 : 1) * NQ + 2 * (NQ == 1 ? 2 : 1) + 1) * 32) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                             const __grid_constant__ CUtensorMap map_v,
                                                                             AttnArgs a, int* error_flag) {
   using L = FaLayout<D64, NQ>;
-  constexpr int D = L::D, BN = FA_BN, FA_KV_STAGES = L::STAGES, SPB = L::SPB, FA_SOFTMAX_WARPS = L::SOFTMAX_WARPS;
+  constexpr int D = L::D, BN = FA_BN, FA_KV_STAGES = L::STAGES, SPB = L::SPB, FA_SOFTMAX_WARPS = L::SOFTMAX_WARPS, HS = L::HS, PW = L::PW;
+  constexpr int HC = BN / HS;                                  // score columns of one softmax thread
   // instruction descriptors: D = f32, A = B = bf16, M = 128; S: N = BN, both operands K-major;
   // PV: N = D, B MN-major (bit 16)
   constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
@@ -107,6 +122,8 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
   __shared__ __align__(8) uint64_t s_full[NQ][SPB], p_full[NQ][SPB], pv_done[NQ][SPB], q_ready;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed_flag;
+  __shared__ float pair_value[NQ][4][HS][32];      // what the warps of a row quarter tell one another: a row maximum, a row sum
+  __shared__ int pair_ok[NQ][4][HS];
   volatile int* failed = &failed_flag;
 
   // ---- which rows and keys (uniform over the CTA); a CTA without rows leaves before any set-up
@@ -135,12 +152,12 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     for (int q = 0; q < NQ; ++q)
-      for (int b = 0; b < SPB; ++b) { mbar_init(&s_full[q][b], 1); mbar_init(&p_full[q][b], 4); mbar_init(&pv_done[q][b], 1); }
+      for (int b = 0; b < SPB; ++b) { mbar_init(&s_full[q][b], 1); mbar_init(&p_full[q][b], 4 * HS); mbar_init(&pv_done[q][b], 1); }
     mbar_init(&q_ready, FA_SOFTMAX_WARPS);
     failed_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == FA_SOFTMAX_WARPS + 1) tmem_alloc(&tmem_base_slot, L::TMEM_COLS);
+  if (warp == FA_SOFTMAX_WARPS + 2 * PW) tmem_alloc(&tmem_base_slot, L::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -149,15 +166,17 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
 
   if (warp < FA_SOFTMAX_WARPS) {
     // =========================================================== softmax warps
-    const int q = warp >> 2, quad = warp & 3;                  // head of this warp, lane quarter
+    // head of this warp, which half of a tile's keys (and of the head's output columns), lane quarter
+    const int q = warp / (4 * HS), half = (warp / 4) % HS, quad = warp & 3;
     const int head = head0 + q;
     const int r = quad * 32 + lane;                            // this thread's row
     unsigned char* q_tile = smem + L::OFF_Q + q * L::Q_BYTES;
     {
       // Q rows into the swizzled operand layout: 16 (or 8) threads fetch a row, 16 bytes each
+      constexpr int TPH = 128 * HS;                            // softmax threads of a head
       constexpr int CPR = D / 8;                               // 16-byte chunks per row
-      constexpr int RPP = 128 / CPR, PASSES = FA_BM / RPP;     // rows per pass of the 128 threads
-      const int tq = threadIdx.x & 127;
+      constexpr int RPP = TPH / CPR, PASSES = FA_BM / RPP;     // rows per pass of the head's threads
+      const int tq = threadIdx.x % TPH;
       const int c = tq % CPR, row0 = tq / CPR;
       uint4 v[PASSES];
 #pragma unroll
@@ -176,54 +195,93 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&q_ready);
     }
+    // The HS warps of a row quarter meet twice per exchange (named barrier 1 + its index, 32 HS threads):
+    // after writing and after reading. Each also says whether its waits have held, so that they stop
+    // together: a warp that left alone would leave its partner at the barrier.
+    auto pair_sync = [&]() {      // barriers 1 to 4 by literal numbers, so that the assembler counts them
+      if (quad == 0) asm volatile("bar.sync 1, 64;" ::: "memory");
+      else if (quad == 1) asm volatile("bar.sync 2, 64;" ::: "memory");
+      else if (quad == 2) asm volatile("bar.sync 3, 64;" ::: "memory");
+      else asm volatile("bar.sync 4, 64;" ::: "memory");
+    };
+    auto exchange = [&](float mine, bool mine_ok, float (&all)[HS]) -> bool {
+      if constexpr (HS == 1) {
+        all[0] = mine;
+        return mine_ok;
+      } else {
+        static_assert(HS <= 2 && NQ * (HS - 1) <= 1, "one pair of warps per row quarter, one head");
+        pair_value[q][quad][half][lane] = mine;
+        if (lane == 0) pair_ok[q][quad][half] = mine_ok ? 1 : 0;
+        pair_sync();
+        bool all_ok = true;
+#pragma unroll
+        for (int h2 = 0; h2 < HS; ++h2) {
+          all[h2] = pair_value[q][quad][h2][lane];
+          all_ok = all_ok && pair_ok[q][quad][h2] != 0;
+        }
+        pair_sync();
+        return all_ok;
+      }
+    };
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const uint32_t tmem_o = tmem_base + lane_addr + L::TMEM_O + (uint32_t)(q * D);
     const int p_abs = p_lo + r;
     float m_used = -INFINITY, l_sum = 0.f;
-    bool ok = true;
+    bool ok = true, stopped = false;
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j % SPB, nth = j / SPB;                    // buffer, and how often it has been used
       const uint32_t tmem_sp = tmem_base + lane_addr + L::TMEM_SP + (uint32_t)((q * SPB + b) * BN);
-      if (!fa_warp_wait(&s_full[q][b], nth & 1, failed)) { ok = false; break; }
+      if (ok && !fa_warp_wait(&s_full[q][b], nth & 1, failed)) ok = false;
       tc_fence_after();
-      uint32_t sraw[BN];
+      uint32_t sraw[HC];
+      float mx = -INFINITY;
+      const int k0 = (t_begin + j) * BN + half * HC;           // the first key of this thread's columns
+      if (ok) {
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) tmem_ld_32_nowait(tmem_sp + c * 32, sraw + c * 32);
-      tmem_ld_wait();
-      const int k0 = (t_begin + j) * BN;
-      const bool edge = (k0 + BN - 1 > p_lo) || (a.window > 0 && k0 < p_lo + FA_BM - a.window);
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: the maxima do not wait on one another
-      if (edge) {
-        const int first = a.window > 0 ? p_abs - a.window + 1 : 0;
+        for (int c = 0; c < HC / 32; ++c) tmem_ld_32_nowait(tmem_sp + half * HC + c * 32, sraw + c * 32);
+        tmem_ld_wait();
+        const bool edge = (k0 + HC - 1 > p_lo) || (a.window > 0 && k0 < p_lo + FA_BM - a.window);
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: the maxima do not wait on one another
+        if (edge) {
+          const int first = a.window > 0 ? p_abs - a.window + 1 : 0;
 #pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          const int kpos = k0 + i;
-          const float v = (kpos <= p_abs && kpos >= first) ? __uint_as_float(sraw[i]) : -INFINITY;
-          sraw[i] = __float_as_uint(v);
-          mx4[i & 3] = fmaxf(mx4[i & 3], v);
+          for (int i = 0; i < HC; ++i) {
+            const int kpos = k0 + i;
+            const float v = (kpos <= p_abs && kpos >= first) ? __uint_as_float(sraw[i]) : -INFINITY;
+            sraw[i] = __float_as_uint(v);
+            mx4[i & 3] = fmaxf(mx4[i & 3], v);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < HC; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sraw[i]));
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sraw[i]));
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the row's maximum over all its columns; every score of the tile has been read by now, so the
+      // probabilities may overwrite them
+      float maxima[HS];
+      if (!exchange(mx, ok, maxima)) { stopped = true; break; }
+#pragma unroll
+      for (int h2 = 0; h2 < HS; ++h2) mx = fmaxf(mx, maxima[h2]);
       const float m_new = fmaxf(m_used, mx * a.scale_log2);
       if (j == 0) {
         m_used = m_new;
       } else {
         const bool grow = m_new > m_used + FA_RESCALE_STEP;    // also when nothing was seen before (-inf)
         if (__any_sync(0xffffffffu, grow)) {
-          // O is final up to tile j - 1 before it is scaled
-          if (!fa_warp_wait(&pv_done[q][(j - 1) % SPB], ((j - 1) / SPB) & 1, failed)) { ok = false; break; }
+          // O is final up to tile j - 1 before it is scaled; each warp scales its share of the columns
+          if (!fa_warp_wait(&pv_done[q][(j - 1) % SPB], ((j - 1) / SPB) & 1, failed)) ok = false;
           tc_fence_after();
           const float alpha = grow ? (m_used == -INFINITY ? 0.f : fa_exp2(m_used - m_new)) : 1.f;
+          if (ok) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld_32(tmem_o + c * 32, o);
+            for (int c = half * (D / 32 / HS); c < (half + 1) * (D / 32 / HS); ++c) {
+              uint32_t o[32];
+              tmem_ld_32(tmem_o + c * 32, o);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32(tmem_o + c * 32, o);
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_32(tmem_o + c * 32, o);
+            }
           }
           if (grow) { l_sum *= alpha; m_used = m_new; }
         }
@@ -232,7 +290,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       float add4[4] = {0.f, 0.f, 0.f, 0.f};
       // P as bf16, two keys per 32-bit column, over the first half of this buffer's columns
 #pragma unroll
-      for (int c = 0; c < BN / 64; ++c) {
+      for (int c = 0; c < HC / 64; ++c) {
         uint32_t packed[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -241,7 +299,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
           add4[i & 3] += p0 + p1;
           packed[i] = fa_pack(p0, p1);
         }
-        tmem_st_32_nowait(tmem_sp + c * 32, packed);
+        tmem_st_32_nowait(tmem_sp + half * (HC / 2) + c * 32, packed);
       }
       l_sum += (add4[0] + add4[1]) + (add4[2] + add4[3]);
       tmem_st_wait();
@@ -249,16 +307,21 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[q][b]);
     }
-    if (ok) {
+    if (!stopped) {
       const int last = n_tiles - 1;
-      ok = fa_warp_wait(&pv_done[q][last % SPB], (last / SPB) & 1, failed);
+      if (ok && !fa_warp_wait(&pv_done[q][last % SPB], (last / SPB) & 1, failed)) ok = false;
+      float sums[HS];
+      ok = exchange(l_sum, ok, sums);
+      l_sum = 0.f;
+#pragma unroll
+      for (int h2 = 0; h2 < HS; ++h2) l_sum += sums[h2];      // in the order of the columns, the same in every warp
     }
-    if (ok) {
+    if (ok && !stopped) {
       tc_fence_after();
       const float inv = 1.f / l_sum;
       bf16* dst = (bf16*)a.out + ((size_t)(q_start + q0 + r) * a.num_heads + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 32 / HS); c < (half + 1) * (D / 32 / HS); ++c) {
         uint32_t o[32];
         tmem_ld_32(tmem_o + c * 32, o);
         if (r < valid) {
@@ -274,50 +337,63 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
         }
       }
     }
-  } else if (warp == FA_SOFTMAX_WARPS) {
-    // =========================================================== TMA producer
+  } else if (warp < FA_SOFTMAX_WARPS + 2 * PW) {
+    // =========================================================== TMA producers: PW warps for the keys, PW for the values
+    // (a copy costs its issuing warp about 100 cycles, a tile has 16 to 32 of them per tensor: one warp
+    // for both tensors needed 3,000 cycles a tile and was the slowest role of the CTA). The warps of a
+    // tensor take alternate copies of a tile; the first of them arms the tile's barrier (a copy of the
+    // other warp that lands before that only makes the byte count negative for a while: the phase
+    // cannot end before the arming thread has arrived).
+    const int which = (warp - FA_SOFTMAX_WARPS) % 2;            // 0: keys, 1: values
+    const int pw = (warp - FA_SOFTMAX_WARPS) / 2;               // which of the tensor's warps
     const int* table = a.block_tables + (size_t)seq * a.table_width;
     constexpr int PARTS = BN / BR;
-    constexpr int COPIES = PARTS * D64;                         // per tile; one lane each, in rounds of 32
+    constexpr int COPIES = PARTS * D64;                         // per tile and tensor: one lane each
+    static_assert(COPIES <= 32, "a lane issues at most one copy per tile and tensor");
     const int kmin = lo & ~(BR - 1), kmax = (ctx - 1) & ~(BR - 1);
+    const int copy = lane * PW + pw;                            // this lane's copy of a tile
+    const int part = copy / D64, h = copy - part * D64;         // its part of the tile and half of the head
+    // The row of the cache tensors where this lane's part of tile j begins: a look-up in the block
+    // table, the same for keys and values. It is fetched a tile ahead: looked up when the copies
+    // are due (twice per tile, a trip to L2 each time) it made this warp the slowest role of the CTA
+    // (3,000 cycles a tile against 1,024 of tensor core and 2,100 of softmax).
+    auto cache_row = [&](int j) -> int {
+      // a part wholly outside the live keys is fetched from the nearest live part (its scores are
+      // masked and its value rows zeroed); every part lies within one page
+      const int kpos = min(max((t_begin + j) * BN + part * BR, kmin), kmax);
+      int page, off;
+      if (a.page_shift >= 0) { page = table[kpos >> a.page_shift]; off = kpos & (a.page_size - 1); }
+      else { const int idx = kpos / a.page_size; page = table[idx]; off = kpos - idx * a.page_size; }
+      return (page * a.num_kv_heads + kvh) * a.page_size + off;
+    };
     bool ok = !wait_test_unarmed();
-    int issued_k = 0, issued_v = 0;
+    int issued = 0;
+    uint64_t* const full_bars = which == 0 ? k_full : v_full;
+    uint64_t* const empty_bars = which == 0 ? k_empty : v_empty;
+    const CUtensorMap* const map = which == 0 ? &map_k : &map_v;
+    const bool mine = copy < COPIES;
+    int y = mine ? cache_row(0) : 0;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % FA_KV_STAGES;
       const uint32_t ph = (j / FA_KV_STAGES) & 1;
-      const int k0 = (t_begin + j) * BN;
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        uint64_t* full = which == 0 ? &k_full[st] : &v_full[st];
-        uint64_t* empty = which == 0 ? &k_empty[st] : &v_empty[st];
-        int good = 1;
-        if (lane == 0) {
-          good = mbar_wait_or_fail(empty, ph ^ 1, failed) ? 1 : 0;
-          if (good) mbar_expect_tx(full, L::KV_BYTES);
-        }
-        good = __shfl_sync(0xffffffffu, good, 0);
-        if (!good) { ok = false; break; }
-        unsigned char* dst = smem + (which == 0 ? L::OFF_K : L::OFF_V) + st * L::KV_BYTES;
-        for (int cpy = lane; cpy < COPIES; cpy += 32) {
-          const int part = cpy / D64, h = cpy - part * D64;
-          // a part wholly outside the live keys is fetched from the nearest live part (its
-          // scores are masked and its value rows zeroed); every part lies within one page
-          int kpos = min(max(k0 + part * BR, kmin), kmax);
-          int page, off;
-          if (a.page_shift >= 0) { page = table[kpos >> a.page_shift]; off = kpos & (a.page_size - 1); }
-          else { const int idx = kpos / a.page_size; page = table[idx]; off = kpos - idx * a.page_size; }
-          const int y = (page * a.num_kv_heads + kvh) * a.page_size + off;
-          tma_load_2d(dst + h * (BN * 128) + part * (BR * 128), which == 0 ? &map_k : &map_v, full, h * 64, y);
-        }
-        if (which == 0) issued_k = j + 1; else issued_v = j + 1;
+      const int y_next = (mine && j + 1 < n_tiles) ? cache_row(j + 1) : 0;      // in flight during this tile's wait
+      int good = 1;
+      if (lane == 0) {
+        good = mbar_wait_or_fail(&empty_bars[st], ph ^ 1, failed) ? 1 : 0;
+        if (good && pw == 0) mbar_expect_tx(&full_bars[st], L::KV_BYTES);
       }
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { ok = false; break; }
+      unsigned char* dst = smem + (which == 0 ? L::OFF_K : L::OFF_V) + st * L::KV_BYTES;
+      if (mine) tma_load_2d(dst + h * (BN * 128) + part * (BR * 128), map, &full_bars[st], h * 64, y);
+      issued = j + 1;
+      y = y_next;
     }
     if (!ok && lane == 0) {
       // leave no copy in flight: the last phases armed on every stage must complete
       for (int back = 0; back < FA_KV_STAGES; ++back) {
-        const int jk = issued_k - 1 - back, jv = issued_v - 1 - back;
-        if (jk >= 0) mbar_wait(&k_full[jk % FA_KV_STAGES], (jk / FA_KV_STAGES) & 1);
-        if (jv >= 0) mbar_wait(&v_full[jv % FA_KV_STAGES], (jv / FA_KV_STAGES) & 1);
+        const int jj = issued - 1 - back;
+        if (jj >= 0) mbar_wait(&full_bars[jj % FA_KV_STAGES], (jj / FA_KV_STAGES) & 1);
       }
     }
   } else {
@@ -410,7 +486,7 @@ __global__ void __launch_bounds__((4 * NQ + 2) * 32) prefill_attn_tc_kernel(cons
   if (*failed && (threadIdx.x & 31) == 0) atomicExch(error_flag, WAIT_FAILED_PREFILL_TCGEN05);
   tc_fence_before();
   __syncthreads();
-  if (warp == FA_SOFTMAX_WARPS + 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
+  if (warp == FA_SOFTMAX_WARPS + 2 * PW) tmem_dealloc(tmem_base, L::TMEM_COLS);
 }
 
 // ---------------------------------------------------------------- host side
