@@ -569,6 +569,152 @@ static int launch_skinny_stream(const bf16* x, const bf16* w, TOut* out, int M, 
   return launch(kern, dim3(tiles < ctas ? tiles : ctas), SK_THREADS, smem, stream, x, w, out, M, N, K);
 }
 
+// The forms of up to 8 rows with 8 weight rows per tile instead of 16: the operands change places, x is
+// the A operand (its rows g; rows g + 8 of the tile are zero) and the weights the B operand (weight
+// row g, 8 per tile), so a lane still loads 8 consecutive k of "its" weight row and of "its" x row
+// for two m16n8k16. An SM takes in about 60 GB/s whatever the kernel, so a product lasts as long as
+// the SM with the most weights needs, and units of half the size spread better: N = 1,024 (o, down) is
+// 64 CTAs of 64 or 96 KB in the 16-row tall form and 128 CTAs of 32 or 48 KB here; the 192 CTAs of
+// gate/up (two of 64 KB on 44 of the 148 SMs) become 384 of 32 KB (three on 88 SMs). Measured on B200,
+// Qwen3-0.6B sizes, ms a decode step with o and down in this form: batch 1 0.758 -> 0.708, batch 8
+// 0.841 -> 0.829. K is split between the warps of the CTA and all its weights are in flight at once
+// (K <= PF * WARPS * 32). FUSE, NORMX, RESID as in gemm_skinny_kernel; RESID leaves the sums of
+// squares per 8 columns (N / 8 parts a row).
+template <typename TOut, bool FUSE, bool NORMX, bool RESID, int WARPS, int PF>
+__global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                                   TOut* __restrict__ out, int M, int N, int K,
+                                                                   SkinnyNorm nrm) {
+  static_assert(!(RESID && FUSE) && WARPS >= 8, "");
+  constexpr int KSTEP = WARPS * 32, CS = 9, TILES = FUSE ? 2 : 1;
+  __shared__ float red[WARPS * TILES * 8 * CS];      // [warp][tile][x row][weight row], rows padded by one word
+  __shared__ float rstd_s[8];
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 8;
+  const bf16* wrow[TILES];
+#pragma unroll
+  for (int r = 0; r < TILES; ++r) wrow[r] = w + (size_t)(r * N + n0 + g) * K + 8 * t + warp * 32;
+  uint4 ring[PF][TILES];
+#pragma unroll
+  for (int p = 0; p < PF; ++p)
+    if (warp * 32 + p * KSTEP < K) {
+#pragma unroll
+      for (int r = 0; r < TILES; ++r) ring[p][r] = ld_stream(wrow[r] + p * KSTEP);
+    }
+  pdl_wait();
+  // this thread's output (x row, weight row): RESID fetches the stream's value now and uses it at the end
+  const int om = threadIdx.x >> 3, orow = threadIdx.x & 7;
+  float resid_before = 0.f;
+  if constexpr (RESID) {
+    if (threadIdx.x < 64 && om < M) resid_before = ld_cg_f32(nrm.resid_out + (size_t)om * N + n0 + orow);
+  }
+  // NORMX: warp m adds up the parts of row m's sum of squares once the products are done
+  float ssq[4] = {0.f, 0.f, 0.f, 0.f};
+  if constexpr (NORMX) {
+    if (warp < M) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int p = lane + 32 * i;
+        if (p < nrm.parts) ssq[i] = ld_cg_f32(nrm.sumsq + warp * nrm.parts + p);
+      }
+    }
+  }
+  const bool xok = g < M;
+  const bf16* xrow = (NORMX ? nrm.resid16 : x) + (size_t)(xok ? g : 0) * K + 8 * t + warp * 32;
+  uint4 xring[PF], wring[NORMX ? PF : 1];
+#pragma unroll
+  for (int p = 0; p < PF; ++p) {
+    const bool in = warp * 32 + p * KSTEP < K;
+    xring[p] = (xok && in) ? ld_cached(xrow + p * KSTEP) : make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (NORMX) wring[p] = in ? ld_cached(nrm.weight + 8 * t + warp * 32 + p * KSTEP) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float acc[TILES][4];
+#pragma unroll
+  for (int r = 0; r < TILES; ++r)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[r][e] = 0.f;
+#pragma unroll
+  for (int p = 0; p < PF; ++p) {
+    if (warp * 32 + p * KSTEP < K) {
+      uint4 a = xring[p];
+      if constexpr (NORMX) a = normed_fragment(xring[p], wring[p]);
+#pragma unroll
+      for (int r = 0; r < TILES; ++r) {
+        mma_bf16_16816(acc[r], a.x, 0u, a.y, 0u, ring[p][r].x, ring[p][r].y);
+        mma_bf16_16816(acc[r], a.z, 0u, a.w, 0u, ring[p][r].z, ring[p][r].w);
+      }
+    }
+  }
+  if constexpr (NORMX) {
+    if (warp < M) {
+      const float ss = warp_sum((ssq[0] + ssq[1]) + (ssq[2] + ssq[3]));      // a fixed order
+      if (lane == 0) rstd_s[warp] = rsqrtf(ss / (float)K + nrm.eps);
+    }
+  }
+  // acc[r][0], acc[r][1]: x row g, weight rows 2 t and 2 t + 1 of tile r (acc[r][2], [3]: the zero rows)
+#pragma unroll
+  for (int r = 0; r < TILES; ++r) {
+    red[((warp * TILES + r) * 8 + g) * CS + 2 * t] = acc[r][0];
+    red[((warp * TILES + r) * 8 + g) * CS + 2 * t + 1] = acc[r][1];
+  }
+  __syncthreads();
+  if (threadIdx.x >= 64) return;            // two warps: 8 x rows x 8 weight rows
+  float ps[WARPS], pu[FUSE ? WARPS : 1], s = 0.f, u = 0.f;
+#pragma unroll
+  for (int wq = 0; wq < WARPS; ++wq) {
+    ps[wq] = red[((wq * TILES) * 8 + om) * CS + orow];
+    if constexpr (FUSE) pu[wq] = red[((wq * TILES + 1) * 8 + om) * CS + orow];
+  }
+#pragma unroll
+  for (int wq = 0; wq < WARPS; ++wq) {      // a fixed order
+    s += ps[wq];
+    if constexpr (FUSE) u += pu[wq];
+  }
+  if constexpr (NORMX) {
+    const float rstd = om < M ? rstd_s[om] : 0.f;
+    s *= rstd;
+    u *= rstd;
+  }
+  if constexpr (RESID) {
+    float r = 0.f;
+    if (om < M) {
+      r = resid_before + round_to<bf16>(s);
+      nrm.resid_out[(size_t)om * N + n0 + orow] = r;
+      nrm.resid16_out[(size_t)om * N + n0 + orow] = from_float<bf16>(r);
+    }
+    float sq = r * r;
+    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+    if (orow == 0 && om < M) nrm.sumsq_out[om * gridDim.x + blockIdx.x] = sq;
+  } else if (om < M) {
+    if constexpr (FUSE) {
+      // rounding points of the unfused path: product -> bf16, silu -> bf16, times up -> bf16
+      const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
+      const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
+      out[(size_t)om * N + n0 + orow] = from_float<TOut>(sv * uv);
+    } else {
+      out[(size_t)om * N + n0 + orow] = from_float<TOut>(s);
+    }
+  }
+}
+
+// Whether tiles of 8 weight rows spread an output of N columns better over the SMs than tiles of 16:
+// the SM with the most tiles then holds fewer weight rows.
+static bool h8_spreads_better(int N) {
+  const int t8 = N / 8, t16 = N / 16;
+  return N % 8 == 0 && ((t8 + 147) / 148) * 8 < ((t16 + 147) / 148) * 16;
+}
+constexpr int SK_H8_TALL_WARPS = 16, SK_H8_TALL_PF = 6;      // o and down: K up to 3,072
+constexpr int SK_H8_WARPS = 8, SK_H8_PF = 4;                 // the products that normalise the stream: K up to 1,024
+// Whether ts_gemm_skinny_to_stream takes the 8-row form for this shape; it then leaves N / 8 parts of
+// the sums of squares per row instead of N / 16 (the consumer adds up at most 128).
+static bool to_stream_takes_h8(int M, int N, int K) {
+  return M <= 8 && h8_spreads_better(N) && N / 8 <= 128 && K <= SK_H8_TALL_PF * SK_H8_TALL_WARPS * 32;
+}
+static bool normed_takes_h8(int M, int N, int K) { return M <= 8 && h8_spreads_better(N) && K <= SK_H8_PF * SK_H8_WARPS * 32; }
+
 template <typename TOut, int NT>
 static int dispatch_skinny_nt(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
   const int rt = row_tiles_for(N, 2);
@@ -639,6 +785,13 @@ extern "C" int ts_gemm_skinny_normed(const void* resid16, const float* sumsq, in
   SkinnyNorm nrm = SkinnyNorm();
   nrm.resid16 = (const bf16*)resid16; nrm.sumsq = sumsq; nrm.parts = parts; nrm.weight = (const bf16*)norm_weight; nrm.eps = eps;
   const bf16* wp = (const bf16*)w;
+  if (normed_takes_h8(M, N, K) && out_dtype == TS_DTYPE_BF16) {
+    if (swiglu)
+      return launch(gemm_skinny_h8_kernel<bf16, true, true, false, SK_H8_WARPS, SK_H8_PF>, N / 8, SK_H8_WARPS * 32, 0, stream,
+                    (const bf16*)nullptr, wp, (bf16*)out, M, N, K, nrm);
+    return launch(gemm_skinny_h8_kernel<bf16, false, true, false, SK_H8_WARPS, SK_H8_PF>, N / 8, SK_H8_WARPS * 32, 0, stream,
+                  (const bf16*)nullptr, wp, (bf16*)out, M, N, K, nrm);
+  }
   if (swiglu) {
     if (out_dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
     if (M <= 8) return launch_skinny<bf16, 1, 1, true, 4, true, false>(nullptr, wp, (bf16*)out, M, N, K, stream, nrm);
@@ -657,7 +810,10 @@ extern "C" int ts_gemm_skinny_normed(const void* resid16, const float* sumsq, in
 
 // resid[M, N] += bf16(x * w^T) in place, resid16 = bf16(resid), and sumsq_out[m * (N / 16) + n / 16]
 // = sum over the 16 columns from n of the new resid[m, .]^2 (RESID above). M <= 16; sumsq_out
-// holds M * N / 16 floats.
+// holds M * N / 16 floats. Where ts_gemm_skinny_to_stream_parts(M, N, K) says so, the parts are of 8
+// columns: sumsq_out[m * (N / 8) + n / 8], M * N / 8 floats.
+extern "C" int ts_gemm_skinny_to_stream_parts(int M, int N, int K) { return to_stream_takes_h8(M, N, K) ? N / 8 : N / 16; }
+
 extern "C" int ts_gemm_skinny_to_stream(const void* x, const void* w, float* resid, void* resid16, float* sumsq_out,
                                         int M, int N, int K, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
@@ -665,6 +821,9 @@ extern "C" int ts_gemm_skinny_to_stream(const void* x, const void* w, float* res
   if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
   SkinnyNorm nrm = SkinnyNorm();
   nrm.resid_out = resid; nrm.resid16_out = (bf16*)resid16; nrm.sumsq_out = sumsq_out;
+  if (to_stream_takes_h8(M, N, K))
+    return launch(gemm_skinny_h8_kernel<bf16, false, false, true, SK_H8_TALL_WARPS, SK_H8_TALL_PF>, N / 8, SK_H8_TALL_WARPS * 32, 0,
+                  stream, (const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, nrm);
   if (M <= 8)
     return launch_skinny<bf16, 1, 1, false, 4, false, true>((const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, stream, nrm);
   return launch_skinny<bf16, 2, 1, false, 4, false, true>((const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, stream, nrm);

@@ -50,6 +50,7 @@ _SIGNATURES: dict[str, list[Any]] = {
                                      _f, _i, _i, _vp, _vp],
     "ts_gemm_skinny_normed": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_to_stream": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "ts_gemm_skinny_to_stream_parts": [_i, _i, _i],
     "ts_prefetch_l2": [_vp, _vp, _i, _i, _vp],
     "ts_prefetch_pages": [_vp, _vp, _c.c_ulonglong, _vp, _i, _vp, _i, _i, _i, _vp],
     "ts_gemm_simt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
@@ -745,10 +746,12 @@ def can_stream_fuse(m: int, n: int, k: int, width: int, dtype: torch.dtype, devi
 
 
 def gemm_to_stream(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, resid16: torch.Tensor,
-                   sumsq: torch.Tensor) -> None:
+                   sumsq: torch.Tensor) -> torch.Tensor:
     """``resid[M, N] += bf16(x[M, K] @ w[N, K]^T)`` in place (float32 stream); ``resid16`` gets
-    the new stream in bf16 and ``sumsq[m * (N / 16) + n // 16]`` the sum of ``resid[m, n : n + 16]^2``,
-    both for the product that normalises the stream next (:func:`gemm_normed`). bf16, ``M <= 16``."""
+    the new stream in bf16 and ``sumsq`` (at least ``N`` floats of scratch) the rows' sums of squares in
+    parts: returned as a view ``[M, parts]`` with ``parts`` = ``N / 16`` or, where the kernel cuts the
+    output into tiles of 8 columns, ``N / 8``; both for the product that normalises the stream next
+    (:func:`gemm_normed`). bf16, ``M <= 16``."""
     m, k = x.shape
     n = w.shape[0]
     if (w.shape[1] != k or tuple(resid.shape) != (m, n) or resid.dtype != torch.float32 or sumsq.dtype != torch.float32
@@ -757,20 +760,22 @@ def gemm_to_stream(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, resid1
         raise KernelError("gemm_to_stream: shape or dtype mismatch")
     _check(_fn("ts_gemm_skinny_to_stream")(_dev(x, "x"), _dev(w, "w"), _dev(resid, "resid"), _dev(resid16, "resid16"),
                                            _dev(sumsq, "sumsq"), m, n, k, _stream()), "gemm_to_stream")
+    parts = int(_fn("ts_gemm_skinny_to_stream_parts")(m, n, k))
+    return sumsq[: m * parts].view(m, parts)
 
 
 def gemm_normed(resid16: torch.Tensor, sumsq: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor,
                 out: torch.Tensor, swiglu: bool = False) -> None:
     """``out = rms_norm(resid) @ w^T`` (or its SwiGLU form, ``w`` = gate rows then up rows) where
-    the norm is applied inside the product: ``resid16`` ``[M, K]`` bf16 and ``sumsq`` as
-    :func:`gemm_to_stream` leaves them (``K / 16`` parts per row), ``norm_weight`` ``[K]`` bf16."""
+    the norm is applied inside the product: ``resid16`` ``[M, K]`` bf16 and ``sumsq`` ``[M, parts]`` as
+    :func:`gemm_to_stream` returned it (at most 128 parts per row), ``norm_weight`` ``[K]`` bf16."""
     m, k = resid16.shape
     n = out.shape[1]
     if (tuple(w.shape) != ((2 * n if swiglu else n), k) or out.shape[0] != m or resid16.dtype != torch.bfloat16
-            or sumsq.dtype != torch.float32 or sumsq.numel() < k or norm_weight.shape != (k,)
-            or w.dtype != torch.bfloat16 or norm_weight.dtype != torch.bfloat16):
+            or sumsq.dtype != torch.float32 or sumsq.dim() != 2 or sumsq.shape[0] != m or not sumsq.is_contiguous()
+            or norm_weight.shape != (k,) or w.dtype != torch.bfloat16 or norm_weight.dtype != torch.bfloat16):
         raise KernelError("gemm_normed: shape or dtype mismatch")
-    _check(_fn("ts_gemm_skinny_normed")(_dev(resid16, "resid16"), _dev(sumsq, "sumsq"), k // 16,
+    _check(_fn("ts_gemm_skinny_normed")(_dev(resid16, "resid16"), _dev(sumsq, "sumsq"), int(sumsq.shape[1]),
                                         _dev(norm_weight, "norm_weight"), float(eps), _dev(w, "w"), _dev(out, "out"), m, n,
                                         k, _code(out.dtype), int(bool(swiglu)), _stream()), "gemm_normed")
 

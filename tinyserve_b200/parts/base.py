@@ -279,9 +279,9 @@ def project_to_stream(x: torch.Tensor, w: torch.Tensor, stream: ResidualStream |
     n = w.shape[0]
     if (stream is not None and stream.delta is None and x.dtype == torch.bfloat16
             and ops.can_stream_fuse(m, n, k, n, x.dtype, x.device)):
-        copy, parts = stream.fusion_buffers(ctx)
-        ops.gemm_to_stream(x, w, stream.resid, copy, parts)
-        stream.resid16, stream.sumsq = copy, parts
+        copy, scratch = stream.fusion_buffers(ctx)
+        stream.sumsq = ops.gemm_to_stream(x, w, stream.resid, copy, scratch)
+        stream.resid16 = copy
         return None
     out = ctx.arena.take((m, n), ctx.dtype)
     ops.gemm(x, w, out)
