@@ -453,7 +453,7 @@ def test_gemm_to_stream_and_normed(m, n, k) -> None:
     w = rnd(n, k, dtype=bf, seed=2, scale=0.05)
     resid = rnd(m, n, seed=3, scale=2.0)
     before = resid.clone()
-    sumsq = torch.full((n,), float("nan"), device="cuda")
+    sumsq = torch.full((2 * n,), float("nan"), device="cuda")
     resid16 = torch.full((m, n), float("nan"), device="cuda", dtype=bf)
     sumsq = ops.gemm_to_stream(x, w, resid, resid16, sumsq)
     assert sumsq.shape[0] == m and sumsq.shape[1] in (n // 16, n // 8)

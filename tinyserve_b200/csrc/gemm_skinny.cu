@@ -580,14 +580,15 @@ static int launch_skinny_stream(const bf16* x, const bf16* w, TOut* out, int M, 
 // 0.841 -> 0.829. K is split between the warps of the CTA and all its weights are in flight at once
 // (K <= PF * WARPS * 32). FUSE, NORMX, RESID as in gemm_skinny_kernel; RESID leaves the sums of
 // squares per 8 columns (N / 8 parts a row).
-template <typename TOut, bool FUSE, bool NORMX, bool RESID, int WARPS, int PF>
+// XR = 1: up to 8 rows of x; XR = 2: up to 16 (the tile's rows g + 8 are then x rows too).
+template <typename TOut, bool FUSE, bool NORMX, bool RESID, int WARPS, int PF, int XR>
 __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                    TOut* __restrict__ out, int M, int N, int K,
                                                                    SkinnyNorm nrm) {
-  static_assert(!(RESID && FUSE) && WARPS >= 8, "");
-  constexpr int KSTEP = WARPS * 32, CS = 9, TILES = FUSE ? 2 : 1;
-  __shared__ float red[WARPS * TILES * 8 * CS];      // [warp][tile][x row][weight row], rows padded by one word
-  __shared__ float rstd_s[8];
+  static_assert(!(RESID && FUSE) && WARPS >= 8 && (XR == 1 || XR == 2), "");
+  constexpr int KSTEP = WARPS * 32, CS = 9, TILES = FUSE ? 2 : 1, ROWS = 8 * XR;
+  __shared__ float red[WARPS * TILES * ROWS * CS];      // [warp][tile][x row][weight row], rows padded by one word
+  __shared__ float rstd_s[ROWS];
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -607,26 +608,29 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* 
   const int om = threadIdx.x >> 3, orow = threadIdx.x & 7;
   float resid_before = 0.f;
   if constexpr (RESID) {
-    if (threadIdx.x < 64 && om < M) resid_before = ld_cg_f32(nrm.resid_out + (size_t)om * N + n0 + orow);
+    if (threadIdx.x < 8 * ROWS && om < M) resid_before = ld_cg_f32(nrm.resid_out + (size_t)om * N + n0 + orow);
   }
-  // NORMX: warp m adds up the parts of row m's sum of squares once the products are done
-  float ssq[4] = {0.f, 0.f, 0.f, 0.f};
+  // NORMX: warp m adds up the parts of the sums of squares of rows m and m + 8 once the products are done
+  float ssq[XR][4];
   if constexpr (NORMX) {
-    if (warp < M) {
+#pragma unroll
+    for (int h = 0; h < XR; ++h)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int p = lane + 32 * i;
-        if (p < nrm.parts) ssq[i] = ld_cg_f32(nrm.sumsq + warp * nrm.parts + p);
+        const int m = warp + 8 * h, p = lane + 32 * i;
+        ssq[h][i] = (warp < 8 && m < M && p < nrm.parts) ? ld_cg_f32(nrm.sumsq + m * nrm.parts + p) : 0.f;
       }
-    }
   }
-  const bool xok = g < M;
-  const bf16* xrow = (NORMX ? nrm.resid16 : x) + (size_t)(xok ? g : 0) * K + 8 * t + warp * 32;
-  uint4 xring[PF], wring[NORMX ? PF : 1];
+  const bf16* xbase = NORMX ? nrm.resid16 : x;
+  uint4 xring[PF][XR], wring[NORMX ? PF : 1];
 #pragma unroll
   for (int p = 0; p < PF; ++p) {
     const bool in = warp * 32 + p * KSTEP < K;
-    xring[p] = (xok && in) ? ld_cached(xrow + p * KSTEP) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int h = 0; h < XR; ++h) {
+      const int m = g + 8 * h;
+      xring[p][h] = (m < M && in) ? ld_cached(xbase + (size_t)m * K + 8 * t + warp * 32 + p * KSTEP) : make_uint4(0u, 0u, 0u, 0u);
+    }
     if constexpr (NORMX) wring[p] = in ? ld_cached(nrm.weight + 8 * t + warp * 32 + p * KSTEP) : make_uint4(0u, 0u, 0u, 0u);
   }
   float acc[TILES][4];
@@ -637,34 +641,42 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* 
 #pragma unroll
   for (int p = 0; p < PF; ++p) {
     if (warp * 32 + p * KSTEP < K) {
-      uint4 a = xring[p];
-      if constexpr (NORMX) a = normed_fragment(xring[p], wring[p]);
+      uint4 a = xring[p][0], a8 = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (XR == 2) a8 = xring[p][1];
+      if constexpr (NORMX) {
+        a = normed_fragment(a, wring[p]);
+        if constexpr (XR == 2) a8 = normed_fragment(a8, wring[p]);
+      }
 #pragma unroll
       for (int r = 0; r < TILES; ++r) {
-        mma_bf16_16816(acc[r], a.x, 0u, a.y, 0u, ring[p][r].x, ring[p][r].y);
-        mma_bf16_16816(acc[r], a.z, 0u, a.w, 0u, ring[p][r].z, ring[p][r].w);
+        mma_bf16_16816(acc[r], a.x, a8.x, a.y, a8.y, ring[p][r].x, ring[p][r].y);
+        mma_bf16_16816(acc[r], a.z, a8.z, a.w, a8.w, ring[p][r].z, ring[p][r].w);
       }
     }
   }
   if constexpr (NORMX) {
-    if (warp < M) {
-      const float ss = warp_sum((ssq[0] + ssq[1]) + (ssq[2] + ssq[3]));      // a fixed order
-      if (lane == 0) rstd_s[warp] = rsqrtf(ss / (float)K + nrm.eps);
+#pragma unroll
+    for (int h = 0; h < XR; ++h) {
+      const int m = warp + 8 * h;
+      const float ss = warp_sum((ssq[h][0] + ssq[h][1]) + (ssq[h][2] + ssq[h][3]));      // a fixed order
+      if (lane == 0 && warp < 8 && m < M) rstd_s[m] = rsqrtf(ss / (float)K + nrm.eps);
     }
   }
-  // acc[r][0], acc[r][1]: x row g, weight rows 2 t and 2 t + 1 of tile r (acc[r][2], [3]: the zero rows)
+  // acc[r][0], [1]: x row g, weight rows 2 t and 2 t + 1 of tile r; acc[r][2], [3]: x row g + 8
 #pragma unroll
-  for (int r = 0; r < TILES; ++r) {
-    red[((warp * TILES + r) * 8 + g) * CS + 2 * t] = acc[r][0];
-    red[((warp * TILES + r) * 8 + g) * CS + 2 * t + 1] = acc[r][1];
-  }
+  for (int r = 0; r < TILES; ++r)
+#pragma unroll
+    for (int h = 0; h < XR; ++h) {
+      red[((warp * TILES + r) * ROWS + g + 8 * h) * CS + 2 * t] = acc[r][2 * h];
+      red[((warp * TILES + r) * ROWS + g + 8 * h) * CS + 2 * t + 1] = acc[r][2 * h + 1];
+    }
   __syncthreads();
-  if (threadIdx.x >= 64) return;            // two warps: 8 x rows x 8 weight rows
+  if (threadIdx.x >= 8 * ROWS) return;      // whole warps: ROWS x rows x 8 weight rows
   float ps[WARPS], pu[FUSE ? WARPS : 1], s = 0.f, u = 0.f;
 #pragma unroll
   for (int wq = 0; wq < WARPS; ++wq) {
-    ps[wq] = red[((wq * TILES) * 8 + om) * CS + orow];
-    if constexpr (FUSE) pu[wq] = red[((wq * TILES + 1) * 8 + om) * CS + orow];
+    ps[wq] = red[((wq * TILES) * ROWS + om) * CS + orow];
+    if constexpr (FUSE) pu[wq] = red[((wq * TILES + 1) * ROWS + om) * CS + orow];
   }
 #pragma unroll
   for (int wq = 0; wq < WARPS; ++wq) {      // a fixed order
@@ -703,17 +715,29 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* 
 // Whether tiles of 8 weight rows spread an output of N columns better over the SMs than tiles of 16:
 // the SM with the most tiles then holds fewer weight rows.
 static bool h8_spreads_better(int N) {
-  const int t8 = N / 8, t16 = N / 16;
-  return N % 8 == 0 && ((t8 + 147) / 148) * 8 < ((t16 + 147) / 148) * 16;
+  const int t8 = N / 8, t16 = N / 16;      // only where tiles of 16 take fewer than two rounds: very tall matrices stream
+  return N % 8 == 0 && t16 < 2 * 148 && ((t8 + 147) / 148) * 8 < ((t16 + 147) / 148) * 16;
 }
 constexpr int SK_H8_TALL_WARPS = 16, SK_H8_TALL_PF = 6;      // o and down: K up to 3,072
 constexpr int SK_H8_WARPS = 8, SK_H8_PF = 4;                 // the products that normalise the stream: K up to 1,024
 // Whether ts_gemm_skinny_to_stream takes the 8-row form for this shape; it then leaves N / 8 parts of
 // the sums of squares per row instead of N / 16 (the consumer adds up at most 128).
 static bool to_stream_takes_h8(int M, int N, int K) {
-  return M <= 8 && h8_spreads_better(N) && N / 8 <= 128 && K <= SK_H8_TALL_PF * SK_H8_TALL_WARPS * 32;
+  return M <= 16 && h8_spreads_better(N) && N / 8 <= 128 && K <= SK_H8_TALL_PF * SK_H8_TALL_WARPS * 32;
 }
-static bool normed_takes_h8(int M, int N, int K) { return M <= 8 && h8_spreads_better(N) && K <= SK_H8_PF * SK_H8_WARPS * 32; }
+static bool normed_takes_h8(int M, int N, int K) { return M <= 16 && h8_spreads_better(N) && K <= SK_H8_PF * SK_H8_WARPS * 32; }
+// The plain and the SwiGLU product of up to 16 rows: narrow outputs take the tall CTAs, wide ones CTAs of 8 warps.
+template <typename TOut, bool FUSE>
+static int launch_h8_plain(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
+  const SkinnyNorm nrm = SkinnyNorm();
+  if (K <= SK_H8_PF * SK_H8_WARPS * 32) {
+    if (M <= 8) return launch(gemm_skinny_h8_kernel<TOut, FUSE, false, false, SK_H8_WARPS, SK_H8_PF, 1>, N / 8, SK_H8_WARPS * 32, 0, stream, x, w, out, M, N, K, nrm);
+    return launch(gemm_skinny_h8_kernel<TOut, FUSE, false, false, SK_H8_WARPS, SK_H8_PF, 2>, N / 8, SK_H8_WARPS * 32, 0, stream, x, w, out, M, N, K, nrm);
+  }
+  if (M <= 8) return launch(gemm_skinny_h8_kernel<TOut, FUSE, false, false, SK_H8_TALL_WARPS, SK_H8_TALL_PF, 1>, N / 8, SK_H8_TALL_WARPS * 32, 0, stream, x, w, out, M, N, K, nrm);
+  return launch(gemm_skinny_h8_kernel<TOut, FUSE, false, false, SK_H8_TALL_WARPS, SK_H8_TALL_PF, 2>, N / 8, SK_H8_TALL_WARPS * 32, 0, stream, x, w, out, M, N, K, nrm);
+}
+static bool plain_takes_h8(int M, int N, int K) { return M <= 16 && h8_spreads_better(N) && K <= SK_H8_TALL_PF * SK_H8_TALL_WARPS * 32; }
 
 template <typename TOut, int NT>
 static int dispatch_skinny_nt(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
@@ -730,6 +754,7 @@ static int dispatch_skinny_nt(const bf16* x, const bf16* w, TOut* out, int M, in
 
 template <typename TOut>
 static int dispatch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream) {
+  if (plain_takes_h8(M, N, K)) return launch_h8_plain<TOut, false>(x, w, out, M, N, K, stream);
   if (M <= 8) return dispatch_skinny_nt<TOut, 1>(x, w, out, M, N, K, stream);
   if (M <= 16) return dispatch_skinny_nt<TOut, 2>(x, w, out, M, N, K, stream);
   if (M <= 32) return dispatch_skinny_nt<TOut, 4>(x, w, out, M, N, K, stream);
@@ -768,6 +793,7 @@ extern "C" int ts_gemm_skinny_swiglu(const void* x, const void* w, void* out, in
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)w;
   bf16* op = (bf16*)out;
+  if (plain_takes_h8(M, inter, K)) return launch_h8_plain<bf16, true>(xp, wp, op, M, inter, K, stream);
   if (M <= 8) return dispatch_swiglu_nt<1>(xp, wp, op, M, inter, K, stream);
   if (M <= 16) return dispatch_swiglu_nt<2>(xp, wp, op, M, inter, K, stream);
   return dispatch_swiglu_nt<4>(xp, wp, op, M, inter, K, stream);
@@ -786,11 +812,14 @@ extern "C" int ts_gemm_skinny_normed(const void* resid16, const float* sumsq, in
   nrm.resid16 = (const bf16*)resid16; nrm.sumsq = sumsq; nrm.parts = parts; nrm.weight = (const bf16*)norm_weight; nrm.eps = eps;
   const bf16* wp = (const bf16*)w;
   if (normed_takes_h8(M, N, K) && out_dtype == TS_DTYPE_BF16) {
+    const bf16* none = nullptr;
+    if (swiglu && M <= 8)
+      return launch(gemm_skinny_h8_kernel<bf16, true, true, false, SK_H8_WARPS, SK_H8_PF, 1>, N / 8, SK_H8_WARPS * 32, 0, stream, none, wp, (bf16*)out, M, N, K, nrm);
     if (swiglu)
-      return launch(gemm_skinny_h8_kernel<bf16, true, true, false, SK_H8_WARPS, SK_H8_PF>, N / 8, SK_H8_WARPS * 32, 0, stream,
-                    (const bf16*)nullptr, wp, (bf16*)out, M, N, K, nrm);
-    return launch(gemm_skinny_h8_kernel<bf16, false, true, false, SK_H8_WARPS, SK_H8_PF>, N / 8, SK_H8_WARPS * 32, 0, stream,
-                  (const bf16*)nullptr, wp, (bf16*)out, M, N, K, nrm);
+      return launch(gemm_skinny_h8_kernel<bf16, true, true, false, SK_H8_WARPS, SK_H8_PF, 2>, N / 8, SK_H8_WARPS * 32, 0, stream, none, wp, (bf16*)out, M, N, K, nrm);
+    if (M <= 8)
+      return launch(gemm_skinny_h8_kernel<bf16, false, true, false, SK_H8_WARPS, SK_H8_PF, 1>, N / 8, SK_H8_WARPS * 32, 0, stream, none, wp, (bf16*)out, M, N, K, nrm);
+    return launch(gemm_skinny_h8_kernel<bf16, false, true, false, SK_H8_WARPS, SK_H8_PF, 2>, N / 8, SK_H8_WARPS * 32, 0, stream, none, wp, (bf16*)out, M, N, K, nrm);
   }
   if (swiglu) {
     if (out_dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
@@ -811,7 +840,7 @@ extern "C" int ts_gemm_skinny_normed(const void* resid16, const float* sumsq, in
 // resid[M, N] += bf16(x * w^T) in place, resid16 = bf16(resid), and sumsq_out[m * (N / 16) + n / 16]
 // = sum over the 16 columns from n of the new resid[m, .]^2 (RESID above). M <= 16; sumsq_out
 // holds M * N / 16 floats. Where ts_gemm_skinny_to_stream_parts(M, N, K) says so, the parts are of 8
-// columns: sumsq_out[m * (N / 8) + n / 8], M * N / 8 floats.
+// columns: sumsq_out[m * (N / 8) + n / 8], M * N / 8 floats (up to 2 N).
 extern "C" int ts_gemm_skinny_to_stream_parts(int M, int N, int K) { return to_stream_takes_h8(M, N, K) ? N / 8 : N / 16; }
 
 extern "C" int ts_gemm_skinny_to_stream(const void* x, const void* w, float* resid, void* resid16, float* sumsq_out,
@@ -821,9 +850,13 @@ extern "C" int ts_gemm_skinny_to_stream(const void* x, const void* w, float* res
   if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
   SkinnyNorm nrm = SkinnyNorm();
   nrm.resid_out = resid; nrm.resid16_out = (bf16*)resid16; nrm.sumsq_out = sumsq_out;
-  if (to_stream_takes_h8(M, N, K))
-    return launch(gemm_skinny_h8_kernel<bf16, false, false, true, SK_H8_TALL_WARPS, SK_H8_TALL_PF>, N / 8, SK_H8_TALL_WARPS * 32, 0,
-                  stream, (const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, nrm);
+  if (to_stream_takes_h8(M, N, K)) {
+    if (M <= 8)
+      return launch(gemm_skinny_h8_kernel<bf16, false, false, true, SK_H8_TALL_WARPS, SK_H8_TALL_PF, 1>, N / 8, SK_H8_TALL_WARPS * 32,
+                    0, stream, (const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, nrm);
+    return launch(gemm_skinny_h8_kernel<bf16, false, false, true, SK_H8_TALL_WARPS, SK_H8_TALL_PF, 2>, N / 8, SK_H8_TALL_WARPS * 32,
+                  0, stream, (const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, nrm);
+  }
   if (M <= 8)
     return launch_skinny<bf16, 1, 1, false, 4, false, true>((const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, stream, nrm);
   return launch_skinny<bf16, 2, 1, false, 4, false, true>((const bf16*)x, (const bf16*)w, (bf16*)nullptr, M, N, K, stream, nrm);

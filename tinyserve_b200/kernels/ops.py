@@ -323,7 +323,7 @@ def decode_splits(num_decode: int, num_kv_heads: int, group: int, max_context_le
 
 CLUSTER_MERGE = True       # the TMA decode kernel merges 2 to 8 key ranges inside a thread-block cluster
 CLUSTER_MAX = 8            # the portable cluster size
-CLUSTER_ROOM = 16          # CTA slots left free per CTA of a cluster
+CLUSTER_ROOM = 18          # CTA slots left free per CTA of a cluster
 CLUSTER_FILL = 0.82        # and clusters of three or more fill at most this much of the machine
 
 
@@ -338,8 +338,9 @@ def choose_splits(ctas: int, slots: int, most: int, cluster: bool = False) -> in
     cheaper but needs all CTAs of a cluster to find room on one GPC at the same moment, while the
     kernel before it is still leaving. The more CTAs a cluster has, the more of the machine must
     stay free for that: measured at batch 1 to 24 (16 / 8 heads of 128), the best number of ranges
-    was each time the largest s <= 8 with ``s * ctas <= slots - 16 s`` (batch 8: 5 ranges, 0.95 ms
-    a step; 6 ranges, which fill 86% of the slots, 1.04 ms; without clusters 1.02 ms), except at
+    was each time the largest s <= 8 with ``s * ctas <= slots - 18 s`` (batch 8: 5 ranges, 0.95 ms
+    a step; 6 ranges, which fill 86% of the slots, 1.04 ms; without clusters 1.02 ms; batch 9: 5 ranges
+    fill 81%, 0.97 ms, 4 ranges 0.93 ms; batch 7: 6 ranges, 76%, are the best), except at
     batch 16, where 3 ranges pass that rule and fill 86%: 1.31 ms a step, with now and then a layer
     whose attention takes twice as long, against 1.21 ms with 2 ranges. Hence the second bound on
     what clusters of three or more may fill."""
@@ -726,11 +727,12 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
 # rows' sums of squares, and the next product normalises that copy while it loads it. It saves two
 # of seven launches per layer. Measured on B200 (Qwen3-0.6B sizes, 1,024-token contexts, with the
 # weights prefetched into L2): the decode step gains 6.7 % at batch 1, 6.3 % at 2, 1.3 % at 4,
-# 0.9 % at 8 and loses 2 % at 16 (the 16-row variants of the product run out of registers), hence
-# up to 8 rows. (Before the weights were prefetched the norm kernels hid behind the next product's
-# weight stream and the fusion gained nothing.)
+# 0.9 % at 8. With the 16-row forms of the products in tiles of 16 weight rows it lost 2 % at 16 rows
+# (they ran out of registers); with those in tiles of 8 weight rows it gains 1.3 % at 9 rows and is
+# level at 12 and 16, hence up to 16 rows, the most the skinny kernels take. (Before the weights were
+# prefetched the norm kernels hid behind the next product's weight stream and the fusion gained nothing.)
 FUSE_STREAM_NORM = True
-STREAM_FUSE_MAX_ROWS = 8
+STREAM_FUSE_MAX_ROWS = 16
 
 
 STREAM_FUSE_MAX_WIDTH = 2048      # 128 parts of 16 columns: what a warp of the consumer adds up
@@ -748,14 +750,14 @@ def can_stream_fuse(m: int, n: int, k: int, width: int, dtype: torch.dtype, devi
 def gemm_to_stream(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, resid16: torch.Tensor,
                    sumsq: torch.Tensor) -> torch.Tensor:
     """``resid[M, N] += bf16(x[M, K] @ w[N, K]^T)`` in place (float32 stream); ``resid16`` gets
-    the new stream in bf16 and ``sumsq`` (at least ``N`` floats of scratch) the rows' sums of squares in
+    the new stream in bf16 and ``sumsq`` (at least ``2 N`` floats of scratch) the rows' sums of squares in
     parts: returned as a view ``[M, parts]`` with ``parts`` = ``N / 16`` or, where the kernel cuts the
     output into tiles of 8 columns, ``N / 8``; both for the product that normalises the stream next
     (:func:`gemm_normed`). bf16, ``M <= 16``."""
     m, k = x.shape
     n = w.shape[0]
     if (w.shape[1] != k or tuple(resid.shape) != (m, n) or resid.dtype != torch.float32 or sumsq.dtype != torch.float32
-            or sumsq.numel() < n or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
+            or sumsq.numel() < 2 * n or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
             or tuple(resid16.shape) != (m, n) or resid16.dtype != torch.bfloat16):
         raise KernelError("gemm_to_stream: shape or dtype mismatch")
     _check(_fn("ts_gemm_skinny_to_stream")(_dev(x, "x"), _dev(w, "w"), _dev(resid, "resid"), _dev(resid16, "resid16"),

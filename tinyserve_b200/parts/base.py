@@ -220,9 +220,9 @@ class ResidualStream:
 
     def fusion_buffers(self, ctx: "StepContext") -> tuple[torch.Tensor, torch.Tensor]:
         """Scratch for the stream's copy in the model dtype and for the parts of the rows' sums
-        of squares (one float per column)."""
+        of squares (up to 16 rows x a part per 8 columns: two floats per column)."""
         if self._sumsq_buf is None:
-            self._sumsq_buf = ctx.arena.take_step((self.resid.shape[1],), torch.float32)
+            self._sumsq_buf = ctx.arena.take_step((2 * self.resid.shape[1],), torch.float32)
             self._resid16_buf = ctx.arena.take_step(tuple(self.resid.shape), ctx.dtype)
         return self._resid16_buf, self._sumsq_buf
 

@@ -7,7 +7,7 @@ has drawn so far. So the noise a request draws does not depend on its batch-mate
 prompt was cut into portions, or on being recomputed after a preemption (upstream keeps a
 ``torch.Generator`` per seeded request for the same end, src/tinyserve/engine.py:126-147). The
 logits it is applied to are the model's: in float32 they do not depend on the batch either; in
-bfloat16 they do within rounding (decode steps of up to 8 rows fold the RMSNorm into the products
+bfloat16 they do within rounding (decode steps of up to 16 rows fold the RMSNorm into the products
 around it, with other rounding points than the norm kernel that larger steps run), so a bfloat16
 request may draw another token at a near-tie when it runs in a batch of another size.
 """
