@@ -569,15 +569,15 @@ static int launch_skinny_stream(const bf16* x, const bf16* w, TOut* out, int M, 
   return launch(kern, dim3(tiles < ctas ? tiles : ctas), SK_THREADS, smem, stream, x, w, out, M, N, K);
 }
 
-// The forms of up to 8 rows with 8 weight rows per tile instead of 16: the operands change places, x is
-// the A operand (its rows g; rows g + 8 of the tile are zero) and the weights the B operand (weight
+// The forms of up to 16 rows with 8 weight rows per tile instead of 16: the operands change places, x is
+// the A operand (its rows g, and g + 8 where there are more than 8) and the weights the B operand (weight
 // row g, 8 per tile), so a lane still loads 8 consecutive k of "its" weight row and of "its" x row
 // for two m16n8k16. An SM takes in about 60 GB/s whatever the kernel, so a product lasts as long as
 // the SM with the most weights needs, and units of half the size spread better: N = 1,024 (o, down) is
 // 64 CTAs of 64 or 96 KB in the 16-row tall form and 128 CTAs of 32 or 48 KB here; the 192 CTAs of
 // gate/up (two of 64 KB on 44 of the 148 SMs) become 384 of 32 KB (three on 88 SMs). Measured on B200,
 // Qwen3-0.6B sizes, ms a decode step with o and down in this form: batch 1 0.758 -> 0.708, batch 8
-// 0.841 -> 0.829. K is split between the warps of the CTA and all its weights are in flight at once
+// 0.841 -> 0.829; with gate/up too 0.683 and 0.816. K is split between the warps of the CTA and all its weights are in flight at once
 // (K <= PF * WARPS * 32). FUSE, NORMX, RESID as in gemm_skinny_kernel; RESID leaves the sums of
 // squares per 8 columns (N / 8 parts a row).
 // XR = 1: up to 8 rows of x; XR = 2: up to 16 (the tile's rows g + 8 are then x rows too).
