@@ -37,3 +37,33 @@ def test_key_ranges_at_the_measured_batches() -> None:
 def test_without_cluster_merge_the_old_rule_holds(monkeypatch) -> None:
     monkeypatch.setattr(ops, "CLUSTER_MERGE", False)
     assert ops.choose_splits(64, 444, 64, cluster=True) == ops.choose_splits(64, 444, 64) == 6
+
+
+def test_which_tiles_the_tcgen05_product_takes() -> None:
+    """Pairs of CTAs (256-row tiles) where those fill at least 85 % of the rounds they take on 74 pairs,
+    single CTAs (128-row tiles) where only those do on 148 SMs, else the vendor library."""
+    # 2,048 rows: qkv of the 0.6B sizes (8 x 16 pair tiles: two rounds, 86 %) and of the 8B sizes
+    assert ops.tcgen05_tiles(2048, 4096, 256) == "pairs"
+    assert ops.tcgen05_tiles(2048, 6144, 256) == "pairs"
+    # gate/up with the activation in the epilogue: tiles of 128 output columns
+    assert ops.tcgen05_tiles(2048, 3072, 128) == "pairs"
+    # narrow outputs (o and down of the 0.6B sizes: 32 pair tiles) and 320 tiles of 2.2 rounds: the library
+    assert ops.tcgen05_tiles(2048, 1024, 256) == ""
+    assert ops.tcgen05_tiles(2048, 5120, 256) == ""
+    # nine 128-row tiles x sixteen fill 148 SMs (97 %), five 256-row tiles x sixteen do not fill 74 pairs twice
+    assert ops.tcgen05_tiles(1152, 2048, 128) == "single"
+    assert ops.tcgen05_tiles(2304, 2048, 128) == "pairs"
+    for m in (128, 512, 2048, 8192):
+        for n in (1024, 4096, 24576, 151936):
+            kind = ops.tcgen05_tiles(m, n, 256)
+            if kind == "pairs":
+                assert ops.tcgen05_pairs_fill_the_machine(m, n, 256)
+            elif kind == "single":
+                assert ops.tcgen05_fills_the_machine(m, n, 256) and not ops.tcgen05_pairs_fill_the_machine(m, n, 256)
+            else:
+                assert not ops.tcgen05_fills_the_machine(m, n, 256)
+
+
+def test_pairs_can_be_switched_off(monkeypatch) -> None:
+    monkeypatch.setattr(ops, "TCGEN05_PAIR", False)
+    assert ops.tcgen05_tiles(2048, 4096, 256) == "single"
