@@ -67,3 +67,22 @@ def test_which_tiles_the_tcgen05_product_takes() -> None:
 def test_pairs_can_be_switched_off(monkeypatch) -> None:
     monkeypatch.setattr(ops, "TCGEN05_PAIR", False)
     assert ops.tcgen05_tiles(2048, 4096, 256) == "single"
+
+
+def test_parts_of_the_sums_of_squares_that_the_stream_product_leaves() -> None:
+    """``ts_gemm_skinny_to_stream`` cuts narrow outputs into tiles of 8 columns (N / 8 parts of the rows'
+    sums of squares) where that spreads the weights better over the SMs and all of K fits a CTA's loads in
+    flight, else into tiles of 16; the rule is a host function of the library, so it runs without a GPU.
+    The product that folds the norm in adds up at most 128 parts a row."""
+    from tinyserve_b200.kernels.build import library
+
+    parts = library().ts_gemm_skinny_to_stream_parts
+    assert parts(1, 1024, 2048) == parts(8, 1024, 3072) == parts(16, 1024, 2048) == 128      # o and down of the 0.6B sizes
+    assert parts(8, 1024, 4096) == 64                  # K too long for one CTA's loads in flight
+    assert parts(8, 2048, 1024) == 128                 # 128 tiles of 16 columns: halves spread no better
+    assert parts(8, 4096, 4096) == 256
+    for n in range(16, 2049, 16):
+        for m in (1, 8, 9, 16):
+            p = parts(m, n, 1024)
+            assert p in (n // 16, n // 8)
+            assert p == n // 16 or p <= 128
