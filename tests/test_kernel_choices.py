@@ -74,9 +74,12 @@ def test_parts_of_the_sums_of_squares_that_the_stream_product_leaves() -> None:
     sums of squares) where that spreads the weights better over the SMs and all of K fits a CTA's loads in
     flight, else into tiles of 16; the rule is a host function of the library, so it runs without a GPU.
     The product that folds the norm in adds up at most 128 parts a row."""
-    from tinyserve_b200.kernels.build import library
+    from tinyserve_b200.kernels.build import KernelBuildError, library
 
-    parts = library().ts_gemm_skinny_to_stream_parts
+    try:
+        parts = library().ts_gemm_skinny_to_stream_parts
+    except (KernelBuildError, OSError) as e:      # no nvcc or no CUDA runtime on this host
+        pytest.skip(f"the kernel library cannot be built or loaded here: {e}")
     assert parts(1, 1024, 2048) == parts(8, 1024, 3072) == parts(16, 1024, 2048) == 128      # o and down of the 0.6B sizes
     assert parts(8, 1024, 4096) == 64                  # K too long for one CTA's loads in flight
     assert parts(8, 2048, 1024) == 128                 # 128 tiles of 16 columns: halves spread no better
